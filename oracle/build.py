@@ -1,0 +1,144 @@
+"""Build recipe for the parity checkers (TEST INFRASTRUCTURE ONLY).
+
+Two artefacts, neither of which the product path may load:
+
+* ``oracle/libattn_oracle.so`` — the plain-C restatement in ``oracle/attn_oracle.c``.
+* ``oracle/_ref/libghref_<flavour>.so`` — the reference project's own amd64/OpenMP attention operations,
+  compiled from the reference tree WHERE IT LIES (no source is copied into this repository) through
+  ``oracle/ref_harness.cc``.  Only built when the reference tree is present; the built libraries travel
+  with the repository snapshot to machines that do not have the tree.
+
+Two things stand between GCC 13 and the reference headers, and both are handled without touching arithmetic:
+
+1. ``glog`` is not installed: ``oracle/shim/glog/logging.h`` supplies the macros the headers use.
+2. GCC 13 rejects the out-of-class member definitions in ``src/arch/amd64/llama2/ops.hh`` because their
+   template heads omit the class's ``requires ModelConfig<Config>`` clause (GCC 12, which the reference's CI
+   pins, accepted them).  A temporary copy of that ONE header with the clause inserted after each such
+   template head is written to a scratch directory outside the repository and put first on the include path.
+
+Flavours: ``native`` uses the reference's own flags (``etc/cflags.cmake``: -O3 -march=native -ffast-math
+-fsingle-precision-constant, plus OpenMP); ``v3`` swaps -march=native for -march=x86-64-v3 so that the
+library still loads on a host whose CPU lacks the build host's extensions.  ``load_ref()`` picks ``native``
+only when the running CPU advertises every flag the build host had.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import re
+import shutil
+import subprocess
+import tempfile
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+REF_ROOT = Path(os.environ.get("GLINTHAWK_REFERENCE", "/root/reference"))
+REF_OUT = HERE / "_ref"
+ORACLE_SO = HERE / "libattn_oracle.so"
+
+_REF_FLAGS = ["-std=c++20", "-O3", "-DNDEBUG", "-ffast-math", "-fsingle-precision-constant", "-fopenmp",
+              "-DTARGET_PLATFORM_AMD64", "-shared", "-fPIC", "-w"]
+_TEMPLATE_HEAD = "template<typename Config, typename DType, typename ContextType>"
+
+
+def _cpu_flags() -> list[str]:
+    try:
+        for line in Path("/proc/cpuinfo").read_text().splitlines():
+            if line.startswith("flags"):
+                return sorted(set(line.split(":", 1)[1].split()))
+    except OSError:
+        pass
+    return []
+
+
+def _newer(target: Path, *sources: Path) -> bool:
+    return target.exists() and all(target.stat().st_mtime >= s.stat().st_mtime for s in sources)
+
+
+def build_oracle(force: bool = False) -> Path:
+    srcs = [HERE / "attn_oracle.c", HERE / "attn_oracle_impl.inc"]
+    if not force and _newer(ORACLE_SO, *srcs):
+        return ORACLE_SO
+    cmd = ["gcc", "-O2", "-march=x86-64-v3", "-fopenmp", "-shared", "-fPIC", "-Wall", "-Wextra",
+           str(srcs[0]), "-o", str(ORACLE_SO), "-lm"]
+    subprocess.run(cmd, check=True)
+    return ORACLE_SO
+
+
+def _patched_include_dir(scratch: Path) -> Path:
+    """A scratch include root holding the one header GCC 13 needs adjusted; everything else resolves
+    to the reference tree through the second -I."""
+    src = REF_ROOT / "src" / "arch" / "amd64" / "llama2" / "ops.hh"
+    text = src.read_text()
+    patched, n = re.subn(re.escape(_TEMPLATE_HEAD) + r"\n(?!requires)",
+                         _TEMPLATE_HEAD + "\nrequires ModelConfig<Config>\n", text)
+    # the class declaration itself already carries the clause (the look-ahead skips it)
+    if n < 6:
+        raise RuntimeError(f"expected at least 6 out-of-class definitions to adjust, found {n}")
+    dst_dir = scratch / "arch" / "amd64" / "llama2"
+    dst_dir.mkdir(parents=True)
+    (dst_dir / "ops.hh").write_text(patched)
+    # "../common/ops.hh" is resolved relative to the including file first
+    os.symlink(REF_ROOT / "src" / "arch" / "amd64" / "common", scratch / "arch" / "amd64" / "common")
+    return scratch
+
+
+def ref_available() -> bool:
+    return (REF_ROOT / "src" / "arch" / "amd64" / "llama2" / "ops.hh").exists()
+
+
+def build_ref(force: bool = False) -> list[Path]:
+    """Compile the reference's amd64 attention operations behind ref_harness.cc (both flavours)."""
+    if not ref_available():
+        return sorted(REF_OUT.glob("libghref_*.so"))
+    REF_OUT.mkdir(exist_ok=True)
+    harness = HERE / "ref_harness.cc"
+    outs = {"native": REF_OUT / "libghref_native.so", "v3": REF_OUT / "libghref_v3.so"}
+    if not force and all(_newer(o, harness, HERE / "shim" / "glog" / "logging.h") for o in outs.values()):
+        return list(outs.values())
+    scratch = Path(tempfile.mkdtemp(prefix="ghref_build_"))
+    try:
+        inc = _patched_include_dir(scratch)
+        extra_srcs = [str(REF_ROOT / "src" / "util" / "demangle.cc")]
+        for flavour, out in outs.items():
+            march = "-march=native" if flavour == "native" else "-march=x86-64-v3"
+            cmd = ["g++", *_REF_FLAGS, march, f"-I{HERE / 'shim'}", f"-I{inc}", f"-I{REF_ROOT / 'src'}",
+                   str(harness), *extra_srcs, "-o", str(out)]
+            subprocess.run(cmd, check=True)
+        (REF_OUT / "BUILD_INFO.json").write_text(json.dumps({
+            "compiler": subprocess.run(["g++", "--version"], capture_output=True, text=True).stdout.splitlines()[0],
+            "flags": _REF_FLAGS,
+            "native_cpu_flags": _cpu_flags(),
+            "sources": "reference tree: src/arch/amd64/llama2/ops.hh, src/models/llama2/context.hh (+ includes)",
+        }, indent=1))
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)
+    return list(outs.values())
+
+
+def load_oracle() -> ctypes.CDLL:
+    return ctypes.CDLL(str(build_oracle()))
+
+
+def ref_flavour() -> str | None:
+    """Which prebuilt reference library this host can run, or None when there is none."""
+    native, v3 = REF_OUT / "libghref_native.so", REF_OUT / "libghref_v3.so"
+    info = REF_OUT / "BUILD_INFO.json"
+    if native.exists() and info.exists():
+        need = set(json.loads(info.read_text()).get("native_cpu_flags", []))
+        if need and need <= set(_cpu_flags()):
+            return "native"
+    if v3.exists():
+        return "v3"
+    return None
+
+
+def load_ref() -> ctypes.CDLL | None:
+    fl = ref_flavour()
+    return ctypes.CDLL(str(REF_OUT / f"libghref_{fl}.so")) if fl else None
+
+
+if __name__ == "__main__":
+    print("oracle:", build_oracle(force=True))
+    print("reference:", [str(p) for p in build_ref(force=True)] or "reference tree absent, nothing built")
