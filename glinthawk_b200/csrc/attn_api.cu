@@ -1,0 +1,999 @@
+// C ABI of the attention stage (see include/glinthawk_attn.h for the contract of every entry point).
+#include "../../include/glinthawk_attn.h"
+
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "gh_driver.hh"
+#include "gh_kernels.cuh"
+#include "kv_pool.hh"
+#include "planner.hh"
+
+using namespace gh;
+
+namespace {
+
+constexpr uint32_t kRing = 16;       // batch descriptions that may be in flight at once
+constexpr uint32_t kHostStages = 4;  // staging sets for the host-buffer entry point
+constexpr uint32_t kExtraItems = 2048;
+
+struct DeviceGuard
+{
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard( int dev )
+  {
+    if ( cudaGetDevice( &prev ) != cudaSuccess )
+      prev = -1;
+    if ( prev != dev )
+      ok = cudaSetDevice( dev ) == cudaSuccess;
+  }
+  ~DeviceGuard()
+  {
+    if ( prev >= 0 )
+      cudaSetDevice( prev );
+  }
+};
+
+// One uploaded batch description: [CtxMeta x max_batch][WorkItem x max_items][ptr x max_batch][pos x max_batch]
+struct RingEntry
+{
+  char* host = nullptr; // pinned
+  char* dev = nullptr;
+  cudaEvent_t last_use = nullptr;
+  cudaStream_t last_stream = nullptr;
+  bool used = false, multi_stream = false;
+};
+
+struct HostStage
+{
+  char* q = nullptr;
+  char* kv = nullptr;
+  char* xb = nullptr;
+  char* raw = nullptr; // conversion staging, sized for fp32
+  cudaEvent_t done = nullptr;
+  bool used = false;
+};
+
+} // namespace
+
+struct gh_attn
+{
+  gh_attn_config cfg {};
+  Shape sh {};
+  size_t elem = 0;
+  int device = 0;
+  uint32_t sm_count = 148;
+  KvPool pool;
+  std::string err;
+  gh_attn_stats stats {};
+
+  const void* rope_cos = nullptr;
+  const void* rope_sin = nullptr;
+
+  // batch descriptions
+  uint32_t max_items = 0;
+  size_t off_items = 0, off_ptrs = 0, off_pos = 0, entry_bytes = 0;
+  RingEntry ring[kRing];
+  uint32_t ring_next = 0;
+  int cur = -1; // ring entry of the batch set up last, -1 = none
+  uint32_t cur_batch = 0, cur_items = 0;
+  std::vector<int32_t> cur_slots;
+  std::vector<uint32_t> cur_pos;
+
+  // split partials
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  int* counters = nullptr;
+  uint32_t* dev_error = nullptr;
+
+  bool use_mma = false;
+  CUtensorMap kv_map {};
+
+  HostStage stage[kHostStages];
+  uint32_t stage_next = 0;
+};
+
+namespace {
+
+int fail( gh_attn* h, int status, const std::string& msg )
+{
+  if ( h != nullptr )
+    h->err = msg;
+  return status;
+}
+
+int cuda_fail( gh_attn* h, const char* what, cudaError_t e )
+{
+  (void)cudaGetLastError();
+  return fail( h, e == cudaErrorMemoryAllocation ? GH_ERR_OOM : GH_ERR_CUDA, std::string( what ) + ": " + cudaGetErrorString( e ) );
+}
+
+#define GH_CUDA( h, expr )                                                                                             \
+  do {                                                                                                                 \
+    const cudaError_t e__ = ( expr );                                                                                  \
+    if ( e__ != cudaSuccess )                                                                                          \
+      return cuda_fail( ( h ), #expr, e__ );                                                                           \
+  } while ( 0 )
+
+size_t dtype_size( uint32_t dt )
+{
+  return dt == GH_F32 ? 4 : 2;
+}
+
+bool dtype_ok( uint32_t dt )
+{
+  return dt == GH_F16 || dt == GH_F32 || dt == GH_BF16;
+}
+
+// Claims the next batch-description buffer, waiting (on the host) only if the device still reads it.
+int ring_claim( gh_attn* h, int* idx )
+{
+  const uint32_t k = h->ring_next;
+  h->ring_next = ( k + 1 ) % kRing;
+  RingEntry& r = h->ring[k];
+  if ( r.used ) {
+    if ( r.multi_stream )
+      GH_CUDA( h, cudaDeviceSynchronize() );
+    else
+      GH_CUDA( h, cudaEventSynchronize( r.last_use ) );
+  }
+  r.used = false;
+  r.multi_stream = false;
+  r.last_stream = nullptr;
+  *idx = static_cast<int>( k );
+  return GH_OK;
+}
+
+int ring_touch( gh_attn* h, int idx, cudaStream_t st )
+{
+  RingEntry& r = h->ring[idx];
+  if ( r.used && r.last_stream != st )
+    r.multi_stream = true;
+  r.used = true;
+  r.last_stream = st;
+  GH_CUDA( h, cudaEventRecord( r.last_use, st ) );
+  return GH_OK;
+}
+
+CtxMeta* entry_ctx( gh_attn* h, char* base )
+{
+  (void)h;
+  return reinterpret_cast<CtxMeta*>( base );
+}
+WorkItem* entry_items( gh_attn* h, char* base )
+{
+  return reinterpret_cast<WorkItem*>( base + h->off_items );
+}
+void** entry_ptrs( gh_attn* h, char* base )
+{
+  return reinterpret_cast<void**>( base + h->off_ptrs );
+}
+uint32_t* entry_pos( gh_attn* h, char* base )
+{
+  return reinterpret_cast<uint32_t*>( base + h->off_pos );
+}
+
+// Plans `ctx` (kv_off and pos filled in by the caller) and uploads the description into a fresh ring entry.
+int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int* entry, uint32_t* n_items )
+{
+  PlanParams pp;
+  pp.n_kv_heads = h->use_mma ? h->sh.n_kv_heads : h->sh.n_heads;
+  pp.sm_count = h->sm_count;
+  pp.tile = decode_mma_tile_tokens();
+  pp.fixed_chunk = h->cfg.decode_chunk;
+  pp.max_items = h->max_items;
+  Plan plan;
+  if ( !plan_batch( pp, ctx, plan ) )
+    return fail( h, GH_ERR_INVALID, "batch does not fit the work-item buffer" );
+
+  int idx;
+  if ( const int rc = ring_claim( h, &idx ); rc != GH_OK )
+    return rc;
+  RingEntry& r = h->ring[idx];
+  std::memcpy( entry_ctx( h, r.host ), ctx.data(), ctx.size() * sizeof( CtxMeta ) );
+  std::memcpy( entry_items( h, r.host ), plan.items.data(), plan.items.size() * sizeof( WorkItem ) );
+  // one copy covers the context records and the items (they are adjacent up to the items actually used)
+  const size_t bytes = h->off_items + plan.items.size() * sizeof( WorkItem );
+  GH_CUDA( h, cudaMemcpyAsync( r.dev, r.host, bytes, cudaMemcpyHostToDevice, st ) );
+  if ( const int rc = ring_touch( h, idx, st ); rc != GH_OK )
+    return rc;
+  *entry = idx;
+  *n_items = static_cast<uint32_t>( plan.items.size() );
+  h->stats.last_items = *n_items;
+  h->stats.last_chunk = plan.chunk;
+  return GH_OK;
+}
+
+DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, long long layer_off, const void* q, void* xb )
+{
+  DecodeArgs a {};
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.ctx = entry_ctx( h, h->ring[entry].dev );
+  a.items = entry_items( h, h->ring[entry].dev );
+  a.n_items = n_items;
+  a.arena = h->pool.arena();
+  a.layer_off = layer_off;
+  a.q = q;
+  a.xb = xb;
+  a.part_o = h->part_o;
+  a.part_ml = h->part_ml;
+  a.counters = h->counters;
+  a.dev_error = h->dev_error;
+  a.sm_count = h->sm_count;
+  return a;
+}
+
+int run_decode( gh_attn* h, const DecodeArgs& a, bool allow_mma, cudaStream_t st )
+{
+  cudaError_t e;
+  if ( h->use_mma && allow_mma ) {
+    e = launch_decode_mma( a, &h->kv_map, st, &h->stats.kernel_launches );
+    h->stats.last_kernel = 1;
+  } else {
+    e = launch_decode_generic( a, st, &h->stats.kernel_launches );
+    h->stats.last_kernel = 0;
+  }
+  if ( e != cudaSuccess )
+    return cuda_fail( h, "decode kernel launch", e );
+  return GH_OK;
+}
+
+int check_batch_ready( gh_attn* h, uint32_t layer )
+{
+  if ( h->cur < 0 )
+    return fail( h, GH_ERR_STATE, "no batch: call gh_attn_batch_begin first" );
+  if ( layer >= h->sh.n_layers )
+    return fail( h, GH_ERR_INVALID, "layer " + std::to_string( layer ) + " is not hosted" );
+  return GH_OK;
+}
+
+// Context::prepare for every active prompt of the current batch (src/models/llama2/model.hh:617-621).
+int prepare_layer( gh_attn* h, uint32_t layer )
+{
+  if ( !h->pool.paged() )
+    return GH_OK;
+  for ( uint32_t i = 0; i < h->cur_batch; i++ ) {
+    if ( h->cur_slots[i] < 0 )
+      continue;
+    const int rc = h->pool.prepare( h->cur_slots[i], layer, h->cur_pos[i], false, h->err );
+    if ( rc != GH_OK )
+      return rc;
+  }
+  return GH_OK;
+}
+
+} // namespace
+
+// ---------------------------------------------------------------------------------------------------------
+
+extern "C" {
+
+const char* gh_status_string( int status )
+{
+  switch ( status ) {
+    case GH_OK: return "ok";
+    case GH_ERR_INVALID: return "invalid argument";
+    case GH_ERR_CUDA: return "CUDA error";
+    case GH_ERR_NO_SLOT: return "no free context slot";
+    case GH_ERR_CAPACITY: return "token position beyond slot capacity";
+    case GH_ERR_OOM: return "out of device memory";
+    case GH_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case GH_ERR_STATE: return "call out of order";
+    case GH_ERR_NOT_FOUND: return "unknown context id";
+    default: return "unknown status";
+  }
+}
+
+int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
+{
+  if ( cfg == nullptr || out == nullptr || cfg->struct_size != sizeof( gh_attn_config ) )
+    return GH_ERR_INVALID;
+  *out = nullptr;
+  if ( cfg->n_heads == 0 || cfg->n_kv_heads == 0 || cfg->n_heads % cfg->n_kv_heads != 0
+       || cfg->n_heads / cfg->n_kv_heads > (uint32_t)kMaxGroup || cfg->head_size == 0 || cfg->head_size % 8 != 0
+       || cfg->head_size > (uint32_t)kMaxHeadSize || cfg->seq_len == 0 || cfg->n_layers_hosted == 0
+       || !dtype_ok( cfg->dtype ) || cfg->max_batch == 0 || cfg->max_batch > (uint32_t)kMaxBatch
+       || cfg->max_contexts == 0 || cfg->backing > GH_BACKING_PAGED )
+    return GH_ERR_INVALID;
+
+  int n_dev = 0;
+  if ( cudaGetDeviceCount( &n_dev ) != cudaSuccess || cfg->device < 0 || cfg->device >= n_dev ) {
+    (void)cudaGetLastError();
+    return GH_ERR_CUDA; // no CPU path exists: without a usable device the stage cannot be created
+  }
+
+  std::unique_ptr<gh_attn> h( new gh_attn() );
+  h->cfg = *cfg;
+  h->device = cfg->device;
+  DeviceGuard guard( h->device );
+  if ( !guard.ok )
+    return GH_ERR_CUDA;
+  GH_CUDA( h.get(), cudaFree( nullptr ) );
+
+  cudaDeviceProp prop {};
+  GH_CUDA( h.get(), cudaGetDeviceProperties( &prop, h->device ) );
+  h->sm_count = static_cast<uint32_t>( prop.multiProcessorCount );
+
+  Shape& sh = h->sh;
+  sh.n_heads = cfg->n_heads;
+  sh.n_kv_heads = cfg->n_kv_heads;
+  sh.group = cfg->n_heads / cfg->n_kv_heads;
+  sh.head_size = cfg->head_size;
+  sh.kv_dim = cfg->n_kv_heads * cfg->head_size;
+  sh.seq_len = cfg->seq_len;
+  sh.n_layers = cfg->n_layers_hosted;
+  sh.row_elems = 2 * sh.kv_dim;
+  h->elem = dtype_size( cfg->dtype );
+
+  h->use_mma = !cfg->force_generic && decode_mma_supported( sh, cfg->dtype );
+
+  PoolGeometry g;
+  g.elem_bytes = h->elem;
+  g.row_bytes = static_cast<size_t>( sh.row_elems ) * h->elem;
+  g.layer_bytes = g.row_bytes * sh.seq_len;
+  g.slot_bytes = g.layer_bytes * sh.n_layers;
+  g.seq_len = sh.seq_len;
+  g.n_layers = sh.n_layers;
+  g.max_contexts = cfg->max_contexts;
+  const uint32_t tile = h->use_mma ? decode_mma_tile_tokens() : 1;
+  int rc = h->pool.init( g, cfg->backing == GH_BACKING_PAGED, h->device, cfg->page_budget, tile, h->err );
+  if ( rc != GH_OK ) {
+    std::fprintf( stderr, "gh_attn_create: %s\n", h->err.c_str() );
+    return rc;
+  }
+
+  // batch-description ring
+  h->max_items = cfg->max_batch + kExtraItems;
+  h->off_items = sizeof( CtxMeta ) * cfg->max_batch;
+  h->off_ptrs = h->off_items + sizeof( WorkItem ) * h->max_items;
+  h->off_pos = h->off_ptrs + sizeof( void* ) * cfg->max_batch;
+  h->entry_bytes = ( h->off_pos + sizeof( uint32_t ) * cfg->max_batch + 255 ) / 256 * 256;
+  char* host_all = nullptr;
+  char* dev_all = nullptr;
+  GH_CUDA( h.get(), cudaMallocHost( reinterpret_cast<void**>( &host_all ), h->entry_bytes * kRing ) );
+  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &dev_all ), h->entry_bytes * kRing ) );
+  for ( uint32_t k = 0; k < kRing; k++ ) {
+    h->ring[k].host = host_all + k * h->entry_bytes;
+    h->ring[k].dev = dev_all + k * h->entry_bytes;
+    GH_CUDA( h.get(), cudaEventCreateWithFlags( &h->ring[k].last_use, cudaEventDisableTiming ) );
+  }
+
+  // split partial records: one per (work item, query head)
+  const size_t recs = static_cast<size_t>( h->max_items ) * sh.n_heads;
+  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->part_o ), recs * sh.head_size * sizeof( float ) ) );
+  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->part_ml ), recs * 2 * sizeof( float ) ) );
+  const size_t n_counters = static_cast<size_t>( cfg->max_batch ) * sh.n_heads;
+  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->counters ), n_counters * sizeof( int ) ) );
+  GH_CUDA( h.get(), cudaMemset( h->counters, 0, n_counters * sizeof( int ) ) );
+  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->dev_error ), sizeof( uint32_t ) ) );
+  GH_CUDA( h.get(), cudaMemset( h->dev_error, 0, sizeof( uint32_t ) ) );
+  h->stats.scratch_bytes = recs * ( sh.head_size + 2 ) * sizeof( float ) + n_counters * sizeof( int )
+                           + 2 * h->entry_bytes * kRing;
+
+  if ( h->use_mma ) {
+    const DriverApi* api = driver_api( h->err );
+    if ( api == nullptr )
+      return GH_ERR_CUDA;
+    const uint64_t total_rows = h->pool.arena_bytes() / g.row_bytes;
+    if ( total_rows >= ( 1ull << 32 ) ) {
+      h->use_mma = false; // arena too large for one descriptor; the CUDA-core kernel has no such limit
+    } else {
+      const cuuint64_t dims[2] = { sh.row_elems, total_rows };
+      const cuuint64_t strides[1] = { g.row_bytes };
+      const cuuint32_t box[2] = { 64, decode_mma_tile_tokens() };
+      const cuuint32_t estr[2] = { 1, 1 };
+      const CUresult r = api->TensorMapEncodeTiled(
+        &h->kv_map, cfg->dtype == GH_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+        h->pool.arena(), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE );
+      if ( r != CUDA_SUCCESS ) {
+        h->err = "cuTensorMapEncodeTiled: " + driver_error( api, r );
+        std::fprintf( stderr, "gh_attn_create: %s\n", h->err.c_str() );
+        return GH_ERR_CUDA;
+      }
+      GH_CUDA( h.get(), decode_mma_prepare() );
+    }
+  }
+
+  h->cur_slots.reserve( cfg->max_batch );
+  h->cur_pos.reserve( cfg->max_batch );
+  *out = h.release();
+  return GH_OK;
+}
+
+int gh_attn_destroy( gh_attn_t h )
+{
+  if ( h == nullptr )
+    return GH_ERR_INVALID;
+  DeviceGuard guard( h->device );
+  cudaDeviceSynchronize();
+  for ( auto& s : h->stage ) {
+    cudaFree( s.q );
+    cudaFree( s.kv );
+    cudaFree( s.xb );
+    cudaFree( s.raw );
+    if ( s.done )
+      cudaEventDestroy( s.done );
+  }
+  for ( auto& r : h->ring )
+    if ( r.last_use )
+      cudaEventDestroy( r.last_use );
+  if ( h->ring[0].host )
+    cudaFreeHost( h->ring[0].host );
+  cudaFree( h->ring[0].dev );
+  cudaFree( h->part_o );
+  cudaFree( h->part_ml );
+  cudaFree( h->counters );
+  cudaFree( h->dev_error );
+  h->pool.destroy();
+  (void)cudaGetLastError();
+  delete h;
+  return GH_OK;
+}
+
+const char* gh_attn_last_error( gh_attn_t h )
+{
+  return h != nullptr ? h->err.c_str() : "null handle";
+}
+
+int gh_attn_get_stats( gh_attn_t h, gh_attn_stats* out )
+{
+  if ( h == nullptr || out == nullptr )
+    return GH_ERR_INVALID;
+  DeviceGuard guard( h->device );
+  h->stats.bytes_mapped = h->pool.bytes_mapped();
+  h->stats.bytes_reserved = h->pool.arena_bytes();
+  h->stats.slots_free = h->pool.slots_free();
+  h->stats.slots_allocated = h->pool.slots_allocated();
+  uint32_t flag = 0;
+  GH_CUDA( h, cudaMemcpy( &flag, h->dev_error, sizeof( flag ), cudaMemcpyDeviceToHost ) );
+  h->stats.device_error = flag;
+  *out = h->stats;
+  return GH_OK;
+}
+
+int gh_attn_set_rope_tables( gh_attn_t h, const void* freq_cis_real, const void* freq_cis_imag )
+{
+  if ( h == nullptr || freq_cis_real == nullptr || freq_cis_imag == nullptr )
+    return GH_ERR_INVALID;
+  h->rope_cos = freq_cis_real;
+  h->rope_sin = freq_cis_imag;
+  return GH_OK;
+}
+
+// ---- slot pool ------------------------------------------------------------------------------------------
+
+int gh_slot_acquire( gh_attn_t h, uint32_t context_id, int32_t* slot )
+{
+  if ( h == nullptr || slot == nullptr )
+    return GH_ERR_INVALID;
+  const int rc = h->pool.acquire( context_id, slot );
+  return rc == GH_OK ? rc : fail( h, rc, "no free context slot" );
+}
+
+int gh_slots_acquire_batch( gh_attn_t h, uint64_t batch, const uint32_t* context_ids, int32_t* slots )
+{
+  if ( h == nullptr || ( batch > 0 && ( context_ids == nullptr || slots == nullptr ) ) )
+    return GH_ERR_INVALID;
+  const int rc = h->pool.acquire_batch( batch, context_ids, slots );
+  return rc == GH_OK ? rc : fail( h, rc, "not enough free context slots for the batch" );
+}
+
+int gh_slot_lookup( gh_attn_t h, uint32_t context_id, int32_t* slot )
+{
+  if ( h == nullptr || slot == nullptr )
+    return GH_ERR_INVALID;
+  return h->pool.lookup( context_id, slot );
+}
+
+int gh_slot_release( gh_attn_t h, uint32_t context_id )
+{
+  if ( h == nullptr )
+    return GH_ERR_INVALID;
+  DeviceGuard guard( h->device );
+  return h->pool.release( context_id, h->err );
+}
+
+int gh_slot_prepare( gh_attn_t h, int32_t slot, uint32_t layer, uint32_t pos, int can_release )
+{
+  if ( h == nullptr )
+    return GH_ERR_INVALID;
+  if ( slot == -1 )
+    return GH_OK; // the empty context prepares trivially (context.hh:223-225)
+  DeviceGuard guard( h->device );
+  const int rc = h->pool.prepare( slot, layer, pos, can_release != 0, h->err );
+  if ( rc == GH_ERR_INVALID )
+    h->err = "slot or layer out of range";
+  else if ( rc == GH_ERR_CAPACITY )
+    h->err = "token position " + std::to_string( pos ) + " >= slot capacity " + std::to_string( h->sh.seq_len );
+  return rc;
+}
+
+int gh_slot_layer_ptr( gh_attn_t h, int32_t slot, uint32_t layer, void** ptr )
+{
+  if ( h == nullptr || ptr == nullptr )
+    return GH_ERR_INVALID;
+  if ( slot == -1 ) { // empty context -> empty layer view (context.hh:117-118)
+    *ptr = nullptr;
+    return GH_OK;
+  }
+  if ( !h->pool.valid_slot( slot ) || layer >= h->sh.n_layers )
+    return fail( h, GH_ERR_INVALID, "slot or layer out of range" );
+  *ptr = h->pool.arena() + h->pool.slot_offset( slot ) + h->pool.layer_offset( layer );
+  return GH_OK;
+}
+
+int gh_slot_token_ptr( gh_attn_t h, int32_t slot, uint32_t layer, uint32_t token, void** ptr )
+{
+  if ( h != nullptr && token >= h->sh.seq_len )
+    return fail( h, GH_ERR_CAPACITY, "token beyond slot capacity" );
+  const int rc = gh_slot_layer_ptr( h, slot, layer, ptr );
+  if ( rc == GH_OK && *ptr != nullptr )
+    *ptr = static_cast<char*>( *ptr ) + static_cast<size_t>( token ) * h->pool.geometry().row_bytes;
+  return rc;
+}
+
+size_t gh_slot_bytes( gh_attn_t h )
+{
+  return h != nullptr ? h->pool.geometry().slot_bytes : 0;
+}
+
+// ---- fused hot path -------------------------------------------------------------------------------------
+
+int gh_attn_batch_begin( gh_attn_t h, uint64_t batch, const int32_t* slots, const uint32_t* pos, void* stream )
+{
+  if ( h == nullptr || batch == 0 || batch > h->cfg.max_batch || slots == nullptr || pos == nullptr )
+    return fail( h, GH_ERR_INVALID, "bad batch arguments" );
+  DeviceGuard guard( h->device );
+  std::vector<CtxMeta> ctx( batch );
+  for ( uint64_t i = 0; i < batch; i++ ) {
+    CtxMeta& c = ctx[i];
+    c = CtxMeta {};
+    c.pos = pos[i];
+    if ( slots[i] == -1 ) {
+      c.kv_off = kInactive;
+      continue;
+    }
+    if ( !h->pool.valid_slot( slots[i] ) )
+      return fail( h, GH_ERR_INVALID, "slot out of range at batch index " + std::to_string( i ) );
+    if ( pos[i] >= h->sh.seq_len )
+      return fail( h, GH_ERR_CAPACITY,
+                   "token position " + std::to_string( pos[i] ) + " >= slot capacity at batch index " + std::to_string( i ) );
+    c.kv_off = h->pool.slot_offset( slots[i] );
+  }
+  h->cur = -1;
+  int entry;
+  uint32_t n_items;
+  if ( const int rc = plan_and_upload( h, ctx, static_cast<cudaStream_t>( stream ), &entry, &n_items ); rc != GH_OK )
+    return rc;
+  h->cur = entry;
+  h->cur_batch = static_cast<uint32_t>( batch );
+  h->cur_items = n_items;
+  h->cur_slots.assign( slots, slots + batch );
+  h->cur_pos.assign( pos, pos + batch );
+  return GH_OK;
+}
+
+int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new, void* stream )
+{
+  if ( h == nullptr || kv_new == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
+    return rc;
+  if ( h->rope_cos == nullptr )
+    return fail( h, GH_ERR_STATE, "RoPE tables not set" );
+  DeviceGuard guard( h->device );
+  if ( const int rc = prepare_layer( h, layer ); rc != GH_OK )
+    return rc;
+  AppendArgs a {};
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.batch = h->cur_batch;
+  a.ctx = entry_ctx( h, h->ring[h->cur].dev );
+  a.arena = h->pool.arena();
+  a.layer_off = h->pool.layer_offset( layer );
+  a.q = q_inout;
+  a.kv_new = kv_new;
+  a.rope_cos = h->rope_cos;
+  a.rope_sin = h->rope_sin;
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
+    return cuda_fail( h, "append kernel launch", e );
+  return ring_touch( h, h->cur, st );
+}
+
+int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* stream )
+{
+  if ( h == nullptr || q == nullptr || xb == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
+    return rc;
+  DeviceGuard guard( h->device );
+  if ( const int rc = prepare_layer( h, layer ); rc != GH_OK )
+    return rc;
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  const DecodeArgs a = decode_args( h, h->cur, h->cur_items, h->pool.layer_offset( layer ), q, xb );
+  if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
+    return rc;
+  return ring_touch( h, h->cur, st );
+}
+
+int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new, void* xb, void* stream )
+{
+  if ( const int rc = gh_attn_append( h, layer, q_inout, kv_new, stream ); rc != GH_OK )
+    return rc;
+  return gh_attn_decode( h, layer, q_inout, xb, stream );
+}
+
+int gh_attn_forward_attention_host( gh_attn_t h,
+                                    uint32_t layer,
+                                    uint32_t io_dtype,
+                                    const void* q_host,
+                                    const void* kv_host,
+                                    void* xb_host,
+                                    void* stream )
+{
+  if ( h == nullptr || q_host == nullptr || kv_host == nullptr || xb_host == nullptr || !dtype_ok( io_dtype ) )
+    return fail( h, GH_ERR_INVALID, "bad argument" );
+  if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
+    return rc;
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  const size_t B = h->cur_batch;
+  const size_t q_elems = B * h->sh.n_heads * h->sh.head_size;
+  const size_t kv_elems = B * h->sh.row_elems;
+
+  HostStage& s = h->stage[h->stage_next];
+  h->stage_next = ( h->stage_next + 1 ) % kHostStages;
+  if ( s.q == nullptr ) {
+    const size_t mb = h->cfg.max_batch;
+    GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &s.q ), mb * h->sh.n_heads * h->sh.head_size * h->elem ) );
+    GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &s.kv ), mb * h->sh.row_elems * h->elem ) );
+    GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &s.xb ), mb * h->sh.n_heads * h->sh.head_size * h->elem ) );
+    GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &s.raw ),
+                            mb * ( h->sh.n_heads * h->sh.head_size + h->sh.row_elems ) * sizeof( float ) ) );
+    GH_CUDA( h, cudaEventCreateWithFlags( &s.done, cudaEventDisableTiming ) );
+  }
+  if ( s.used )
+    GH_CUDA( h, cudaEventSynchronize( s.done ) );
+  s.used = true;
+
+  const size_t io = dtype_size( io_dtype );
+  if ( io_dtype == h->cfg.dtype ) {
+    GH_CUDA( h, cudaMemcpyAsync( s.q, q_host, q_elems * io, cudaMemcpyHostToDevice, st ) );
+    GH_CUDA( h, cudaMemcpyAsync( s.kv, kv_host, kv_elems * io, cudaMemcpyHostToDevice, st ) );
+  } else {
+    char* raw_q = s.raw;
+    char* raw_kv = s.raw + q_elems * io;
+    GH_CUDA( h, cudaMemcpyAsync( raw_q, q_host, q_elems * io, cudaMemcpyHostToDevice, st ) );
+    GH_CUDA( h, cudaMemcpyAsync( raw_kv, kv_host, kv_elems * io, cudaMemcpyHostToDevice, st ) );
+    GH_CUDA( h, launch_convert( s.q, h->cfg.dtype, raw_q, io_dtype, q_elems, st, &h->stats.kernel_launches ) );
+    GH_CUDA( h, launch_convert( s.kv, h->cfg.dtype, raw_kv, io_dtype, kv_elems, st, &h->stats.kernel_launches ) );
+  }
+  if ( const int rc = gh_attn_step( h, layer, s.q, s.kv, s.xb, stream ); rc != GH_OK )
+    return rc;
+  if ( io_dtype == h->cfg.dtype ) {
+    GH_CUDA( h, cudaMemcpyAsync( xb_host, s.xb, q_elems * io, cudaMemcpyDeviceToHost, st ) );
+  } else {
+    GH_CUDA( h, launch_convert( s.raw, io_dtype, s.xb, h->cfg.dtype, q_elems, st, &h->stats.kernel_launches ) );
+    GH_CUDA( h, cudaMemcpyAsync( xb_host, s.raw, q_elems * io, cudaMemcpyDeviceToHost, st ) );
+  }
+  GH_CUDA( h, cudaEventRecord( s.done, st ) );
+  return GH_OK;
+}
+
+// ---- the reference's operations, argument for argument -------------------------------------------------
+
+namespace {
+
+// Uploads a host array of device pointers (and optionally positions) into a fresh ring entry.
+int upload_ptrs( gh_attn* h, uint64_t batch, const void* const* ptrs, const uint32_t* pos, cudaStream_t st, int* entry )
+{
+  if ( batch == 0 || batch > h->cfg.max_batch || ptrs == nullptr )
+    return fail( h, GH_ERR_INVALID, "bad batch arguments" );
+  int idx;
+  if ( const int rc = ring_claim( h, &idx ); rc != GH_OK )
+    return rc;
+  RingEntry& r = h->ring[idx];
+  std::memcpy( entry_ptrs( h, r.host ), ptrs, batch * sizeof( void* ) );
+  if ( pos != nullptr )
+    std::memcpy( entry_pos( h, r.host ), pos, batch * sizeof( uint32_t ) );
+  GH_CUDA( h, cudaMemcpyAsync( r.dev + h->off_ptrs, r.host + h->off_ptrs, h->entry_bytes - h->off_ptrs,
+                               cudaMemcpyHostToDevice, st ) );
+  if ( const int rc = ring_touch( h, idx, st ); rc != GH_OK )
+    return rc;
+  *entry = idx;
+  return GH_OK;
+}
+
+ScoreArgs score_args( gh_attn* h, int entry, uint64_t batch, const void* q, void* att, void* xb )
+{
+  ScoreArgs a {};
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.batch = static_cast<uint32_t>( batch );
+  a.layer_bases = reinterpret_cast<const void* const*>( entry_ptrs( h, h->ring[entry].dev ) );
+  a.pos = entry_pos( h, h->ring[entry].dev );
+  a.q = q;
+  a.att = att;
+  a.xb = xb;
+  return a;
+}
+
+} // namespace
+
+int gh_op_copy_kv_cache( gh_attn_t h, void* const* token_rows, const void* state_kv, uint64_t batch, void* stream )
+{
+  if ( h == nullptr || state_kv == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  int entry;
+  if ( const int rc = upload_ptrs( h, batch, const_cast<const void* const*>( token_rows ), nullptr, st, &entry ); rc != GH_OK )
+    return rc;
+  AppendArgs a {};
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.batch = static_cast<uint32_t>( batch );
+  a.token_rows = entry_ptrs( h, h->ring[entry].dev );
+  a.kv_new = state_kv;
+  if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
+    return cuda_fail( h, "copy_kv_cache launch", e );
+  return ring_touch( h, entry, st );
+}
+
+int gh_op_apply_rope( gh_attn_t h,
+                      uint64_t batch,
+                      const uint32_t* pos,
+                      const void* freq_cis_real,
+                      const void* freq_cis_imag,
+                      void* state_q,
+                      void* const* token_rows,
+                      void* stream )
+{
+  if ( h == nullptr || pos == nullptr || freq_cis_real == nullptr || freq_cis_imag == nullptr || state_q == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  for ( uint64_t i = 0; i < batch && i < h->cfg.max_batch; i++ )
+    if ( token_rows != nullptr && token_rows[i] != nullptr && pos[i] >= h->sh.seq_len )
+      return fail( h, GH_ERR_CAPACITY, "token position beyond the RoPE tables" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  int entry;
+  if ( const int rc = upload_ptrs( h, batch, const_cast<const void* const*>( token_rows ), pos, st, &entry ); rc != GH_OK )
+    return rc;
+  AppendArgs a {};
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.batch = static_cast<uint32_t>( batch );
+  a.token_rows = entry_ptrs( h, h->ring[entry].dev );
+  a.pos = entry_pos( h, h->ring[entry].dev );
+  a.q = state_q;
+  a.rope_cos = freq_cis_real;
+  a.rope_sin = freq_cis_imag;
+  if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
+    return cuda_fail( h, "apply_rope launch", e );
+  return ring_touch( h, entry, st );
+}
+
+static int check_positions( gh_attn* h, uint64_t batch, const void* const* bases, const uint32_t* pos )
+{
+  if ( pos == nullptr || bases == nullptr || batch == 0 || batch > h->cfg.max_batch )
+    return fail( h, GH_ERR_INVALID, "bad batch arguments" );
+  for ( uint64_t i = 0; i < batch; i++ )
+    if ( bases[i] != nullptr && pos[i] >= h->sh.seq_len )
+      return fail( h, GH_ERR_CAPACITY, "token position beyond slot capacity at batch index " + std::to_string( i ) );
+  return GH_OK;
+}
+
+int gh_op_attention_0_gemm( gh_attn_t h,
+                            const void* query,
+                            const void* const* layer_bases,
+                            void* att,
+                            uint64_t batch,
+                            const uint32_t* pos,
+                            void* stream )
+{
+  if ( h == nullptr || query == nullptr || att == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( const int rc = check_positions( h, batch, layer_bases, pos ); rc != GH_OK )
+    return rc;
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  int entry;
+  if ( const int rc = upload_ptrs( h, batch, layer_bases, pos, st, &entry ); rc != GH_OK )
+    return rc;
+  if ( const cudaError_t e = launch_scores( score_args( h, entry, batch, query, att, nullptr ), st, &h->stats.kernel_launches );
+       e != cudaSuccess )
+    return cuda_fail( h, "attention_0_gemm launch", e );
+  return ring_touch( h, entry, st );
+}
+
+int gh_op_attention_softmax( gh_attn_t h, void* att, const uint32_t* pos, void* temp_buffer, uint64_t batch, void* stream )
+{
+  (void)temp_buffer;
+  if ( h == nullptr || att == nullptr || pos == nullptr || batch == 0 || batch > h->cfg.max_batch )
+    return fail( h, GH_ERR_INVALID, "bad argument" );
+  for ( uint64_t i = 0; i < batch; i++ )
+    if ( pos[i] >= h->sh.seq_len )
+      return fail( h, GH_ERR_CAPACITY, "token position beyond slot capacity" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  std::vector<const void*> none( batch, nullptr );
+  int entry;
+  if ( const int rc = upload_ptrs( h, batch, none.data(), pos, st, &entry ); rc != GH_OK )
+    return rc;
+  if ( const cudaError_t e = launch_softmax( score_args( h, entry, batch, nullptr, att, nullptr ), st, &h->stats.kernel_launches );
+       e != cudaSuccess )
+    return cuda_fail( h, "attention_softmax launch", e );
+  return ring_touch( h, entry, st );
+}
+
+int gh_op_attention_2_gemm( gh_attn_t h,
+                            const void* att,
+                            const void* const* layer_bases,
+                            void* xb,
+                            uint64_t batch,
+                            const uint32_t* pos,
+                            void* stream )
+{
+  if ( h == nullptr || att == nullptr || xb == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( const int rc = check_positions( h, batch, layer_bases, pos ); rc != GH_OK )
+    return rc;
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  int entry;
+  if ( const int rc = upload_ptrs( h, batch, layer_bases, pos, st, &entry ); rc != GH_OK )
+    return rc;
+  if ( const cudaError_t e = launch_values( score_args( h, entry, batch, nullptr, const_cast<void*>( att ), xb ), st,
+                                            &h->stats.kernel_launches );
+       e != cudaSuccess )
+    return cuda_fail( h, "attention_2_gemm launch", e );
+  return ring_touch( h, entry, st );
+}
+
+int gh_op_attention_fused( gh_attn_t h,
+                           const void* query,
+                           const void* const* layer_bases,
+                           void* xb,
+                           uint64_t batch,
+                           const uint32_t* pos,
+                           void* stream )
+{
+  if ( h == nullptr || query == nullptr || xb == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( const int rc = check_positions( h, batch, layer_bases, pos ); rc != GH_OK )
+    return rc;
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  const char* arena = h->pool.arena();
+  const size_t row_bytes = h->pool.geometry().row_bytes;
+  bool in_arena = true;
+  std::vector<CtxMeta> ctx( batch );
+  for ( uint64_t i = 0; i < batch; i++ ) {
+    CtxMeta& c = ctx[i];
+    c = CtxMeta {};
+    c.pos = pos[i];
+    if ( layer_bases[i] == nullptr ) {
+      c.kv_off = kInactive;
+      continue;
+    }
+    const char* p = static_cast<const char*>( layer_bases[i] );
+    c.kv_off = p - arena;
+    if ( p < arena || p >= arena + h->pool.arena_bytes() || ( c.kv_off % static_cast<long long>( row_bytes ) ) != 0 )
+      in_arena = false; // foreign memory: the TMA descriptor does not cover it, use plain loads
+  }
+  int entry;
+  uint32_t n_items;
+  if ( const int rc = plan_and_upload( h, ctx, st, &entry, &n_items ); rc != GH_OK )
+    return rc;
+  const DecodeArgs a = decode_args( h, entry, n_items, 0, query, xb );
+  if ( const int rc = run_decode( h, a, in_arena, st ); rc != GH_OK )
+    return rc;
+  return ring_touch( h, entry, st );
+}
+
+int gh_op_convert_and_copy( gh_attn_t h,
+                            void* dst,
+                            uint32_t dst_dtype,
+                            const void* src,
+                            uint32_t src_dtype,
+                            uint64_t n,
+                            uint32_t copy_type )
+{
+  if ( h == nullptr || dst == nullptr || src == nullptr || !dtype_ok( dst_dtype ) || !dtype_ok( src_dtype ) )
+    return fail( h, GH_ERR_INVALID, "bad argument" );
+  if ( n == 0 )
+    return GH_OK;
+  DeviceGuard guard( h->device );
+  const size_t db = dtype_size( dst_dtype ), sb = dtype_size( src_dtype );
+  if ( copy_type == GH_COPY_DEVICE_TO_DEVICE ) {
+    if ( dst_dtype == src_dtype )
+      GH_CUDA( h, cudaMemcpy( dst, src, n * db, cudaMemcpyDeviceToDevice ) );
+    else
+      GH_CUDA( h, launch_convert( dst, dst_dtype, src, src_dtype, n, nullptr, &h->stats.kernel_launches ) );
+    GH_CUDA( h, cudaStreamSynchronize( nullptr ) );
+    return GH_OK;
+  }
+  if ( copy_type != GH_COPY_HOST_TO_DEVICE && copy_type != GH_COPY_DEVICE_TO_HOST )
+    return fail( h, GH_ERR_INVALID, "invalid copy type" );
+  const bool h2d = copy_type == GH_COPY_HOST_TO_DEVICE;
+  if ( dst_dtype == src_dtype ) {
+    GH_CUDA( h, cudaMemcpy( dst, src, n * db, h2d ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost ) );
+    return GH_OK;
+  }
+  // The element conversion runs on the device (the reference converts on the host through a temporary array,
+  // src/arch/cuda/llama2/ops.cuh:463-486); the result is the same static_cast per element.
+  void* tmp = nullptr;
+  GH_CUDA( h, cudaMalloc( &tmp, n * ( h2d ? sb : db ) ) );
+  cudaError_t e;
+  if ( h2d ) {
+    e = cudaMemcpy( tmp, src, n * sb, cudaMemcpyHostToDevice );
+    if ( e == cudaSuccess )
+      e = launch_convert( dst, dst_dtype, tmp, src_dtype, n, nullptr, &h->stats.kernel_launches );
+    if ( e == cudaSuccess )
+      e = cudaStreamSynchronize( nullptr );
+  } else {
+    e = launch_convert( tmp, dst_dtype, src, src_dtype, n, nullptr, &h->stats.kernel_launches );
+    if ( e == cudaSuccess )
+      e = cudaMemcpy( dst, tmp, n * db, cudaMemcpyDeviceToHost );
+  }
+  cudaFree( tmp );
+  if ( e != cudaSuccess )
+    return cuda_fail( h, "convert_and_copy", e );
+  return GH_OK;
+}
+
+int gh_plan_batch( uint32_t blocks_per_item,
+                   uint32_t sm_count,
+                   uint32_t tile,
+                   uint32_t fixed_chunk,
+                   uint32_t max_items,
+                   uint64_t batch,
+                   const uint32_t* pos,
+                   int32_t* items_out,
+                   uint32_t* n_items,
+                   uint32_t* chunk )
+{
+  if ( pos == nullptr || items_out == nullptr || n_items == nullptr || chunk == nullptr || blocks_per_item == 0
+       || sm_count == 0 || tile == 0 || max_items == 0 )
+    return GH_ERR_INVALID;
+  std::vector<CtxMeta> ctx( batch );
+  for ( uint64_t i = 0; i < batch; i++ ) {
+    ctx[i] = CtxMeta {};
+    ctx[i].pos = pos[i];
+    ctx[i].kv_off = pos[i] == 0xffffffffu ? kInactive : 0;
+  }
+  PlanParams pp;
+  pp.n_kv_heads = blocks_per_item;
+  pp.sm_count = sm_count;
+  pp.tile = tile;
+  pp.fixed_chunk = fixed_chunk;
+  pp.max_items = max_items;
+  Plan plan;
+  if ( !plan_batch( pp, ctx, plan ) )
+    return GH_ERR_INVALID;
+  std::memcpy( items_out, plan.items.data(), plan.items.size() * sizeof( WorkItem ) );
+  *n_items = static_cast<uint32_t>( plan.items.size() );
+  *chunk = plan.chunk;
+  return GH_OK;
+}
+
+int gh_fill_normal( gh_attn_t h, void* dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t offset, void* stream )
+{
+  if ( h == nullptr || dst == nullptr || !dtype_ok( dtype ) )
+    return fail( h, GH_ERR_INVALID, "bad argument" );
+  DeviceGuard guard( h->device );
+  if ( const cudaError_t e = launch_fill_normal( dst, n, dtype, seed, offset, static_cast<cudaStream_t>( stream ),
+                                                 &h->stats.kernel_launches );
+       e != cudaSuccess )
+    return cuda_fail( h, "fill kernel launch", e );
+  return GH_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,75 @@
+// Host-side launch interface of the attention-stage kernels.  Each launcher returns the cudaError_t of the
+// launch (cudaSuccess when the batch is empty and nothing was launched) and adds the number of kernels it
+// launched to *launches.
+#pragma once
+
+#include <cuda.h>
+
+#include "gh_common.cuh"
+
+namespace gh {
+
+struct AppendArgs
+{
+  Shape sh;
+  uint32_t dtype;
+  uint32_t batch;
+  const CtxMeta* ctx;   // device, [batch]; used when token_rows == nullptr
+  void* const* token_rows; // device array of row pointers (the reference's token contexts), or nullptr
+  const uint32_t* pos;  // device, [batch]; used together with token_rows
+  char* arena;
+  long long layer_off;  // byte offset of the hosted layer inside a slot
+  void* q;              // [batch][n_heads * head_size], rotated in place; may be nullptr (K/V only)
+  const void* kv_new;   // [batch][2 * kv_dim]; nullptr = rotate the row already in the slot (apply_rope alone)
+  const void* rope_cos; // [seq_len][head_size / 2]; nullptr = copy without rotation (copy_kv_cache alone)
+  const void* rope_sin;
+};
+
+struct DecodeArgs
+{
+  Shape sh;
+  uint32_t dtype;
+  const CtxMeta* ctx;
+  const WorkItem* items;
+  uint32_t n_items;
+  const char* arena;
+  long long layer_off;
+  const void* q;
+  void* xb;
+  float* part_o;
+  float* part_ml;
+  int* counters;
+  uint32_t* dev_error;
+  uint32_t sm_count;
+};
+
+struct ScoreArgs // the reference's three unfused operations
+{
+  Shape sh;
+  uint32_t dtype;
+  uint32_t batch;
+  const void* const* layer_bases; // device array [batch] of layer base pointers, null = skip
+  const uint32_t* pos;            // device [batch]
+  const void* q;
+  void* att; // [batch][n_heads][seq_len]
+  void* xb;
+};
+
+cudaError_t launch_append( const AppendArgs& a, cudaStream_t st, uint64_t* launches );
+cudaError_t launch_decode_generic( const DecodeArgs& a, cudaStream_t st, uint64_t* launches );
+// TMA + tensor-core decode kernel; `kv_map` describes the whole arena as [rows][2 * kv_dim].
+bool decode_mma_supported( const Shape& sh, uint32_t dtype );
+cudaError_t decode_mma_prepare(); // one-time function attributes
+cudaError_t launch_decode_mma( const DecodeArgs& a, const CUtensorMap* kv_map, cudaStream_t st, uint64_t* launches );
+uint32_t decode_mma_tile_tokens();
+
+cudaError_t launch_scores( const ScoreArgs& a, cudaStream_t st, uint64_t* launches );  // attention_0_gemm
+cudaError_t launch_softmax( const ScoreArgs& a, cudaStream_t st, uint64_t* launches ); // attention_softmax
+cudaError_t launch_values( const ScoreArgs& a, cudaStream_t st, uint64_t* launches );  // attention_2_gemm
+
+cudaError_t launch_convert( void* dst, uint32_t dst_dtype, const void* src, uint32_t src_dtype, uint64_t n,
+                            cudaStream_t st, uint64_t* launches );
+cudaError_t launch_fill_normal( void* dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t offset,
+                                cudaStream_t st, uint64_t* launches );
+
+} // namespace gh

@@ -1,0 +1,266 @@
+/*
+ * glinthawk_attn.h — C ABI of the B200 (sm_100a) KV-cache attention stage.
+ *
+ * A drop-in for the attention-stage part of Glinthawk's `Operations` interface and its per-context KV
+ * storage.  Every entry point names the reference interface it replaces (paths are relative to the
+ * reference project).  Plain pointers and sizes only; every function returns a gh_status code and never
+ * aborts the process.  There is no CPU fallback: every compute entry point launches CUDA kernels.
+ *
+ * Conventions
+ *   - "device pointer" = CUDA device memory on the handle's device; "host array" = ordinary host memory.
+ *   - dtype codes are the reference's DataType values (src/models/types.hh:20-25).
+ *   - KV layout is the reference's (src/models/llama2/context.hh:79-89,115-127,177-189): a context slot is
+ *     [hosted layer][token][K: kv_head x head_size | V: kv_head x head_size], token t of a layer at
+ *     layer_base + t * 2 * kv_dim elements.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  All compute calls are
+ *     asynchronous with respect to the host unless stated otherwise.
+ *   - A handle is used by one host thread at a time (the reference calls its operations from one execution
+ *     thread per model instance, src/compute/kernel.hh:103-136).
+ */
+#ifndef GLINTHAWK_ATTN_H
+#define GLINTHAWK_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gh_attn* gh_attn_t;
+
+typedef enum gh_status
+{
+  GH_OK = 0,
+  GH_ERR_INVALID = 1,     /* bad argument (null pointer, size out of range, unknown code) */
+  GH_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed; see gh_attn_last_error */
+  GH_ERR_NO_SLOT = 3,     /* the slot pool has no free context left */
+  GH_ERR_CAPACITY = 4,    /* token position >= slot capacity (seq_len) */
+  GH_ERR_OOM = 5,         /* device memory (or the configured page budget) exhausted */
+  GH_ERR_UNSUPPORTED = 6, /* shape / dtype combination has no kernel */
+  GH_ERR_STATE = 7,       /* call out of order (e.g. a layer call before gh_attn_batch_begin) */
+  GH_ERR_NOT_FOUND = 8    /* unknown context id */
+} gh_status;
+
+/* Reference DataType codes (src/models/types.hh:20-25). */
+typedef enum gh_dtype
+{
+  GH_F16 = 0,
+  GH_F32 = 1,
+  GH_BF16 = 2
+} gh_dtype;
+
+/* Reference CopyType values (src/models/types.hh:132-138). */
+typedef enum gh_copy_type
+{
+  GH_COPY_HOST_TO_DEVICE = 0,
+  GH_COPY_DEVICE_TO_HOST = 1,
+  GH_COPY_DEVICE_TO_DEVICE = 2,
+  GH_COPY_HOST_TO_HOST = 3 /* rejected, as in the reference's CUDA backend (ops.cuh:490) */
+} gh_copy_type;
+
+/* How context slots are backed.  STATIC = every slot fully resident, like the reference's `Context`
+ * (src/arch/cuda/llama2/ops.cuh:105-122); PAGED = address space reserved per slot and 2 MiB physical pages
+ * mapped on demand, like `DynamicContext` (src/models/llama2/context.hh:192-249 over
+ * src/arch/cuda/common/vmem.cuh:77-160). */
+typedef enum gh_backing
+{
+  GH_BACKING_STATIC = 0,
+  GH_BACKING_PAGED = 1
+} gh_backing;
+
+/* Shape and sizing.  Replaces the compile-time `ModelConfig` constants (src/models/llama2/variants.hh:9-33)
+ * and the parts of `ConfigRuntime` the attention stage reads (src/models/llama2/base.hh:28-70):
+ * concurrency_limit -> max_batch, max_context_count -> max_contexts, num_attention_layers_hosted ->
+ * n_layers_hosted. */
+typedef struct gh_attn_config
+{
+  uint32_t struct_size;     /* sizeof(gh_attn_config), for forward compatibility */
+  uint32_t n_heads;         /* query heads */
+  uint32_t n_kv_heads;      /* key/value heads; n_heads % n_kv_heads == 0, group size <= 16 */
+  uint32_t head_size;       /* multiple of 8, <= 256 */
+  uint32_t seq_len;         /* slot capacity in tokens */
+  uint32_t n_layers_hosted; /* attention layers whose KV lives in every slot */
+  uint32_t dtype;           /* gh_dtype of KV, q, xb and the RoPE tables */
+  uint32_t max_batch;       /* <= 1024 (MAX_BATCH_SIZE, src/models/llama2/base.hh:26) */
+  uint32_t max_contexts;    /* number of slots in the pool */
+  uint32_t backing;         /* gh_backing */
+  int32_t device;           /* CUDA device ordinal */
+  uint32_t decode_chunk;    /* tokens per split of a long context; 0 = chosen per batch */
+  uint64_t page_budget;     /* PAGED only: upper bound on mapped bytes, 0 = no bound */
+  uint32_t force_generic;   /* 1 = always use the CUDA-core decode kernel (testing) */
+  uint32_t reserved;
+} gh_attn_config;
+
+typedef struct gh_attn_stats
+{
+  uint64_t kernel_launches; /* kernels this handle has launched since creation */
+  uint64_t bytes_mapped;    /* device bytes currently backing slots */
+  uint64_t bytes_reserved;  /* address space reserved for slots */
+  uint64_t scratch_bytes;   /* split partials + batch metadata */
+  uint32_t slots_free;
+  uint32_t slots_allocated;
+  uint32_t last_items;      /* work items (context splits) of the most recent batch */
+  uint32_t last_chunk;      /* split length used by the most recent batch */
+  uint32_t last_kernel;     /* 0 = CUDA-core decode kernel, 1 = TMA + tensor-core decode kernel */
+  uint32_t device_error;    /* sticky flag written by kernels whose bounded waits ran out */
+} gh_attn_stats;
+
+/* ---- lifetime ------------------------------------------------------------------------------------- */
+
+/* Replaces the `LlamaOperations( const ConfigRuntime& )` constructor (src/arch/cuda/llama2/ops.cuh:226-269)
+ * plus the slot pre-allocation of `PreallocatingContextManager` (src/compute/contextman.hh:90-102). */
+int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out );
+int gh_attn_destroy( gh_attn_t h );
+/* Text of the most recent failure on this handle (valid until the next call on it). */
+const char* gh_attn_last_error( gh_attn_t h );
+const char* gh_status_string( int status );
+int gh_attn_get_stats( gh_attn_t h, gh_attn_stats* out );
+
+/* RoPE tables [seq_len][head_size/2] of the handle's dtype, device pointers, not owned.  They are what
+ * `apply_rope` receives as freq_cis_real / freq_cis_imag (src/models/llama2/base.hh:110-112). */
+int gh_attn_set_rope_tables( gh_attn_t h, const void* freq_cis_real, const void* freq_cis_imag );
+
+/* ---- slot pool: PreallocatingContextManager (src/compute/contextman.hh:57-197) -------------------- */
+
+/* get_context (contextman.hh:104-124): the slot already bound to context_id, else bind a free one. */
+int gh_slot_acquire( gh_attn_t h, uint32_t context_id, int32_t* slot );
+/* get_contexts (contextman.hh:127-171): all-or-nothing for a batch; context id 0 (NULL_CONTEXT,
+ * src/models/types.hh:18) marks an inactive prompt and yields slot -1 (the "empty context"). */
+int gh_slots_acquire_batch( gh_attn_t h, uint64_t batch, const uint32_t* context_ids, int32_t* slots );
+int gh_slot_lookup( gh_attn_t h, uint32_t context_id, int32_t* slot );
+/* release_context (contextman.hh:180-196; fatal in the reference, supported here): unbinds the id and, for
+ * PAGED backing, returns the slot's pages to the pool. */
+int gh_slot_release( gh_attn_t h, uint32_t context_id );
+
+/* ---- context views: Context / LayerContext / TokenContext (src/models/llama2/context.hh:61-190) ---- */
+
+/* Context::prepare( layer, token_pos, can_release ) (context.hh:164-169, 221-248): make sure the slot can
+ * hold token `pos` of hosted layer `layer`; can_release drops what the slot held before. */
+int gh_slot_prepare( gh_attn_t h, int32_t slot, uint32_t layer, uint32_t pos, int can_release );
+/* Context::layer( l ) -> LayerContext (context.hh:171): device pointer of the layer's first token row. */
+int gh_slot_layer_ptr( gh_attn_t h, int32_t slot, uint32_t layer, void** ptr );
+/* LayerContext::token( t ).key() (context.hh:115-120, 79): device pointer of one token row. */
+int gh_slot_token_ptr( gh_attn_t h, int32_t slot, uint32_t layer, uint32_t token, void** ptr );
+/* Context::max_size( n_layers_hosted ) (context.hh:173). */
+size_t gh_slot_bytes( gh_attn_t h );
+
+/* ---- fused hot path -------------------------------------------------------------------------------- */
+
+/* Per-batch set-up, the attention-relevant part of Llama2::forward_prelude / forward_attention
+ * (src/models/llama2/model.hh:446-477, 611-628): records slot and token position of every prompt of the
+ * batch (host arrays, as the reference's ScratchPad keeps them, src/models/llama2/base.hh:197-202), plans
+ * the splits of long contexts and uploads the batch description on `stream`.  slot -1 = inactive prompt.
+ * The per-layer calls below refer to the batch set up last. */
+int gh_attn_batch_begin( gh_attn_t h, uint64_t batch, const int32_t* slots, const uint32_t* pos, void* stream );
+
+/* copy_kv_cache + apply_rope in one kernel (src/arch/amd64/llama2/ops.hh:335-352 and :300-333; order of
+ * src/models/llama2/model.hh:345-364): row i of kv_new ([K,V], 2*kv_dim elements) goes to token pos[i] of
+ * hosted layer `layer` of slot[i], K rotated on the way (fp32 arithmetic from the stored tables, one
+ * rounding); V is copied bit for bit; q [batch][n_heads*head_size] is rotated in place. */
+int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new, void* stream );
+
+/* attention_0_gemm + attention_softmax + attention_2_gemm in one kernel (src/arch/amd64/llama2/ops.hh:
+ * 170-223, 283-298, 225-281): xb[i][head] = softmax_t( q.K_t / sqrt(head_size) ) . V over t <= pos[i], fp32
+ * accumulation, no score matrix in memory.  Rows of inactive prompts are left untouched. */
+int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* stream );
+
+/* gh_attn_append then gh_attn_decode: Llama2::attention_ops with the cache update of pre_attention_ops
+ * (src/models/llama2/model.hh:345-387). */
+int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new, void* xb, void* stream );
+
+/* Llama2::forward_attention for one layer with HOST buffers (src/models/llama2/model.hh:630-722): q_host
+ * [batch][n_heads*head_size] and kv_host [batch][2*kv_dim] of dtype `io_dtype` are converted and copied in
+ * (convert_and_copy, src/arch/cuda/llama2/ops.cuh:455-492), the stage runs, and xb is converted and copied
+ * back into xb_host.  Asynchronous: xb_host is valid once `stream` has drained.  Host buffers should be
+ * pinned for the copies to overlap. */
+int gh_attn_forward_attention_host( gh_attn_t h,
+                                    uint32_t layer,
+                                    uint32_t io_dtype,
+                                    const void* q_host,
+                                    const void* kv_host,
+                                    void* xb_host,
+                                    void* stream );
+
+/* ---- the reference's five operations, argument for argument --------------------------------------- */
+/* `token_rows` / `layer_bases` are HOST arrays of device pointers (what TokenContext::key() and
+ * LayerContext::token(0).key() return); a null entry means "inactive, skip" (ops.hh:195,250,314,344).
+ * `pos` is a host array.  These materialise the score matrix `att` [batch][n_heads][seq_len] exactly as the
+ * reference does and round where it rounds. */
+
+/* copy_kv_cache( token_contexts[], state_kv, batch ) — src/arch/cuda/llama2/ops.cuh:435-453. */
+int gh_op_copy_kv_cache( gh_attn_t h, void* const* token_rows, const void* state_kv, uint64_t batch, void* stream );
+/* apply_rope( batch, token_positions, freq_cis_real, freq_cis_imag, state_q, token_contexts[] ) —
+ * src/arch/cuda/llama2/ops.cuh:413-433; arithmetic follows the amd64 rule (ops.hh:150-162). */
+int gh_op_apply_rope( gh_attn_t h,
+                      uint64_t batch,
+                      const uint32_t* pos,
+                      const void* freq_cis_real,
+                      const void* freq_cis_imag,
+                      void* state_q,
+                      void* const* token_rows,
+                      void* stream );
+/* attention_0_gemm( query, layer_contexts[], att, batch, token_positions ) — ops.cuh:272-324. */
+int gh_op_attention_0_gemm( gh_attn_t h,
+                            const void* query,
+                            const void* const* layer_bases,
+                            void* att,
+                            uint64_t batch,
+                            const uint32_t* pos,
+                            void* stream );
+/* attention_softmax( att, token_positions, temp_buffer, batch ) — ops.cuh:385-411. temp_buffer is unused. */
+int gh_op_attention_softmax( gh_attn_t h, void* att, const uint32_t* pos, void* temp_buffer, uint64_t batch, void* stream );
+/* attention_2_gemm( att, layer_contexts[], xb, batch, token_positions ) — ops.cuh:326-383. */
+int gh_op_attention_2_gemm( gh_attn_t h,
+                            const void* att,
+                            const void* const* layer_bases,
+                            void* xb,
+                            uint64_t batch,
+                            const uint32_t* pos,
+                            void* stream );
+/* Fused stand-in for the three calls above with the same inputs: reads q and the layer contexts, writes xb,
+ * never touches `att`.  What an adapter calls from attention_0_gemm when it does not need `att`. */
+int gh_op_attention_fused( gh_attn_t h,
+                           const void* query,
+                           const void* const* layer_bases,
+                           void* xb,
+                           uint64_t batch,
+                           const uint32_t* pos,
+                           void* stream );
+/* convert_and_copy<Dst,Src>( dst, src, n, CopyType ) — ops.cuh:455-492.  Blocking, like the reference's. */
+int gh_op_convert_and_copy( gh_attn_t h,
+                            void* dst,
+                            uint32_t dst_dtype,
+                            const void* src,
+                            uint32_t src_dtype,
+                            uint64_t n,
+                            uint32_t copy_type );
+
+/* ---- helpers for benchmarks and tests ------------------------------------------------------------- */
+
+/* Fills n elements of `dtype` at device pointer `dst` with N(0,1) values from a counter-based generator
+ * keyed by (seed, element index + offset).  No reference counterpart (the reference's profiler fills its
+ * contexts with uniform noise, src/profile/profiler.hh:79-93). */
+int gh_fill_normal( gh_attn_t h, void* dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t offset, void* stream );
+
+/* Host-only (touches no device): the split plan gh_attn_batch_begin makes for token positions `pos`
+ * (UINT32_MAX marks an inactive prompt).  `blocks_per_item` is the number of thread blocks a work item fans out
+ * to (kv heads for the tensor-core kernel).  Writes n_items records {context, t_begin, t_end, split} to
+ * items_out (room for max_items) and the split length to *chunk.  No reference counterpart: the reference
+ * loops over the batch on the host and launches per context (src/arch/cuda/llama2/ops.cuh:272-453). */
+int gh_plan_batch( uint32_t blocks_per_item,
+                   uint32_t sm_count,
+                   uint32_t tile,
+                   uint32_t fixed_chunk,
+                   uint32_t max_items,
+                   uint64_t batch,
+                   const uint32_t* pos,
+                   int32_t* items_out,
+                   uint32_t* n_items,
+                   uint32_t* chunk );
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GLINTHAWK_ATTN_H */

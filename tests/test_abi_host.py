@@ -1,0 +1,105 @@
+"""CPU-only checks of the drop-in boundary: the shared library loads without a GPU, exports every symbol the
+public header declares, reports errors as status codes, and its host-side planner behaves."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from glinthawk_b200 import _lib
+from glinthawk_b200.stage import plan_batch
+
+
+def test_library_exports_every_declared_symbol():
+    names = _lib.declared_symbols()
+    assert len(names) >= 27
+    for n in names:
+        assert hasattr(_lib.lib, n), f"{n} is declared in include/glinthawk_attn.h but not exported"
+    assert set(names) == set(_lib._PROTOS), "binding table and header disagree"
+
+
+def test_status_strings():
+    assert _lib.lib.gh_status_string(0) == b"ok"
+    assert b"slot" in _lib.lib.gh_status_string(_lib.GH_ERR_NO_SLOT)
+
+
+def test_create_rejects_bad_config():
+    h = C.c_void_p(0)
+    cfg = _lib.Config(C.sizeof(_lib.Config), 6, 4, 48, 256, 1, _lib.GH_F32, 4, 4, 0, 0, 0, 0, 0, 0)  # 6 % 4 != 0
+    assert _lib.lib.gh_attn_create(C.byref(cfg), C.byref(h)) == _lib.GH_ERR_INVALID
+    cfg = _lib.Config(C.sizeof(_lib.Config) - 4, 6, 6, 48, 256, 1, _lib.GH_F32, 4, 4, 0, 0, 0, 0, 0, 0)
+    assert _lib.lib.gh_attn_create(C.byref(cfg), C.byref(h)) == _lib.GH_ERR_INVALID
+    cfg = _lib.Config(C.sizeof(_lib.Config), 6, 6, 48, 256, 1, _lib.GH_F32, 4096, 4, 0, 0, 0, 0, 0, 0)  # batch > 1024
+    assert _lib.lib.gh_attn_create(C.byref(cfg), C.byref(h)) == _lib.GH_ERR_INVALID
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour on a machine without a GPU")
+def test_create_without_gpu_fails_loudly():
+    """No CPU fallback: without a device the stage cannot be created."""
+    h = C.c_void_p(0)
+    cfg = _lib.Config(C.sizeof(_lib.Config), 6, 6, 48, 256, 1, _lib.GH_F32, 4, 4, 0, 0, 0, 0, 0, 0)
+    assert _lib.lib.gh_attn_create(C.byref(cfg), C.byref(h)) == _lib.GH_ERR_CUDA
+    assert not h.value
+
+
+def test_null_handle_is_an_error_not_a_crash():
+    assert _lib.lib.gh_attn_destroy(None) == _lib.GH_ERR_INVALID
+    assert _lib.lib.gh_attn_last_error(None) == b"null handle"
+    s = C.c_int32(0)
+    assert _lib.lib.gh_slot_acquire(None, 1, C.byref(s)) == _lib.GH_ERR_INVALID
+
+
+def _check_plan(pos, items, chunk, tile):
+    pos = np.asarray(pos, dtype=np.int64)
+    covered = {i: [] for i in range(len(pos))}
+    for ctx, b, e, split in items:
+        assert 0 <= b < e
+        assert b % tile == 0, "split boundaries must sit on tile multiples"
+        covered[ctx].append((b, e, split))
+    for i, p in enumerate(pos):
+        if p == 0xFFFFFFFF:
+            assert covered[i] == []
+            continue
+        segs = sorted(covered[i])
+        assert segs[0][0] == 0 and segs[-1][1] == p + 1
+        for (b0, e0, s0), (b1, e1, s1) in zip(segs, segs[1:]):
+            assert e0 == b1 and s1 == s0 + 1
+        assert all(e - b <= chunk for b, e, _ in segs)
+    lens = [e - b for _, b, e, _ in items]
+    assert lens == sorted(lens, reverse=True), "items must be ordered longest first"
+
+
+def test_plan_covers_every_token_exactly_once():
+    rng = np.random.default_rng(0)
+    pos = rng.integers(0, 4096, size=256).astype(np.uint32)
+    items, chunk = plan_batch(pos, blocks_per_item=8)
+    _check_plan(pos, items, chunk, 64)
+    assert chunk % 64 == 0 and chunk >= 256
+
+
+def test_plan_edge_cases():
+    items, chunk = plan_batch([0], blocks_per_item=8)
+    assert items.tolist() == [[0, 0, 1, 0]]
+    items, chunk = plan_batch([0xFFFFFFFF, 5, 0xFFFFFFFF], blocks_per_item=1)
+    assert items.tolist() == [[1, 0, 6, 0]]
+    items, chunk = plan_batch([0xFFFFFFFF] * 4, blocks_per_item=1)
+    assert len(items) == 0
+    # a fixed split length is honoured (rounded to the tile) and splits are balanced
+    items, chunk = plan_batch([1000], blocks_per_item=8, fixed_chunk=300)
+    assert chunk == 320
+    _check_plan([1000], items, chunk, 64)
+    assert len(items) == 4
+    # a tiny item buffer forces longer splits instead of failing
+    pos = np.full(8, 4095, dtype=np.uint32)
+    items, chunk = plan_batch(pos, blocks_per_item=8, fixed_chunk=64, max_items=16)
+    assert len(items) <= 16
+    _check_plan(pos, items, chunk, 64)
+    # more active contexts than items: refused
+    with pytest.raises(Exception):
+        plan_batch(np.zeros(32, dtype=np.uint32), blocks_per_item=1, max_items=16)
+
+
+def test_plan_scales_split_length_with_work():
+    small, c_small = plan_batch(np.full(32, 1000, dtype=np.uint32), blocks_per_item=8)
+    big, c_big = plan_batch(np.full(1024, 4000, dtype=np.uint32), blocks_per_item=8)
+    assert c_small == 256 and c_big > c_small

@@ -1,0 +1,191 @@
+"""Parity of the CUDA path, called through the C ABI, with the CPU oracle and with the fixtures produced by
+the reference's own amd64 backend.  Tolerances are the contract's: V bit-exact, rotated K/q within 1e-3
+relative, attention output within 2e-2 absolute (fp16/bf16) or 1e-4 (fp32)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from tests import cases, gpu_util
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+@pytest.mark.parametrize("spec", cases.GOLDEN_SPECS, ids=lambda s: s["name"])
+def test_fused_step_matches_reference_fixture(spec):
+    case = cases.golden_case(spec)
+    gold = np.load(GOLDEN / f"{case.name}.npz")
+    want = cases.StepResult([r for r in gold["rows"]], gold["q"], gold["xb"])
+    st = gpu_util.make_stage(case)
+    slots = gpu_util.load_case(st, case, layer=1)
+    res = gpu_util.run_step(st, case, slots, layer=1)
+    gpu_util.assert_step_close(res, want, case)
+    st.close()
+
+
+@pytest.mark.parametrize("spec", cases.GOLDEN_SPECS[:10], ids=lambda s: s["name"])
+@pytest.mark.parametrize("variant", ["generic", "paged", "chunk64", "two_calls"])
+def test_fused_step_variants_match_oracle(oracle, spec, variant):
+    """The same cases through the CUDA-core kernel, paged slots, the smallest split length (every context cut
+    into 64-token items, so the partial-record merge runs everywhere), and append/decode as two calls."""
+    case = cases.golden_case(spec)
+    want = oracle.layer_step(case)
+    st = gpu_util.make_stage(case, force_generic=variant == "generic", paged=variant == "paged",
+                             decode_chunk=64 if variant == "chunk64" else 0)
+    slots = gpu_util.load_case(st, case, layer=0)
+    res = gpu_util.run_step(st, case, slots, layer=0, fused_call=variant != "two_calls")
+    gpu_util.assert_step_close(res, want, case)
+    st.close()
+
+
+@pytest.mark.parametrize("dtype", [cases.F16, cases.BF16, cases.F32])
+@pytest.mark.parametrize("shape_name", ["mini_mha", "mini_g4", "mini_g8", "mini_g16", "tiny15m"])
+def test_fused_step_all_dtypes(oracle, shape_name, dtype):
+    S = cases.SHAPES[shape_name].seq_len
+    pos = [0, 1, 63, 64, 65, 127, 128, S // 2, S - 1]
+    case = cases.make_case("dt", shape_name, dtype, pos, seed=1000 + dtype)
+    want = oracle.layer_step(case)
+    st = gpu_util.make_stage(case, decode_chunk=128)
+    slots = gpu_util.load_case(st, case, layer=1)
+    res = gpu_util.run_step(st, case, slots, layer=1)
+    gpu_util.assert_step_close(res, want, case)
+    st.close()
+
+
+def test_consecutive_decode_steps_grow_the_cache(oracle):
+    """Several layer-steps in a row on two layers: each step sees the rows the previous ones appended."""
+    case = cases.make_case("multi", "mini_g8", cases.F16, [10, 62, 300], seed=5)
+    st = gpu_util.make_stage(case, layers=2, paged=True)
+    slots = {l: None for l in (0, 1)}
+    slots = gpu_util.load_case(st, case, layer=0)
+    for i in range(case.B):  # same pre-filled rows in layer 1
+        p = int(case.pos[i])
+        st.prepare(int(slots[i]), 1, p, False)
+        st.layer_view(int(slots[i]), 1, p).copy_(gpu_util.to_dev(case.cache[i][:p], case.dtype))
+    cur = case
+    rng = np.random.default_rng(99)
+    for step in range(4):
+        want = oracle.layer_step(cur)
+        for layer in (0, 1):
+            res = gpu_util.run_step(st, cur, slots, layer)
+            gpu_util.assert_step_close(res, want, cur)
+        # next token: the cache now holds the appended rows
+        new_cache = [np.concatenate([c[: int(p)], r[None, :], np.zeros((1, c.shape[1]), c.dtype)])
+                     for c, p, r in zip(cur.cache, cur.pos, want.rows)]
+        cur = cases.Case(cur.name, cur.shape, cur.dtype, cur.pos + 1, cur.active, new_cache,
+                         rng.standard_normal(cur.q.shape).astype(cur.q.dtype),
+                         rng.standard_normal(cur.kv_new.shape).astype(cur.kv_new.dtype), cur.fcr, cur.fci)
+    st.close()
+
+
+@pytest.mark.parametrize("dtype", [cases.F16, cases.F32, cases.BF16])
+def test_reference_operations_one_by_one(oracle, dtype):
+    """copy_kv_cache, apply_rope, attention_0_gemm, attention_softmax, attention_2_gemm with the reference's
+    argument lists, each checked on its own output (including the score matrix `att`)."""
+    case = cases.make_case("ops", "mini_g4", dtype, [0, 17, 200, 90], seed=21, inactive=[3])
+    sh = case.shape
+    want = oracle.layer_step(case, keep_att=True)
+    st = gpu_util.make_stage(case)
+    slots = gpu_util.load_case(st, case, layer=1)
+    layer_ptrs = [st.layer_ptr(int(s), 1) if s >= 0 else 0 for s in slots]
+    token_ptrs = [st.token_ptr(int(s), 1, int(p)) if s >= 0 else 0 for s, p in zip(slots, case.pos)]
+    q = gpu_util.to_dev(case.q, dtype)
+    kv = gpu_util.to_dev(case.kv_new, dtype)
+    att = torch.zeros((case.B, sh.n_heads, sh.seq_len), dtype=q.dtype, device="cuda")
+    xb = torch.zeros_like(q)
+
+    st.copy_kv_cache(token_ptrs, kv, case.B)
+    torch.cuda.synchronize()
+    for i in range(case.B):
+        if case.active[i]:
+            row = gpu_util.to_host(st.layer_view(int(slots[i]), 1, int(case.pos[i]) + 1)[int(case.pos[i])], dtype)
+            assert np.array_equal(row.view(np.uint8), case.kv_new[i].view(np.uint8)), "raw copy before RoPE"
+
+    st.apply_rope(case.B, case.pos, gpu_util.to_dev(case.fcr, dtype), gpu_util.to_dev(case.fci, dtype), q, token_ptrs)
+    st.attention_0_gemm(q, layer_ptrs, att, case.B, case.pos)
+    st.attention_softmax(att, case.pos, None, case.B)
+    st.attention_2_gemm(att, layer_ptrs, xb, case.B, case.pos)
+    torch.cuda.synchronize()
+
+    rows = [gpu_util.to_host(st.layer_view(int(s), 1, int(p) + 1)[int(p)], dtype) if s >= 0 else None
+            for s, p in zip(slots, case.pos)]
+    res = cases.StepResult(rows, gpu_util.to_host(q, dtype), gpu_util.to_host(xb, dtype))
+    # unfused ops round where the reference rounds: much tighter than the contract
+    gpu_util.assert_step_close(res, want, case, xb_atol={cases.F32: 2e-6, cases.F16: 2e-3, cases.BF16: 1.6e-2}[dtype])
+    att_h = gpu_util.to_host(att, dtype)
+    for i, p in enumerate(case.pos):
+        if case.active[i]:
+            np.testing.assert_allclose(cases.as_f32(att_h[i, :, : p + 1], dtype),
+                                       cases.as_f32(want.att[i, :, : p + 1], dtype), rtol=0,
+                                       atol={cases.F32: 1e-6, cases.F16: 1e-3, cases.BF16: 8e-3}[dtype])
+
+    # the fused stand-in for the three attention calls gives the same xb from the same arguments
+    xb2 = torch.zeros_like(q)
+    st.attention_fused(q, layer_ptrs, xb2, case.B, case.pos)
+    torch.cuda.synchronize()
+    for i in range(case.B):
+        if case.active[i]:
+            np.testing.assert_allclose(cases.as_f32(gpu_util.to_host(xb2, dtype)[i], dtype),
+                                       cases.as_f32(want.xb[i], dtype), rtol=0, atol=cases.TOL_XB[dtype])
+    # inactive prompts are skipped: their xb row is untouched
+    assert torch.count_nonzero(xb[3]) == 0 and torch.count_nonzero(xb2[3]) == 0
+    st.close()
+
+
+def test_attention_fused_on_foreign_memory(oracle):
+    """Layer contexts that do not live in the stage's own arena (plain cudaMalloc'd buffers) still work."""
+    case = cases.make_case("foreign", "mini_g8", cases.F16, [70, 400], seed=31)
+    want = oracle.layer_step(case)
+    st = gpu_util.make_stage(case)
+    bufs = []
+    for i in range(case.B):
+        c = case.cache[i].copy()
+        c[int(case.pos[i])] = want.rows[i]
+        bufs.append(gpu_util.to_dev(c, case.dtype))
+    q = gpu_util.to_dev(want.q, case.dtype)
+    xb = torch.zeros_like(q)
+    st.attention_fused(q, [b.data_ptr() for b in bufs], xb, case.B, case.pos)
+    torch.cuda.synchronize()
+    assert st.stats().last_kernel == 0
+    np.testing.assert_allclose(xb.float().cpu().numpy(), want.xb.astype(np.float32), rtol=0, atol=cases.TOL_XB[cases.F16])
+    st.close()
+
+
+@pytest.mark.parametrize("io_dtype", [cases.F16, cases.F32])
+def test_forward_attention_with_host_buffers(oracle, io_dtype):
+    """The piped-mode entry point: q and the new [K,V] rows arrive in host memory, possibly in another dtype
+    (the reference mixes fp16 pre/post-attention with fp32 attention), and xb goes back to the host."""
+    case = cases.make_case("host", "mini_g8", cases.F16, [5, 64, 333], seed=41)
+    want = oracle.layer_step(case)
+    st = gpu_util.make_stage(case)
+    slots = gpu_util.load_case(st, case, layer=0)
+    npdt = cases.NP_DTYPE[io_dtype]
+    q_h = torch.from_numpy(case.q.astype(npdt)).pin_memory()
+    kv_h = torch.from_numpy(case.kv_new.astype(npdt)).pin_memory()
+    xb_h = torch.zeros_like(q_h).pin_memory()
+    st.batch_begin(slots, case.pos)
+    st.forward_attention_host(0, io_dtype, q_h, kv_h, xb_h)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(xb_h.numpy().astype(np.float32), want.xb.astype(np.float32), rtol=0,
+                               atol=cases.TOL_XB[cases.F16])
+    st.close()
+
+
+def test_convert_and_copy():
+    case = cases.make_case("cc", "tiny15m", cases.F32, [3], seed=1)
+    st = gpu_util.make_stage(case)
+    x = np.random.default_rng(3).standard_normal(5000).astype(np.float32)
+    d16 = torch.zeros(5000, dtype=torch.float16, device="cuda")
+    st.convert_and_copy(d16, torch.float16, x, torch.float32, 5000, 0)  # host fp32 -> device fp16
+    assert np.array_equal(d16.cpu().numpy(), x.astype(np.float16))
+    back = np.zeros(5000, dtype=np.float32)
+    st.convert_and_copy(back, torch.float32, d16, torch.float16, 5000, 1)  # device fp16 -> host fp32
+    assert np.array_equal(back, x.astype(np.float16).astype(np.float32))
+    same = np.zeros(5000, dtype=np.float16)
+    st.convert_and_copy(same, torch.float16, d16, torch.float16, 5000, 1)
+    assert np.array_equal(same, x.astype(np.float16))
+    with pytest.raises(Exception):
+        st.convert_and_copy(same, torch.float16, same, torch.float16, 10, 3)  # host-to-host is rejected
+    st.close()
