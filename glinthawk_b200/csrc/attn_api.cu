@@ -380,7 +380,7 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
     if ( api == nullptr )
       return GH_ERR_CUDA;
     const uint64_t total_rows = h->pool.arena_bytes() / g.row_bytes;
-    if ( total_rows >= ( 1ull << 32 ) ) {
+    if ( total_rows >= ( 1ull << 31 ) ) { // TMA coordinates are signed 32-bit
       h->use_mma = false; // arena too large for one descriptor; the CUDA-core kernel has no such limit
     } else {
       const cuuint64_t dims[2] = { sh.row_elems, total_rows };

@@ -48,7 +48,7 @@ def test_context_views_follow_the_reference_layout():
 
 
 def test_paged_slots_map_on_demand_and_release():
-    sh = SHAPES["mini_g8"]  # row 4 KiB -> 512 tokens per 2 MiB page
+    sh = SHAPES["l70b_4k"]  # row 4 KiB -> 512 tokens per 2 MiB page, 16 MiB per layer
     st = AttentionStage(sh, torch.float16, n_layers_hosted=2, max_batch=4, max_contexts=4, paged=True)
     s = st.get_context(7)
     assert st.stats().bytes_mapped == 0 and st.stats().bytes_reserved >= 4 * st.slot_bytes()
@@ -59,19 +59,27 @@ def test_paged_slots_map_on_demand_and_release():
     assert st.stats().bytes_mapped == one  # same page
     st.prepare(s, 1, 511)
     assert st.stats().bytes_mapped == 2 * one
-    v = st.layer_view(s, 1, 512)
+    st.prepare(s, 1, 512)  # the 513th token of layer 1 starts a new page
+    assert st.stats().bytes_mapped == 3 * one
+    v = st.layer_view(s, 1, 1024)
     v.fill_(1.0)
     torch.cuda.synchronize()
-    assert float(v.float().sum()) == 512 * 2 * sh.kv_dim
+    assert float(v.float().sum()) == 1024 * 2 * sh.kv_dim
     st.prepare(s, 0, 0, can_release=True)  # a new prompt starts in this slot
     assert st.stats().bytes_mapped == one
     st.release_context(7)
     assert st.stats().bytes_mapped == 0
+    # a slot whose pages went back to the pool can be bound and filled again
+    s2 = st.get_context(8)
+    st.prepare(s2, 1, 2000)
+    st.layer_view(s2, 1, 2001).fill_(2.0)
+    torch.cuda.synchronize()
+    assert st.stats().bytes_mapped == 4 * one
     st.close()
 
 
 def test_paged_budget_is_an_error_status():
-    sh = SHAPES["mini_g8"]
+    sh = SHAPES["l70b_4k"]
     st = AttentionStage(sh, torch.float16, n_layers_hosted=2, max_batch=4, max_contexts=4, paged=True,
                         page_budget=2 << 20)
     s = st.get_context(1)
