@@ -28,6 +28,11 @@ class Config(C.Structure):
                 ("page_budget", C.c_uint64), ("force_generic", C.c_uint32), ("reserved", C.c_uint32)]
 
 
+class NoallocShape(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("n_heads", C.c_uint32), ("n_kv_heads", C.c_uint32),
+                ("head_size", C.c_uint32), ("dtype", C.c_uint32)]
+
+
 class Stats(C.Structure):
     _fields_ = [("kernel_launches", C.c_uint64), ("bytes_mapped", C.c_uint64), ("bytes_reserved", C.c_uint64),
                 ("scratch_bytes", C.c_uint64), ("slots_free", C.c_uint32), ("slots_allocated", C.c_uint32),
@@ -64,6 +69,8 @@ _PROTOS = {
     "gh_op_attention_fused": (C.c_int, [_P, _P, _P, _P, _U64, _P, _P]),
     "gh_op_convert_and_copy": (C.c_int, [_P, _P, _U32, _P, _U32, _U64, _U32]),
     "gh_fill_normal": (C.c_int, [_P, _P, _U64, _U32, _U64, _U64, _P]),
+    "gh_decode_noalloc": (C.c_int, [C.POINTER(NoallocShape), _U64, _P, _P, _P, _P, _P]),
+    "gh_decode_noalloc_error": (C.c_char_p, []),
     "gh_plan_batch": (C.c_int, [_U32, _U32, _U32, _U32, _U32, _U64, _P, _P, C.POINTER(_U32), C.POINTER(_U32)]),
 }
 

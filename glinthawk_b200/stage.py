@@ -239,3 +239,17 @@ def plan_batch(pos, *, blocks_per_item: int, sm_count: int = 148, tile: int = 64
     if rc != _lib.GH_OK:
         raise GlinthawkAttnError(rc, "gh_plan_batch")
     return items[: n.value].copy(), chunk.value
+
+
+def decode_noalloc(shape: AttnShape, dtype, layer_contexts, token_positions, query, xb, stream=None) -> None:
+    """``gh_decode_noalloc``: fused decode attention for callers that must not allocate device memory (a worker
+    whose GPU memory is fully handed out at start-up, a loop that cannot take cudaMalloc's device-wide
+    synchronisation).  Needs no stage; scratch is a fixed array inside the library.  Raises with the library's
+    message when a size limit is exceeded."""
+    bases = np.ascontiguousarray([int(p or 0) for p in layer_contexts], dtype=np.uint64)
+    pos = np.ascontiguousarray(token_positions, dtype=np.uint32)
+    sh = _lib.NoallocShape(C.sizeof(_lib.NoallocShape), shape.n_heads, shape.n_kv_heads, shape.head_size,
+                           dtype_code(dtype))
+    rc = lib.gh_decode_noalloc(C.byref(sh), len(pos), _ptr(bases), _ptr(pos), _ptr(query), _ptr(xb), _stream(stream))
+    if rc != _lib.GH_OK:
+        raise GlinthawkAttnError(rc, lib.gh_decode_noalloc_error().decode())

@@ -243,6 +243,49 @@ int gh_op_convert_and_copy( gh_attn_t h,
  * contexts with uniform noise, src/profile/profiler.hh:79-93). */
 int gh_fill_normal( gh_attn_t h, void* dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t offset, void* stream );
 
+/* ---- decode attention without any allocation ------------------------------------------------------ */
+
+/* Limits of gh_decode_noalloc; requests beyond them are refused. */
+#define GH_NOALLOC_MAX_BATCH 64u       /* contexts per call */
+#define GH_NOALLOC_MAX_ITEMS 128u      /* work items after cutting long contexts (the call adapts the cut to fit) */
+#define GH_NOALLOC_MAX_HEADS 128u      /* query heads */
+#define GH_NOALLOC_MAX_Q_ELEMS 8192u   /* n_heads * head_size */
+#define GH_NOALLOC_SCRATCH_BYTES 4456448u /* size of the built-in scratch array, held per GPU */
+
+typedef struct gh_noalloc_shape
+{
+  uint32_t struct_size; /* sizeof(gh_noalloc_shape) */
+  uint32_t n_heads;
+  uint32_t n_kv_heads;
+  uint32_t head_size;
+  uint32_t dtype;       /* gh_dtype of the KV rows, q and xb */
+} gh_noalloc_shape;
+
+/* This entry point has no counterpart in the reference.  It computes what gh_op_attention_fused computes — xb from
+ * q and the layer contexts, for t <= pos[i] — but needs no handle and allocates nothing: not with cudaMalloc, not
+ * through any library.  It is for code that runs where device allocation is off the table: inside a worker that
+ * gave all of its GPU memory to weights and context slots at start-up and treats a failed allocation as fatal, or
+ * inside a serving loop that must not trigger the device-wide synchronisation an allocation implies.  The scratch it
+ * needs (split partial results, arrival counters, the batch description) lives in a fixed array of
+ * GH_NOALLOC_SCRATCH_BYTES inside the library image; every GPU the library is used on holds that array until the
+ * process exits.
+ *
+ * `layer_bases` is a host array of device pointers to the first token row of each context's layer (null = skip),
+ * `pos` a host array, q and xb device pointers, exactly as for gh_op_attention_fused; the current CUDA device is
+ * used.  The first call on a device resolves the array's device address; make it before any stream capture on
+ * that device.  Every call reuses the same array and clears the counters in it on `stream` before launching, so
+ * calls whose kernels could run concurrently on one GPU race with each other and must be ordered by the caller.
+ * Returns GH_ERR_INVALID when a limit above is exceeded; gh_decode_noalloc_error() then names the limit. */
+int gh_decode_noalloc( const gh_noalloc_shape* shape,
+                       uint64_t batch,
+                       const void* const* layer_bases,
+                       const uint32_t* pos,
+                       const void* q,
+                       void* xb,
+                       void* stream );
+/* Message of the calling thread's most recent gh_decode_noalloc failure ("" after a success). */
+const char* gh_decode_noalloc_error( void );
+
 /* Host-only (touches no device): the split plan gh_attn_batch_begin makes for token positions `pos`
  * (UINT32_MAX marks an inactive prompt).  `blocks_per_item` is the number of thread blocks a work item fans out
  * to (kv heads for the tensor-core kernel).  Writes n_items records {context, t_begin, t_end, split} to
