@@ -166,10 +166,17 @@ def time_cpu_sample(wl, lens, n_ctx, n_layers, seed, reps):
     }, times
 
 
+def use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every core, so
+    the variable is put back before the OpenMP runtime of the reference library starts."""
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
+
 def run_reference_arm(args, wl, n_layers, batch):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    use_all_host_threads()
     headroom = args.warmup + args.steps + 8
     lens = wl.lengths(args.seed, headroom)[:batch]
     n_ctx = min(args.cpu_contexts, batch)
@@ -363,6 +370,7 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        use_all_host_threads()
         cpu, _ = time_cpu_sample(wl, lens0, args.cpu_contexts, n_layers, args.seed, reps=3)
 
     if rank == 0:

@@ -18,7 +18,8 @@ namespace {
 
 constexpr uint32_t kRing = 16;       // batch descriptions that may be in flight at once
 constexpr uint32_t kHostStages = 4;  // staging sets for the host-buffer entry point
-constexpr uint32_t kExtraItems = 2048;
+constexpr uint32_t kExtraItems = 1024;
+constexpr uint32_t kScratchSets = 4; // decode launches of one handle that may be in flight on different streams
 
 struct DeviceGuard
 {
@@ -46,6 +47,19 @@ struct RingEntry
   cudaEvent_t last_use = nullptr;
   cudaStream_t last_stream = nullptr;
   bool used = false, multi_stream = false;
+};
+
+// Scratch of one decode launch: split partial records, arrival counters, the persistent kernel's scheduling words.
+// A launch owns its set until its kernel has finished, so launches on different streams never share one.
+struct ScratchSet
+{
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  int* counters = nullptr; // [max_batch * n_heads] arrival counters, then 2 scheduling words
+  int* sched = nullptr;
+  cudaEvent_t done = nullptr;
+  cudaStream_t stream = nullptr;
+  bool used = false;
 };
 
 struct HostStage
@@ -85,9 +99,8 @@ struct gh_attn
   std::vector<uint32_t> cur_pos;
 
   // split partials
-  float* part_o = nullptr;
-  float* part_ml = nullptr;
-  int* counters = nullptr;
+  ScratchSet scratch[kScratchSets];
+  uint32_t scratch_next = 0;
   uint32_t* dev_error = nullptr;
 
   bool use_mma = false;
@@ -208,6 +221,26 @@ int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int
   return GH_OK;
 }
 
+// Hands out the next scratch set.  If its previous launch ran on another stream, the new stream is made to wait
+// for it on the device; the host never blocks here.
+int scratch_claim( gh_attn* h, cudaStream_t st, ScratchSet** out )
+{
+  ScratchSet& s = h->scratch[h->scratch_next];
+  h->scratch_next = ( h->scratch_next + 1 ) % kScratchSets;
+  if ( s.used && s.stream != st )
+    GH_CUDA( h, cudaStreamWaitEvent( st, s.done, 0 ) );
+  *out = &s;
+  return GH_OK;
+}
+
+int scratch_release( gh_attn* h, ScratchSet* s, cudaStream_t st )
+{
+  s->used = true;
+  s->stream = st;
+  GH_CUDA( h, cudaEventRecord( s->done, st ) );
+  return GH_OK;
+}
+
 DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, long long layer_off, const void* q, void* xb )
 {
   DecodeArgs a {};
@@ -220,16 +253,20 @@ DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, long long layer
   a.layer_off = layer_off;
   a.q = q;
   a.xb = xb;
-  a.part_o = h->part_o;
-  a.part_ml = h->part_ml;
-  a.counters = h->counters;
   a.dev_error = h->dev_error;
   a.sm_count = h->sm_count;
   return a;
 }
 
-int run_decode( gh_attn* h, const DecodeArgs& a, bool allow_mma, cudaStream_t st )
+int run_decode( gh_attn* h, DecodeArgs a, bool allow_mma, cudaStream_t st )
 {
+  ScratchSet* set = nullptr;
+  if ( const int rc = scratch_claim( h, st, &set ); rc != GH_OK )
+    return rc;
+  a.part_o = set->part_o;
+  a.part_ml = set->part_ml;
+  a.counters = set->counters;
+  a.sched = set->sched;
   cudaError_t e;
   if ( h->use_mma && allow_mma ) {
     e = launch_decode_mma( a, &h->kv_map, st, &h->stats.kernel_launches );
@@ -240,7 +277,7 @@ int run_decode( gh_attn* h, const DecodeArgs& a, bool allow_mma, cudaStream_t st
   }
   if ( e != cudaSuccess )
     return cuda_fail( h, "decode kernel launch", e );
-  return GH_OK;
+  return scratch_release( h, set, st );
 }
 
 int check_batch_ready( gh_attn* h, uint32_t layer )
@@ -365,14 +402,18 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
 
   // split partial records: one per (work item, query head)
   const size_t recs = static_cast<size_t>( h->max_items ) * sh.n_heads;
-  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->part_o ), recs * sh.head_size * sizeof( float ) ) );
-  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->part_ml ), recs * 2 * sizeof( float ) ) );
-  const size_t n_counters = static_cast<size_t>( cfg->max_batch ) * sh.n_heads;
-  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->counters ), n_counters * sizeof( int ) ) );
-  GH_CUDA( h.get(), cudaMemset( h->counters, 0, n_counters * sizeof( int ) ) );
+  const size_t n_counters = static_cast<size_t>( cfg->max_batch ) * sh.n_heads + 2;
+  for ( auto& set : h->scratch ) {
+    GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_o ), recs * sh.head_size * sizeof( float ) ) );
+    GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_ml ), recs * 2 * sizeof( float ) ) );
+    GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.counters ), n_counters * sizeof( int ) ) );
+    GH_CUDA( h.get(), cudaMemset( set.counters, 0, n_counters * sizeof( int ) ) );
+    set.sched = set.counters + ( n_counters - 2 );
+    GH_CUDA( h.get(), cudaEventCreateWithFlags( &set.done, cudaEventDisableTiming ) );
+  }
   GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->dev_error ), sizeof( uint32_t ) ) );
   GH_CUDA( h.get(), cudaMemset( h->dev_error, 0, sizeof( uint32_t ) ) );
-  h->stats.scratch_bytes = recs * ( sh.head_size + 2 ) * sizeof( float ) + n_counters * sizeof( int )
+  h->stats.scratch_bytes = kScratchSets * ( recs * ( sh.head_size + 2 ) * sizeof( float ) + n_counters * sizeof( int ) )
                            + 2 * h->entry_bytes * kRing;
 
   if ( h->use_mma ) {
@@ -426,9 +467,13 @@ int gh_attn_destroy( gh_attn_t h )
   if ( h->ring[0].host )
     cudaFreeHost( h->ring[0].host );
   cudaFree( h->ring[0].dev );
-  cudaFree( h->part_o );
-  cudaFree( h->part_ml );
-  cudaFree( h->counters );
+  for ( auto& set : h->scratch ) {
+    cudaFree( set.part_o );
+    cudaFree( set.part_ml );
+    cudaFree( set.counters );
+    if ( set.done )
+      cudaEventDestroy( set.done );
+  }
   cudaFree( h->dev_error );
   h->pool.destroy();
   (void)cudaGetLastError();
@@ -659,8 +704,8 @@ int gh_attn_forward_attention_host( gh_attn_t h,
                             mb * ( h->sh.n_heads * h->sh.head_size + h->sh.row_elems ) * sizeof( float ) ) );
     GH_CUDA( h, cudaEventCreateWithFlags( &s.done, cudaEventDisableTiming ) );
   }
-  if ( s.used )
-    GH_CUDA( h, cudaEventSynchronize( s.done ) );
+  if ( s.used ) // the staging set may still be in use by an earlier layer on another stream: order on the device
+    GH_CUDA( h, cudaStreamWaitEvent( st, s.done, 0 ) );
   s.used = true;
 
   const size_t io = dtype_size( io_dtype );

@@ -39,6 +39,7 @@ struct DecodeArgs
   float* part_o;
   float* part_ml;
   int* counters;
+  int* sched; // two words, zero between launches: next work unit, blocks that have left
   uint32_t* dev_error;
   uint32_t sm_count;
 };

@@ -189,3 +189,39 @@ def test_convert_and_copy():
     with pytest.raises(Exception):
         st.convert_and_copy(same, torch.float16, same, torch.float16, 10, 3)  # host-to-host is rejected
     st.close()
+
+
+def test_layers_in_flight_on_several_streams(oracle):
+    """One batch, four layers, each layer's host-buffer call on its own stream (what an end-to-end driver does to
+    overlap copies with kernels).  Every context is cut into 64-token items, so every launch uses split partial
+    records and arrival counters; launches in flight together must not share them."""
+    pos = [130, 511, 64, 300, 1, 447]
+    layer_cases = [cases.make_case(f"l{l}", "mini_g8", cases.F16, pos, seed=500 + l) for l in range(4)]
+    wants = [oracle.layer_step(c) for c in layer_cases]
+    st = gpu_util.make_stage(layer_cases[0], layers=4, decode_chunk=64, paged=True)
+    slots = gpu_util.load_case(st, layer_cases[0], layer=0)
+    for l in range(1, 4):
+        for i, p in enumerate(pos):
+            st.prepare(int(slots[i]), l, p, False)
+            if p > 0:
+                st.layer_view(int(slots[i]), l, p).copy_(gpu_util.to_dev(layer_cases[l].cache[i][:p], cases.F16))
+    torch.cuda.synchronize()
+    q_h = [torch.from_numpy(c.q).pin_memory() for c in layer_cases]
+    kv_h = [torch.from_numpy(c.kv_new).pin_memory() for c in layer_cases]
+    xb_h = [torch.zeros_like(q).pin_memory() for q in q_h]
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    main = torch.cuda.current_stream()
+    for rep in range(3):  # repeat so that scratch sets and staging buffers are reused across streams
+        st.batch_begin(slots, pos, stream=main)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        for s in streams:
+            s.wait_event(ready)
+        for l in range(4):
+            st.forward_attention_host(l, cases.F16, q_h[l], kv_h[l], xb_h[l], stream=streams[(l + rep) % 3])
+        torch.cuda.synchronize()
+        for l in range(4):
+            np.testing.assert_allclose(xb_h[l].numpy().astype(np.float32), wants[l].xb.astype(np.float32), rtol=0,
+                                       atol=cases.TOL_XB[cases.F16], err_msg=f"layer {l}, repetition {rep}")
+    assert st.stats().device_error == 0
+    st.close()
