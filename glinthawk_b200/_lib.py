@@ -6,11 +6,12 @@ compute entry point of the library launches CUDA kernels or returns an error sta
 from __future__ import annotations
 
 import ctypes as C
+import os
 import re
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "libglinthawk_attn.so"
+LIB_PATH = Path(os.environ.get("GLINTHAWK_ATTN_LIB", PKG / "libglinthawk_attn.so"))  # override for A/B runs
 HEADER = PKG.parent / "include" / "glinthawk_attn.h"
 
 GH_OK, GH_ERR_INVALID, GH_ERR_CUDA, GH_ERR_NO_SLOT, GH_ERR_CAPACITY = 0, 1, 2, 3, 4

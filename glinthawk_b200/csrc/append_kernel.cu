@@ -6,7 +6,10 @@
 // table values and operands are loaded from the storage type into fp32, the rotation is computed in fp32 and
 // rounded once.  V is never converted: it moves as 16-byte chunks, bit for bit.
 //
-// HBM-bound and tiny (a few MiB per launch): one thread block per context, every thread moves 16-byte chunks.
+// Tiny (a few MiB per launch) and therefore latency-bound: the grid is (context, slice) with one 16-byte chunk
+// per thread, so every load of the launch is in flight at once.  The kernel lets the kernel behind it in the
+// stream start its prologue early (programmatic dependent launch); that kernel must wait for this one before it
+// touches q or the slot rows.
 #include "gh_kernels.cuh"
 
 namespace gh {
@@ -37,6 +40,7 @@ __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
   constexpr int N = Vec16<T>::N;
   const int i = blockIdx.x;
   const Shape& sh = a.sh;
+  asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
 
   T* row;
   uint32_t pos;
@@ -64,7 +68,7 @@ __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
   const int k_units = k_chunks * per_chunk;
   const int v_units = src != nullptr ? k_chunks : 0;
 
-  for ( int u = threadIdx.x; u < k_units + v_units; u += blockDim.x ) {
+  for ( int u = blockIdx.y * blockDim.x + threadIdx.x; u < k_units + v_units; u += gridDim.y * blockDim.x ) {
     if ( u >= k_units ) { // V: plain copy
       const int e = ( u - k_units ) * N;
       st16( row + sh.kv_dim + e, ld16( src + sh.kv_dim + e ) );
@@ -95,10 +99,14 @@ cudaError_t launch_append( const AppendArgs& a, cudaStream_t st, uint64_t* launc
 {
   if ( a.batch == 0 )
     return cudaSuccess;
+  // chunk operations per context: K chunks (each with the group's q chunks) + V chunks
+  const unsigned n16 = a.dtype == DT_F32 ? 4 : 8;
+  const unsigned units = ( a.sh.kv_dim / n16 ) * ( 2 + a.sh.group );
+  const dim3 grid( a.batch, ( units + 255 ) / 256 );
   switch ( a.dtype ) {
-    case DT_F32: append_kernel<float><<<a.batch, 256, 0, st>>>( a ); break;
-    case DT_F16: append_kernel<__half><<<a.batch, 256, 0, st>>>( a ); break;
-    case DT_BF16: append_kernel<__nv_bfloat16><<<a.batch, 256, 0, st>>>( a ); break;
+    case DT_F32: append_kernel<float><<<grid, 256, 0, st>>>( a ); break;
+    case DT_F16: append_kernel<__half><<<grid, 256, 0, st>>>( a ); break;
+    case DT_BF16: append_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>( a ); break;
     default: return cudaErrorInvalidValue;
   }
   ( *launches )++;

@@ -49,14 +49,13 @@ struct RingEntry
   bool used = false, multi_stream = false;
 };
 
-// Scratch of one decode launch: split partial records, arrival counters, the persistent kernel's scheduling words.
+// Scratch of one decode launch: split partial records and arrival counters.
 // A launch owns its set until its kernel has finished, so launches on different streams never share one.
 struct ScratchSet
 {
   float* part_o = nullptr;
   float* part_ml = nullptr;
-  int* counters = nullptr; // [max_batch * n_heads] arrival counters, then 2 scheduling words
-  int* sched = nullptr;
+  int* counters = nullptr; // [max_batch * n_heads] arrival counters
   cudaEvent_t done = nullptr;
   cudaStream_t stream = nullptr;
   bool used = false;
@@ -199,6 +198,7 @@ int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int
   pp.tile = decode_mma_tile_tokens();
   pp.fixed_chunk = h->cfg.decode_chunk;
   pp.max_items = h->max_items;
+  pp.blocks_per_sm = h->use_mma ? 4 : 8;
   Plan plan;
   if ( !plan_batch( pp, ctx, plan ) )
     return fail( h, GH_ERR_INVALID, "batch does not fit the work-item buffer" );
@@ -266,7 +266,6 @@ int run_decode( gh_attn* h, DecodeArgs a, bool allow_mma, cudaStream_t st )
   a.part_o = set->part_o;
   a.part_ml = set->part_ml;
   a.counters = set->counters;
-  a.sched = set->sched;
   cudaError_t e;
   if ( h->use_mma && allow_mma ) {
     e = launch_decode_mma( a, &h->kv_map, st, &h->stats.kernel_launches );
@@ -402,13 +401,12 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
 
   // split partial records: one per (work item, query head)
   const size_t recs = static_cast<size_t>( h->max_items ) * sh.n_heads;
-  const size_t n_counters = static_cast<size_t>( cfg->max_batch ) * sh.n_heads + 2;
+  const size_t n_counters = static_cast<size_t>( cfg->max_batch ) * sh.n_heads;
   for ( auto& set : h->scratch ) {
     GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_o ), recs * sh.head_size * sizeof( float ) ) );
     GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_ml ), recs * 2 * sizeof( float ) ) );
     GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.counters ), n_counters * sizeof( int ) ) );
     GH_CUDA( h.get(), cudaMemset( set.counters, 0, n_counters * sizeof( int ) ) );
-    set.sched = set.counters + ( n_counters - 2 );
     GH_CUDA( h.get(), cudaEventCreateWithFlags( &set.done, cudaEventDisableTiming ) );
   }
   GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->dev_error ), sizeof( uint32_t ) ) );
@@ -426,7 +424,7 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
     } else {
       const cuuint64_t dims[2] = { sh.row_elems, total_rows };
       const cuuint64_t strides[1] = { g.row_bytes };
-      const cuuint32_t box[2] = { 64, decode_mma_tile_tokens() };
+      const cuuint32_t box[2] = { 64, decode_mma_box_rows() };
       const cuuint32_t estr[2] = { 1, 1 };
       const CUresult r = api->TensorMapEncodeTiled(
         &h->kv_map, cfg->dtype == GH_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,

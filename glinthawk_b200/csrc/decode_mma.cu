@@ -6,22 +6,23 @@
 // them.  The arithmetic it must agree with is the amd64 backend's (src/arch/amd64/llama2/ops.hh:170-298).
 //
 // Decomposition.  A work item is a run of tokens [t_begin, t_end) of one context (t_begin a multiple of the
-// 64-token tile); a work unit is one (work item, kv head), so all query heads of a GQA group share every K/V byte
-// that is fetched.  Thread blocks are persistent and pull units from a counter.  A block is 4 consumer warps +
-// 1 producer warp:
-//   * The producer's elected lane walks the item tile by tile and issues four TMA tile loads per tile
-//     (K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127; each a [64 tokens x 128 B] box, 128-byte swizzle)
-//     into a ring of shared-memory stages, completion signalled on an mbarrier per stage.  The KV arena is ONE
+// 64-token tile); one thread block handles one (work item, kv head), so all query heads of a GQA group share
+// every K/V byte that is fetched.  A block is NW consumer warps + 1 producer warp (NW = 2 by default):
+//   * The producer's elected lane walks the item tile by tile (a tile is 16*NW tokens) and issues four TMA tile
+//     loads per 32 tokens (K dims 0-63, K dims 64-127, V dims 0-63, V dims 64-127; each a [32 tokens x 128 B] box,
+//     128-byte swizzle) into a ring of shared-memory stages, completion signalled on an mbarrier per stage.  The KV arena is ONE
 //     2-D tensor [rows][2*kv_dim], so a context/layer/token is just a row coordinate.  No multicast: every block
 //     fetches its own tiles.
 //   * Consumer warp w owns tokens 16w..16w+15 of every tile: S = Q K^T with mma.m16n8k16 (query heads of the group
 //     are the M rows, padded to 16), online softmax in the log2 domain with quad shuffles, O += P V with the
-//     probabilities re-used from registers.  The four warps keep independent (m, l, O) states that are combined
+//     probabilities re-used from registers.  The warps keep independent (m, l, O) states that are combined
 //     through shared memory at the end ("warp-level merge"); contexts cut into several items are then combined by
 //     the last block to finish (gh_merge.cuh).
 // The path is HBM-bound: 512 B of K+V per (token, kv head) against 2 x 16 x 128 x 2 tensor flops.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a sticky error word and leaves.
+#include <cstdlib>
+
 #include "gh_kernels.cuh"
 #include "gh_merge.cuh"
 
@@ -30,15 +31,25 @@ namespace gh {
 namespace {
 
 constexpr int kHS = 128;
-constexpr int kTile = 64;                     // tokens per stage
-constexpr int kConsumerWarps = kTile / 16;    // 4
-constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kThreads = kConsumers + 32;     // + producer warp
-constexpr int kBoxBytes = kTile * 128;        // one [64 x 64-element] box
-constexpr int kStageBytes = 4 * kBoxBytes;    // K lo, K hi, V lo, V hi
-constexpr int kStages = 3;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024; // + slack to align the ring to 1024 B
+constexpr int kPlanTile = 64; // work items start on multiples of this many tokens
+constexpr int kBoxRows = 32;  // token rows per TMA box (every variant's tile is a multiple)
 constexpr uint32_t kWaitLimit = 1u << 22;
+
+// Compile-time geometry of one kernel variant: NW consumer warps (each owns 16 tokens of a tile), ST ring stages,
+// MINB thread blocks per SM the register budget is sized for.
+template<int NW, int ST, int MINB>
+struct Geo
+{
+  static constexpr int kConsumerWarps = NW;
+  static constexpr int kTile = NW * 16;               // tokens per stage
+  static constexpr int kConsumers = NW * 32;
+  static constexpr int kThreads = kConsumers + 32;    // + producer warp
+  static constexpr int kBoxBytes = kTile * 128;       // one [kTile tokens x 64 elements] box
+  static constexpr int kStageBytes = 4 * kBoxBytes;   // K lo, K hi, V lo, V hi
+  static constexpr int kStages = ST;
+  static constexpr int kSmemBytes = ST * kStageBytes + 1024; // + slack to align the ring to 1024 B
+  static constexpr int kMinBlocks = MINB;
+};
 
 __device__ __forceinline__ uint32_t smem_u32( const void* p )
 {
@@ -147,38 +158,32 @@ __device__ __forceinline__ float fast_exp2( float x )
   return y;
 }
 
-// What a filled stage holds: tile `tile` of work unit `unit` (= work item * n_kv_heads + kv head); unit < 0 ends
-// the stream.  Written by the producer before it arms the stage's barrier, read by the consumers after their wait.
-struct StageTag
-{
-  int unit;
-  int tile;
-};
-
 // G16: the group has more than 8 query heads, so rows 8..15 of the M=16 tile are live too.
-//
-// Persistent blocks: the grid is at most two blocks per SM and every block pulls work units from a shared counter
-// until none are left, longest units first.  The producer runs ahead of the consumers across unit boundaries, so the
-// TMA pipeline does not drain while the consumers merge and write a finished unit.
-template<typename T, bool G16>
-__global__ void __launch_bounds__( kThreads, 2 ) decode_mma_kernel( const DecodeArgs a, const __grid_constant__ CUtensorMap kv_map )
+template<typename T, bool G16, typename G>
+__global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
+  decode_mma_kernel( const DecodeArgs a, const __grid_constant__ CUtensorMap kv_map )
 {
+  constexpr int kTile = G::kTile, kConsumerWarps = G::kConsumerWarps, kConsumers = G::kConsumers;
+  constexpr int kBoxBytes = G::kBoxBytes, kStageBytes = G::kStageBytes, kStages = G::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kStages];
   __shared__ uint64_t bar_empty[kStages];
-  __shared__ StageTag sm_tag[kStages];
-  __shared__ float sm_wm[kConsumerWarps][8];
-  __shared__ float sm_wl[kConsumerWarps][8];
-  __shared__ float sm_m[8];
-  __shared__ float sm_l[8];
+  __shared__ float sm_wm[kConsumerWarps][16];
+  __shared__ float sm_wl[kConsumerWarps][16];
+  __shared__ float sm_m[16];
+  __shared__ float sm_l[16];
   __shared__ int sm_flag;
 
   uint8_t* ring = reinterpret_cast<uint8_t*>( ( reinterpret_cast<uintptr_t>( smem_raw ) + 1023 ) & ~uintptr_t( 1023 ) );
 
   const Shape& sh = a.sh;
+  const int item_idx = blockIdx.x / sh.n_kv_heads;
+  const int kvh = blockIdx.x - item_idx * sh.n_kv_heads;
+  const WorkItem it = a.items[item_idx];
+  const CtxMeta c = a.ctx[it.ctx];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_units = (int)( a.n_items * sh.n_kv_heads );
+  const int n_tiles = ( it.t_end - it.t_begin + kTile - 1 ) / kTile;
 
   if ( threadIdx.x == 0 ) {
     for ( int s = 0; s < kStages; s++ ) {
@@ -193,118 +198,85 @@ __global__ void __launch_bounds__( kThreads, 2 ) decode_mma_kernel( const Decode
     // ---------------- producer ----------------
     if ( lane == 0 ) {
       asm volatile( "prefetch.tensormap [%0];" ::"l"( reinterpret_cast<uint64_t>( &kv_map ) ) : "memory" );
-      const long long row_bytes = (long long)sh.row_elems * (long long)sizeof( T );
-      int fill = 0; // stages filled so far by this block
-      bool ok = true;
-      while ( ok ) {
-        const int u = atomicAdd( &a.sched[0], 1 );
-        if ( u >= n_units )
-          break;
-        const int item_idx = u / (int)sh.n_kv_heads;
-        const int kvh = u - item_idx * (int)sh.n_kv_heads;
-        const WorkItem it = a.items[item_idx];
-        const CtxMeta c = a.ctx[it.ctx];
-        const int n_tiles = ( it.t_end - it.t_begin + kTile - 1 ) / kTile;
-        const int row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / row_bytes ) + it.t_begin;
-        const int xk = kvh * kHS;
-        const int xv = (int)sh.kv_dim + kvh * kHS;
-        for ( int t = 0; t < n_tiles; t++, fill++ ) {
-          const int s = fill % kStages;
-          if ( fill >= kStages && !mbar_wait( &bar_empty[s], ( ( fill / kStages ) - 1 ) & 1 ) ) {
-            atomicOr( a.dev_error, 1u );
-            ok = false;
-            break;
-          }
-          sm_tag[s].unit = u;
-          sm_tag[s].tile = t;
-          uint8_t* st = ring + s * kStageBytes;
-          mbar_expect_tx( &bar_full[s], kStageBytes );
-          const int y = row0 + t * kTile;
-          tma_load_2d( st + 0 * kBoxBytes, &kv_map, xk, y, &bar_full[s] );
-          tma_load_2d( st + 1 * kBoxBytes, &kv_map, xk + 64, y, &bar_full[s] );
-          tma_load_2d( st + 2 * kBoxBytes, &kv_map, xv, y, &bar_full[s] );
-          tma_load_2d( st + 3 * kBoxBytes, &kv_map, xv + 64, y, &bar_full[s] );
-        }
-      }
-      if ( ok ) { // end-of-stream marker for the consumers
-        const int s = fill % kStages;
-        if ( fill < kStages || mbar_wait( &bar_empty[s], ( ( fill / kStages ) - 1 ) & 1 ) ) {
-          sm_tag[s].unit = -1;
-          sm_tag[s].tile = 0;
-          mbar_arrive( &bar_full[s] );
-        } else {
+      // Launched as a programmatic dependent of the kernel before it in the stream (normally the append kernel):
+      // everything above overlapped with that kernel; its writes are visible after this wait.
+      asm volatile( "griddepcontrol.wait;" ::: "memory" );
+      const size_t row_bytes = (size_t)sh.row_elems * sizeof( T );
+      const int row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / (long long)row_bytes ) + it.t_begin;
+      const int xk = kvh * kHS;
+      const int xv = (int)sh.kv_dim + kvh * kHS;
+      for ( int t = 0; t < n_tiles; t++ ) {
+        const int s = t % kStages;
+        if ( t >= kStages && !mbar_wait( &bar_empty[s], ( ( t / kStages ) - 1 ) & 1 ) ) {
           atomicOr( a.dev_error, 1u );
+          break;
         }
-      }
-      // The block that leaves last puts the two scheduling words back to zero for the next launch.
-      __threadfence();
-      if ( atomicAdd( &a.sched[1], 1 ) == (int)gridDim.x - 1 ) {
-        a.sched[0] = 0;
-        a.sched[1] = 0;
+        uint8_t* st = ring + s * kStageBytes;
+        mbar_expect_tx( &bar_full[s], kStageBytes );
+        const int y = row0 + t * kTile;
+#pragma unroll
+        for ( int j = 0; j < kTile / kBoxRows; j++ ) { // the descriptor's box is kBoxRows tokens x 128 B
+          uint8_t* sub = st + j * kBoxRows * 128;
+          tma_load_2d( sub + 0 * kBoxBytes, &kv_map, xk, y + j * kBoxRows, &bar_full[s] );
+          tma_load_2d( sub + 1 * kBoxBytes, &kv_map, xk + 64, y + j * kBoxRows, &bar_full[s] );
+          tma_load_2d( sub + 2 * kBoxBytes, &kv_map, xv, y + j * kBoxRows, &bar_full[s] );
+          tma_load_2d( sub + 3 * kBoxBytes, &kv_map, xv + 64, y + j * kBoxRows, &bar_full[s] );
+        }
       }
     }
     return;
   }
 
   // ---------------- consumers ----------------
-  const int quad_row = lane >> 2;        // row of the M=16 tile this thread holds (and row + 8)
+  const int quad_row = lane >> 2;       // row of the M=16 tile this thread holds (and row + 8)
   const int quad_col = ( lane & 3 ) * 2; // first of its two columns inside an 8-wide tile
   const int group = sh.group;
   const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f; // 1/sqrt(128) * log2(e)
 
-  // ldmatrix lane addressing: matrix index lane/8, row lane%8
+  // Q fragments (A operand), 8 k-steps of 16 dims; rows >= group are zero.
+  uint32_t qf[8][4];
+  asm volatile( "griddepcontrol.wait;" ::: "memory" ); // q was rotated by the kernel before this one
+  {
+    const T* qbase = static_cast<const T*>( a.q ) + (size_t)it.ctx * sh.n_heads * kHS + (size_t)kvh * group * kHS;
+#pragma unroll
+    for ( int ks = 0; ks < 8; ks++ ) {
+      const int d = ks * 16 + quad_col;
+      const bool lo = quad_row < group;
+      const bool hi = G16 && ( quad_row + 8 < group );
+      qf[ks][0] = lo ? *reinterpret_cast<const uint32_t*>( qbase + quad_row * kHS + d ) : 0u;
+      qf[ks][2] = lo ? *reinterpret_cast<const uint32_t*>( qbase + quad_row * kHS + d + 8 ) : 0u;
+      qf[ks][1] = hi ? *reinterpret_cast<const uint32_t*>( qbase + ( quad_row + 8 ) * kHS + d ) : 0u;
+      qf[ks][3] = hi ? *reinterpret_cast<const uint32_t*>( qbase + ( quad_row + 8 ) * kHS + d + 8 ) : 0u;
+    }
+  }
+
+  float o[16][4];
+#pragma unroll
+  for ( int n = 0; n < 16; n++ )
+    o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = { -INFINITY, -INFINITY };
+  float l_run[2] = { 0.f, 0.f };
+
+  // ldmatrix lane addressing (see the header comment): matrix index lane/8, row lane%8
   const int lm = lane >> 3, lr = lane & 7;
   const int k_tok = warp * 16 + ( lm >> 1 ) * 8 + lr; // K: matrices 0,1 -> tokens 0-7, matrices 2,3 -> tokens 8-15
   const int k_chunk_sel = lm & 1;                     //    matrices 0,2 -> dims +0..7, 1,3 -> dims +8..15
   const int v_tok = warp * 16 + ( lm & 1 ) * 8 + lr;  // V: matrices 0,2 -> tokens 0-7, 1,3 -> tokens 8-15
   const int v_chunk_sel = lm >> 1;                    //    matrices 0,1 -> dims +0..7, 2,3 -> dims +8..15
-  const int w0 = warp * 16;
 
-  uint32_t qf[8][4]; // Q fragments (A operand) of the current unit: 8 k-steps of 16 dims; rows >= group are zero
-  float o[16][4];
-  float m_run[2], l_run[2];
-  WorkItem it {};
-  CtxMeta c {};
-  int kvh = 0, n_tiles = 0;
-
-  for ( int cons = 0;; cons++ ) {
-    const int s = cons % kStages;
+  bool ok = true;
+  for ( int t = 0; t < n_tiles; t++ ) {
+    const int s = t % kStages;
     // every lane waits (each needs the acquire); the verdict is made warp-uniform before branching on it
-    if ( !__all_sync( 0xffffffffu, mbar_wait( &bar_full[s], ( cons / kStages ) & 1 ) ) ) {
+    if ( !__all_sync( 0xffffffffu, mbar_wait( &bar_full[s], ( t / kStages ) & 1 ) ) ) {
       if ( lane == 0 )
         atomicOr( a.dev_error, 2u );
-      return;
+      ok = false;
+      break;
     }
-    const StageTag tag = sm_tag[s];
-    if ( tag.unit < 0 )
-      return;
-
-    if ( tag.tile == 0 ) { // a new unit starts: fetch its description and query heads, reset the running state
-      const int item_idx = tag.unit / (int)sh.n_kv_heads;
-      kvh = tag.unit - item_idx * (int)sh.n_kv_heads;
-      it = a.items[item_idx];
-      c = a.ctx[it.ctx];
-      n_tiles = ( it.t_end - it.t_begin + kTile - 1 ) / kTile;
-      const T* qbase = static_cast<const T*>( a.q ) + (size_t)it.ctx * sh.n_heads * kHS + (size_t)kvh * group * kHS;
-      const bool lo = quad_row < group;
-      const bool hi = G16 && ( quad_row + 8 < group );
-#pragma unroll
-      for ( int ks = 0; ks < 8; ks++ ) {
-        const int d = ks * 16 + quad_col;
-        qf[ks][0] = lo ? *reinterpret_cast<const uint32_t*>( qbase + quad_row * kHS + d ) : 0u;
-        qf[ks][2] = lo ? *reinterpret_cast<const uint32_t*>( qbase + quad_row * kHS + d + 8 ) : 0u;
-        qf[ks][1] = hi ? *reinterpret_cast<const uint32_t*>( qbase + ( quad_row + 8 ) * kHS + d ) : 0u;
-        qf[ks][3] = hi ? *reinterpret_cast<const uint32_t*>( qbase + ( quad_row + 8 ) * kHS + d + 8 ) : 0u;
-      }
-#pragma unroll
-      for ( int n = 0; n < 16; n++ )
-        o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-      m_run[0] = m_run[1] = -INFINITY;
-      l_run[0] = l_run[1] = 0.f;
-    }
-
     const uint32_t st = smem_u32( ring + s * kStageBytes );
-    const int valid = min( kTile, it.t_end - it.t_begin - tag.tile * kTile ); // live tokens in this tile
+    const int valid = min( kTile, it.t_end - it.t_begin - t * kTile ); // live tokens in this tile
+    const int w0 = warp * 16;
 
     if ( w0 < valid ) {
       if ( valid < w0 + 16 ) {
@@ -384,97 +356,160 @@ __global__ void __launch_bounds__( kThreads, 2 ) decode_mma_kernel( const Decode
       }
     }
 
-    if ( tag.tile == n_tiles - 1 ) {
-      // ---- the unit is complete.  Its last stage doubles as scratch for combining the four warps' states
-      // (the "warp-level merge"); it goes back to the producer only afterwards.  Eight rows at a time.
-      float* sm_wo = reinterpret_cast<float*>( ring + s * kStageBytes ); // [warp][8][128]
-      float* sm_o = sm_wo + kConsumerWarps * 8 * kHS;                    // [8][128] merged
-#pragma unroll
-      for ( int half = 0; half < ( G16 ? 2 : 1 ); half++ ) {
-        const int rows = min( 8, group - half * 8 );
-        asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" ); // everyone is done reading the stage
-        float l = l_run[half];
-        l += __shfl_xor_sync( 0xffffffffu, l, 1 );
-        l += __shfl_xor_sync( 0xffffffffu, l, 2 );
-        if ( ( lane & 3 ) == 0 ) {
-          sm_wm[warp][quad_row] = m_run[half];
-          sm_wl[warp][quad_row] = l;
-        }
-#pragma unroll
-        for ( int n = 0; n < 16; n++ )
-          *reinterpret_cast<float2*>( &sm_wo[( warp * 8 + quad_row ) * kHS + n * 8 + quad_col] )
-            = make_float2( o[n][half * 2], o[n][half * 2 + 1] );
-        asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
-        {
-          const int d = threadIdx.x; // 128 consumer threads <-> 128 dims
-          for ( int r = 0; r < rows; r++ ) {
-            float M = -INFINITY;
-#pragma unroll
-            for ( int w = 0; w < kConsumerWarps; w++ )
-              M = fmaxf( M, sm_wm[w][r] );
-            float L = 0.f, O = 0.f;
-#pragma unroll
-            for ( int w = 0; w < kConsumerWarps; w++ ) {
-              const float wgt = fast_exp2( sm_wm[w][r] - M );
-              L += wgt * sm_wl[w][r];
-              O += wgt * sm_wo[( w * 8 + r ) * kHS + d];
-            }
-            sm_o[r * kHS + d] = O;
-            if ( d == 0 ) {
-              sm_m[r] = M;
-              sm_l[r] = L;
-            }
-          }
-        }
-        asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
-        const int head0 = kvh * group + half * 8;
-        finish_item<T>( sh, c, it, head0, rows, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
-                        a.counters, it.ctx * (int)sh.n_heads + head0, &sm_flag, threadIdx.x, kConsumers, 1 );
-      }
-      asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" ); // scratch no longer read
+    if ( valid < kTile )
       asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" );
-    } else if ( valid < kTile ) {
-      asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" );
-    }
     __syncwarp();
     if ( lane == 0 )
       mbar_arrive( &bar_empty[s] );
   }
+
+  // ---- combine the four warps' states through shared memory (the ring is free once every warp is here)
+  asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
+  if ( !ok || *reinterpret_cast<volatile uint32_t*>( a.dev_error ) != 0 ) {
+    // A wait ran out somewhere in this block or another: give any copy still in flight time to land, then leave.
+    __nanosleep( 1000000 );
+    return;
+  }
+  constexpr int kRows = G16 ? 16 : 8;
+  static_assert( ( kConsumerWarps + 1 ) * kRows * kHS * 4 <= kStages * kStageBytes, "merge scratch must fit the ring" );
+  float* sm_wo = reinterpret_cast<float*>( ring );                 // [warp][kRows][128]
+  float* sm_o = sm_wo + kConsumerWarps * kRows * kHS;               // [kRows][128] merged
+#pragma unroll
+  for ( int half = 0; half < ( G16 ? 2 : 1 ); half++ ) {
+    float l = l_run[half];
+    l += __shfl_xor_sync( 0xffffffffu, l, 1 );
+    l += __shfl_xor_sync( 0xffffffffu, l, 2 );
+    const int row = quad_row + half * 8;
+    if ( ( lane & 3 ) == 0 ) {
+      sm_wm[warp][row] = m_run[half];
+      sm_wl[warp][row] = l;
+    }
+#pragma unroll
+    for ( int n = 0; n < 16; n++ )
+      *reinterpret_cast<float2*>( &sm_wo[( warp * kRows + row ) * kHS + n * 8 + quad_col] )
+        = make_float2( o[n][half * 2], o[n][half * 2 + 1] );
+  }
+  asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
+
+  for ( int d = threadIdx.x; d < kHS; d += kConsumers ) {
+    for ( int r = 0; r < group; r++ ) {
+      float M = -INFINITY;
+#pragma unroll
+      for ( int w = 0; w < kConsumerWarps; w++ )
+        M = fmaxf( M, sm_wm[w][r] );
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for ( int w = 0; w < kConsumerWarps; w++ ) {
+        const float wgt = fast_exp2( sm_wm[w][r] - M );
+        L += wgt * sm_wl[w][r];
+        O += wgt * sm_wo[( w * kRows + r ) * kHS + d];
+      }
+      sm_o[r * kHS + d] = O;
+      if ( d == 0 ) {
+        sm_m[r] = M;
+        sm_l[r] = L;
+      }
+    }
+  }
+  asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
+
+  finish_item<T>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
+                  a.counters, it.ctx * (int)sh.n_heads + kvh * group, &sm_flag, threadIdx.x, kConsumers, 1 );
+}
+
+template<typename T, typename G>
+cudaError_t launch_g( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t st )
+{
+  cudaLaunchConfig_t cfg {};
+  cfg.gridDim = dim3( a.n_items * a.sh.n_kv_heads );
+  cfg.blockDim = dim3( G::kThreads );
+  cfg.dynamicSmemBytes = G::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization; // start while the previous kernel drains
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if ( a.sh.group > 8 )
+    return cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G>, a, *map );
+  return cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, false, G>, a, *map );
+}
+
+// Kernel geometries that are built.  Variant 0 is the default (fastest measured on B200: four small blocks per SM
+// overlap one block's fill and drain with three others' streaming); the others exist for tuning runs
+// (environment variable GLINTHAWK_DECODE_VARIANT, read once).
+using Geo0 = Geo<2, 3, 4>; // 32-token tiles, 48 KiB ring, 4 blocks per SM
+using Geo1 = Geo<4, 3, 2>; // 64-token tiles, 96 KiB ring, 2 blocks per SM
+using Geo2 = Geo<2, 4, 3>; // 32-token tiles, 64 KiB ring, 3 blocks per SM
+using Geo3 = Geo<2, 6, 2>; // 32-token tiles, 96 KiB ring, 2 blocks per SM
+
+int variant()
+{
+  static const int v = [] {
+    const char* e = std::getenv( "GLINTHAWK_DECODE_VARIANT" );
+    const int x = e != nullptr ? std::atoi( e ) : 0;
+    return ( x >= 0 && x <= 3 ) ? x : 0;
+  }();
+  return v;
 }
 
 template<typename T>
 cudaError_t launch_t( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t st )
 {
-  const unsigned units = a.n_items * a.sh.n_kv_heads;
-  const unsigned grid = units < 2 * a.sm_count ? units : 2 * a.sm_count; // persistent: two blocks per SM
-  if ( a.sh.group > 8 )
-    decode_mma_kernel<T, true><<<grid, kThreads, kSmemBytes, st>>>( a, *map );
-  else
-    decode_mma_kernel<T, false><<<grid, kThreads, kSmemBytes, st>>>( a, *map );
-  return cudaGetLastError();
+  switch ( variant() ) {
+    case 1: return launch_g<T, Geo1>( a, map, st );
+    case 2: return launch_g<T, Geo2>( a, map, st );
+    case 3: return launch_g<T, Geo3>( a, map, st );
+    default: return launch_g<T, Geo0>( a, map, st );
+  }
+}
+
+template<typename T, bool G16, typename G>
+cudaError_t allow_smem()
+{
+  return cudaFuncSetAttribute( decode_mma_kernel<T, G16, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes );
+}
+
+template<typename G>
+cudaError_t allow_smem_all()
+{
+  cudaError_t e = allow_smem<__half, false, G>();
+  if ( e == cudaSuccess )
+    e = allow_smem<__half, true, G>();
+  if ( e == cudaSuccess )
+    e = allow_smem<__nv_bfloat16, false, G>();
+  if ( e == cudaSuccess )
+    e = allow_smem<__nv_bfloat16, true, G>();
+  return e;
 }
 
 } // namespace
 
 uint32_t decode_mma_tile_tokens()
 {
-  return kTile;
+  return kPlanTile;
+}
+
+uint32_t decode_mma_box_rows()
+{
+  return kBoxRows;
 }
 
 bool decode_mma_supported( const Shape& sh, uint32_t dtype )
 {
-  return ( dtype == DT_F16 || dtype == DT_BF16 ) && sh.head_size == kHS && sh.group <= 16 && sh.seq_len % kTile == 0;
+  return ( dtype == DT_F16 || dtype == DT_BF16 ) && sh.head_size == kHS && sh.group <= 16
+         && sh.seq_len % kPlanTile == 0;
 }
 
 cudaError_t decode_mma_prepare()
 {
-  cudaError_t e = cudaFuncSetAttribute( decode_mma_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
+  cudaError_t e = allow_smem_all<Geo0>();
   if ( e == cudaSuccess )
-    e = cudaFuncSetAttribute( decode_mma_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
+    e = allow_smem_all<Geo1>();
   if ( e == cudaSuccess )
-    e = cudaFuncSetAttribute( decode_mma_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
+    e = allow_smem_all<Geo2>();
   if ( e == cudaSuccess )
-    e = cudaFuncSetAttribute( decode_mma_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
+    e = allow_smem_all<Geo3>();
   return e;
 }
 

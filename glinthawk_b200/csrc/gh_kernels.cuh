@@ -39,7 +39,6 @@ struct DecodeArgs
   float* part_o;
   float* part_ml;
   int* counters;
-  int* sched; // two words, zero between launches: next work unit, blocks that have left
   uint32_t* dev_error;
   uint32_t sm_count;
 };
@@ -62,7 +61,8 @@ cudaError_t launch_decode_generic( const DecodeArgs& a, cudaStream_t st, uint64_
 bool decode_mma_supported( const Shape& sh, uint32_t dtype );
 cudaError_t decode_mma_prepare(); // one-time function attributes
 cudaError_t launch_decode_mma( const DecodeArgs& a, const CUtensorMap* kv_map, cudaStream_t st, uint64_t* launches );
-uint32_t decode_mma_tile_tokens();
+uint32_t decode_mma_tile_tokens(); // work items start on multiples of this
+uint32_t decode_mma_box_rows();    // token rows of the TMA box the descriptor must be encoded with
 
 cudaError_t launch_scores( const ScoreArgs& a, cudaStream_t st, uint64_t* launches );  // attention_0_gemm
 cudaError_t launch_softmax( const ScoreArgs& a, cudaStream_t st, uint64_t* launches ); // attention_softmax

@@ -1,14 +1,19 @@
 // Host-side work planning for the fused decode kernels (pure host code, no CUDA calls).
 //
-// A batch is ragged: context i attends over pos[i] + 1 tokens.  Long contexts are cut along the token axis
-// into work items of similar size so that every SM streams KV for the whole launch, and the items are ordered
-// longest-first so the hardware block scheduler approximates longest-processing-time-first.  The reference has
-// no counterpart: it loops over the batch on the host and launches per context
+// A batch is ragged: context i attends over pos[i] + 1 tokens.  Work items are ordered longest-first so that the
+// hardware block scheduler approximates longest-processing-time-first, and long contexts are cut along the token
+// axis only as far as that pays: every extra item costs a pipeline fill and drain, and an item of a cut context
+// also costs a partial record, a fence, an atomic and a share of the final merge (measured on B200: about 2 us
+// for a whole context, about 8 us for a piece, against 23 ns per token).  The split length is therefore chosen by
+// simulating the launch for a few candidate lengths and keeping the one with the shortest makespan.  The
+// reference has no counterpart: it loops over the batch on the host and launches per context
 // (src/arch/cuda/llama2/ops.cuh:272-453).
 #pragma once
 
 #include <algorithm>
 #include <cstdint>
+#include <functional>
+#include <queue>
 #include <vector>
 
 #include "gh_common.cuh"
@@ -22,8 +27,10 @@ struct PlanParams
   uint32_t tile = 64;           // split boundaries are multiples of this many tokens
   uint32_t fixed_chunk = 0;     // non-zero: use exactly this split length
   uint32_t max_items = 0;       // capacity of the item and partial-record buffers
-  uint32_t blocks_per_sm_target = 16; // aim for about this many blocks per SM over the launch
+  uint32_t blocks_per_sm = 2;       // thread blocks resident per SM
   uint32_t min_chunk = 256;
+  uint32_t whole_overhead = 90;     // cost of an uncut context's item beyond its tokens, in token-times
+  uint32_t piece_overhead = 350;    // the same for an item of a cut context
 };
 
 struct Plan
@@ -58,23 +65,72 @@ inline bool plan_batch( const PlanParams& p, std::vector<CtxMeta>& ctx, Plan& ou
   if ( active > p.max_items )
     return false;
 
-  uint32_t chunk = p.fixed_chunk;
-  if ( chunk == 0 ) {
-    const uint64_t blocks_target = static_cast<uint64_t>( p.sm_count ) * p.blocks_per_sm_target;
-    const uint64_t per_block = ( total * p.n_kv_heads + blocks_target - 1 ) / blocks_target;
-    chunk = std::max( round_up_u32( per_block, p.tile ), round_up_u32( p.min_chunk, p.tile ) );
-  } else {
-    chunk = round_up_u32( chunk, p.tile );
-  }
+  uint32_t max_len = 0;
+  for ( const auto& c : ctx )
+    if ( c.kv_off != kInactive )
+      max_len = std::max( max_len, c.pos + 1 );
 
-  for ( ;; ) {
-    uint64_t n_items = 0;
+  auto item_count = [&]( uint32_t chunk ) {
+    uint64_t n = 0;
     for ( const auto& c : ctx )
       if ( c.kv_off != kInactive )
-        n_items += ( static_cast<uint64_t>( c.pos ) + chunk ) / chunk; // ceil( (pos+1) / chunk )
-    if ( n_items <= p.max_items )
-      break;
-    chunk *= 2;
+        n += ( static_cast<uint64_t>( c.pos ) + chunk ) / chunk; // ceil( (pos+1) / chunk )
+    return n;
+  };
+
+  // Predicted makespan, in token-times, of the launch with split length `chunk`: items (each fanning out to
+  // n_kv_heads blocks at once) are dealt longest-first onto the block slots of the GPU.
+  const uint32_t machines = std::max<uint32_t>( 1, p.sm_count * p.blocks_per_sm / std::max<uint32_t>( 1, p.n_kv_heads ) );
+  std::vector<uint32_t> costs;
+  auto makespan = [&]( uint32_t chunk ) {
+    costs.clear();
+    for ( const auto& c : ctx ) {
+      if ( c.kv_off == kInactive )
+        continue;
+      const uint32_t len = c.pos + 1;
+      const uint32_t n = ( len + chunk - 1 ) / chunk;
+      const uint32_t step = round_up_u32( ( len + n - 1 ) / n, p.tile );
+      for ( uint32_t b = 0; b < len; b += step )
+        costs.push_back( std::min( step, len - b ) + ( n > 1 ? p.piece_overhead : p.whole_overhead ) );
+    }
+    std::sort( costs.begin(), costs.end(), std::greater<uint32_t>() );
+    if ( costs.size() <= machines )
+      return static_cast<uint64_t>( costs.front() );
+    std::priority_queue<uint64_t, std::vector<uint64_t>, std::greater<uint64_t>> load;
+    for ( uint32_t m = 0; m < machines; m++ )
+      load.push( costs[m] );
+    uint64_t longest = costs.front();
+    for ( size_t i = machines; i < costs.size(); i++ ) {
+      const uint64_t l = load.top() + costs[i];
+      load.pop();
+      load.push( l );
+      longest = std::max( longest, l );
+    }
+    return longest;
+  };
+
+  uint32_t chunk = p.fixed_chunk;
+  if ( chunk != 0 ) {
+    chunk = round_up_u32( chunk, p.tile );
+    while ( item_count( chunk ) > p.max_items )
+      chunk *= 2;
+  } else {
+    // candidates: no cut at all, then halvings down to the minimum split length
+    const uint32_t top = round_up_u32( max_len, p.tile );
+    uint64_t best = ~0ull;
+    for ( uint32_t cand = top;; cand = round_up_u32( cand / 2, p.tile ) ) {
+      if ( item_count( cand ) <= p.max_items ) {
+        const uint64_t ms = makespan( cand );
+        if ( ms < best ) {
+          best = ms;
+          chunk = cand;
+        }
+      }
+      if ( cand <= std::max( p.min_chunk, p.tile ) )
+        break;
+    }
+    if ( chunk == 0 )
+      return false;
   }
   out.chunk = chunk;
 

@@ -72,9 +72,10 @@ def _check_plan(pos, items, chunk, tile):
 def test_plan_covers_every_token_exactly_once():
     rng = np.random.default_rng(0)
     pos = rng.integers(0, 4096, size=256).astype(np.uint32)
-    items, chunk = plan_batch(pos, blocks_per_item=8)
-    _check_plan(pos, items, chunk, 64)
-    assert chunk % 64 == 0 and chunk >= 256
+    for fixed in (0, 64, 320, 1024):
+        items, chunk = plan_batch(pos, blocks_per_item=8, fixed_chunk=fixed)
+        _check_plan(pos, items, chunk, 64)
+        assert chunk % 64 == 0
 
 
 def test_plan_edge_cases():
@@ -99,7 +100,17 @@ def test_plan_edge_cases():
         plan_batch(np.zeros(32, dtype=np.uint32), blocks_per_item=1, max_items=16)
 
 
-def test_plan_scales_split_length_with_work():
-    small, c_small = plan_batch(np.full(32, 1000, dtype=np.uint32), blocks_per_item=8)
-    big, c_big = plan_batch(np.full(1024, 4000, dtype=np.uint32), blocks_per_item=8)
-    assert c_small == 256 and c_big > c_small
+def test_plan_cuts_contexts_only_when_it_pays():
+    # plenty of contexts for every block slot: cutting would only add per-item overhead
+    pos = np.random.default_rng(1).integers(15, 4096, size=256).astype(np.uint32)
+    items, chunk = plan_batch(pos, blocks_per_item=8)
+    assert len(items) == 256 and chunk >= pos.max() + 1
+    _check_plan(pos, items, chunk, 64)
+    # one long context alone on the GPU: cut down to the minimum split length
+    items, chunk = plan_batch([4095], blocks_per_item=8)
+    assert chunk == 256 and len(items) == 16
+    # a few long contexts among short ones: the long ones are cut, the plan stays valid
+    pos = np.array([4095, 4000, 100, 50, 20, 3000], dtype=np.uint32)
+    items, chunk = plan_batch(pos, blocks_per_item=8)
+    assert 256 <= chunk < 4096
+    _check_plan(pos, items, chunk, 64)
