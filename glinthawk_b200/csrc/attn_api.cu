@@ -39,7 +39,8 @@ struct DeviceGuard
   }
 };
 
-// One uploaded batch description: [CtxMeta x max_batch][WorkItem x max_items][ptr x max_batch][pos x max_batch]
+// One uploaded batch description:
+// [CtxMeta x max_batch][int32 split list x max_batch][WorkItem x max_items][ptr x max_batch][pos x max_batch]
 struct RingEntry
 {
   char* host = nullptr; // pinned
@@ -49,13 +50,12 @@ struct RingEntry
   bool used = false, multi_stream = false;
 };
 
-// Scratch of one decode launch: split partial records and arrival counters.
+// Scratch of one decode launch: the partial records of contexts cut into several work items.
 // A launch owns its set until its kernel has finished, so launches on different streams never share one.
 struct ScratchSet
 {
   float* part_o = nullptr;
   float* part_ml = nullptr;
-  int* counters = nullptr; // [max_batch * n_heads] arrival counters
   cudaEvent_t done = nullptr;
   cudaStream_t stream = nullptr;
   bool used = false;
@@ -89,11 +89,11 @@ struct gh_attn
 
   // batch descriptions
   uint32_t max_items = 0;
-  size_t off_items = 0, off_ptrs = 0, off_pos = 0, entry_bytes = 0;
+  size_t off_split = 0, off_items = 0, off_ptrs = 0, off_pos = 0, entry_bytes = 0;
   RingEntry ring[kRing];
   uint32_t ring_next = 0;
   int cur = -1; // ring entry of the batch set up last, -1 = none
-  uint32_t cur_batch = 0, cur_items = 0;
+  uint32_t cur_batch = 0, cur_items = 0, cur_split = 0;
   std::vector<int32_t> cur_slots;
   std::vector<uint32_t> cur_pos;
 
@@ -176,6 +176,10 @@ CtxMeta* entry_ctx( gh_attn* h, char* base )
   (void)h;
   return reinterpret_cast<CtxMeta*>( base );
 }
+int32_t* entry_split( gh_attn* h, char* base )
+{
+  return reinterpret_cast<int32_t*>( base + h->off_split );
+}
 WorkItem* entry_items( gh_attn* h, char* base )
 {
   return reinterpret_cast<WorkItem*>( base + h->off_items );
@@ -190,7 +194,8 @@ uint32_t* entry_pos( gh_attn* h, char* base )
 }
 
 // Plans `ctx` (kv_off and pos filled in by the caller) and uploads the description into a fresh ring entry.
-int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int* entry, uint32_t* n_items )
+int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int* entry, uint32_t* n_items,
+                     uint32_t* n_split )
 {
   PlanParams pp;
   pp.n_kv_heads = h->use_mma ? h->sh.n_kv_heads : h->sh.n_heads;
@@ -208,14 +213,16 @@ int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int
     return rc;
   RingEntry& r = h->ring[idx];
   std::memcpy( entry_ctx( h, r.host ), ctx.data(), ctx.size() * sizeof( CtxMeta ) );
+  std::memcpy( entry_split( h, r.host ), plan.split_ctx.data(), plan.split_ctx.size() * sizeof( int32_t ) );
   std::memcpy( entry_items( h, r.host ), plan.items.data(), plan.items.size() * sizeof( WorkItem ) );
-  // one copy covers the context records and the items (they are adjacent up to the items actually used)
+  // one copy covers the context records, the split list and the items (adjacent, up to the items actually used)
   const size_t bytes = h->off_items + plan.items.size() * sizeof( WorkItem );
   GH_CUDA( h, cudaMemcpyAsync( r.dev, r.host, bytes, cudaMemcpyHostToDevice, st ) );
   if ( const int rc = ring_touch( h, idx, st ); rc != GH_OK )
     return rc;
   *entry = idx;
   *n_items = static_cast<uint32_t>( plan.items.size() );
+  *n_split = static_cast<uint32_t>( plan.split_ctx.size() );
   h->stats.last_items = *n_items;
   h->stats.last_chunk = plan.chunk;
   return GH_OK;
@@ -241,7 +248,8 @@ int scratch_release( gh_attn* h, ScratchSet* s, cudaStream_t st )
   return GH_OK;
 }
 
-DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, long long layer_off, const void* q, void* xb )
+DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, uint32_t n_split, long long layer_off, const void* q,
+                        void* xb )
 {
   DecodeArgs a {};
   a.sh = h->sh;
@@ -249,6 +257,8 @@ DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, long long layer
   a.ctx = entry_ctx( h, h->ring[entry].dev );
   a.items = entry_items( h, h->ring[entry].dev );
   a.n_items = n_items;
+  a.split_ctx = entry_split( h, h->ring[entry].dev );
+  a.n_split_ctx = n_split;
   a.arena = h->pool.arena();
   a.layer_off = layer_off;
   a.q = q;
@@ -265,7 +275,6 @@ int run_decode( gh_attn* h, DecodeArgs a, bool allow_mma, cudaStream_t st )
     return rc;
   a.part_o = set->part_o;
   a.part_ml = set->part_ml;
-  a.counters = set->counters;
   cudaError_t e;
   if ( h->use_mma && allow_mma ) {
     e = launch_decode_mma( a, &h->kv_map, st, &h->stats.kernel_launches );
@@ -385,7 +394,8 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
 
   // batch-description ring
   h->max_items = cfg->max_batch + kExtraItems;
-  h->off_items = sizeof( CtxMeta ) * cfg->max_batch;
+  h->off_split = sizeof( CtxMeta ) * cfg->max_batch;
+  h->off_items = h->off_split + ( sizeof( int32_t ) * cfg->max_batch + 15 ) / 16 * 16;
   h->off_ptrs = h->off_items + sizeof( WorkItem ) * h->max_items;
   h->off_pos = h->off_ptrs + sizeof( void* ) * cfg->max_batch;
   h->entry_bytes = ( h->off_pos + sizeof( uint32_t ) * cfg->max_batch + 255 ) / 256 * 256;
@@ -401,17 +411,14 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
 
   // split partial records: one per (work item, query head)
   const size_t recs = static_cast<size_t>( h->max_items ) * sh.n_heads;
-  const size_t n_counters = static_cast<size_t>( cfg->max_batch ) * sh.n_heads;
   for ( auto& set : h->scratch ) {
     GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_o ), recs * sh.head_size * sizeof( float ) ) );
     GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_ml ), recs * 2 * sizeof( float ) ) );
-    GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.counters ), n_counters * sizeof( int ) ) );
-    GH_CUDA( h.get(), cudaMemset( set.counters, 0, n_counters * sizeof( int ) ) );
     GH_CUDA( h.get(), cudaEventCreateWithFlags( &set.done, cudaEventDisableTiming ) );
   }
   GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->dev_error ), sizeof( uint32_t ) ) );
   GH_CUDA( h.get(), cudaMemset( h->dev_error, 0, sizeof( uint32_t ) ) );
-  h->stats.scratch_bytes = kScratchSets * ( recs * ( sh.head_size + 2 ) * sizeof( float ) + n_counters * sizeof( int ) )
+  h->stats.scratch_bytes = kScratchSets * ( recs * ( sh.head_size + 2 ) * sizeof( float ) )
                            + 2 * h->entry_bytes * kRing;
 
   if ( h->use_mma ) {
@@ -468,7 +475,6 @@ int gh_attn_destroy( gh_attn_t h )
   for ( auto& set : h->scratch ) {
     cudaFree( set.part_o );
     cudaFree( set.part_ml );
-    cudaFree( set.counters );
     if ( set.done )
       cudaEventDestroy( set.done );
   }
@@ -611,12 +617,14 @@ int gh_attn_batch_begin( gh_attn_t h, uint64_t batch, const int32_t* slots, cons
   }
   h->cur = -1;
   int entry;
-  uint32_t n_items;
-  if ( const int rc = plan_and_upload( h, ctx, static_cast<cudaStream_t>( stream ), &entry, &n_items ); rc != GH_OK )
+  uint32_t n_items, n_split;
+  if ( const int rc = plan_and_upload( h, ctx, static_cast<cudaStream_t>( stream ), &entry, &n_items, &n_split );
+       rc != GH_OK )
     return rc;
   h->cur = entry;
   h->cur_batch = static_cast<uint32_t>( batch );
   h->cur_items = n_items;
+  h->cur_split = n_split;
   h->cur_slots.assign( slots, slots + batch );
   h->cur_pos.assign( pos, pos + batch );
   return GH_OK;
@@ -660,7 +668,7 @@ int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* 
   if ( const int rc = prepare_layer( h, layer ); rc != GH_OK )
     return rc;
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
-  const DecodeArgs a = decode_args( h, h->cur, h->cur_items, h->pool.layer_offset( layer ), q, xb );
+  const DecodeArgs a = decode_args( h, h->cur, h->cur_items, h->cur_split, h->pool.layer_offset( layer ), q, xb );
   if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
     return rc;
   return ring_touch( h, h->cur, st );
@@ -932,10 +940,10 @@ int gh_op_attention_fused( gh_attn_t h,
       in_arena = false; // foreign memory: the TMA descriptor does not cover it, use plain loads
   }
   int entry;
-  uint32_t n_items;
-  if ( const int rc = plan_and_upload( h, ctx, st, &entry, &n_items ); rc != GH_OK )
+  uint32_t n_items, n_split;
+  if ( const int rc = plan_and_upload( h, ctx, st, &entry, &n_items, &n_split ); rc != GH_OK )
     return rc;
-  const DecodeArgs a = decode_args( h, entry, n_items, 0, query, xb );
+  const DecodeArgs a = decode_args( h, entry, n_items, n_split, 0, query, xb );
   if ( const int rc = run_decode( h, a, in_arena, st ); rc != GH_OK )
     return rc;
   return ring_touch( h, entry, st );

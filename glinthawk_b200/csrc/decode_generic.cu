@@ -8,7 +8,7 @@
 //
 // Block = 4 warps working on one (work item, query head).  Warp w takes tokens t_begin + w, + 4, ...; its lanes
 // split the head dimension; a dot product costs one warp reduction.  The four running softmax states are
-// combined through shared memory, then finish_item() writes the result or the partial record.
+// combined through shared memory, then store_item() writes the result or the partial record.
 #include "gh_kernels.cuh"
 #include "gh_merge.cuh"
 
@@ -28,7 +28,6 @@ __global__ void __launch_bounds__( kThreads ) decode_generic_kernel( const Decod
   __shared__ float sm_fo[DPL * 32];
   __shared__ float sm_fm[1];
   __shared__ float sm_fl[1];
-  __shared__ int sm_flag;
 
   const Shape& sh = a.sh;
   const WorkItem it = a.items[blockIdx.x];
@@ -107,8 +106,8 @@ __global__ void __launch_bounds__( kThreads ) decode_generic_kernel( const Decod
   }
   __syncthreads();
 
-  finish_item<T>( sh, c, it, head, 1, sm_fo, sm_fm, sm_fl, static_cast<T*>( a.xb ), a.part_o, a.part_ml, a.counters,
-                  it.ctx * (int)sh.n_heads + head, &sm_flag, threadIdx.x, kThreads, 0 );
+  store_item<T>( sh, c, it, head, 1, sm_fo, sm_fm, sm_fl, static_cast<T*>( a.xb ), a.part_o, a.part_ml, threadIdx.x,
+                 kThreads );
 }
 
 template<typename T>
@@ -121,7 +120,10 @@ cudaError_t launch_t( const DecodeArgs& a, cudaStream_t st )
     decode_generic_kernel<T, 4><<<grid, kThreads, 0, st>>>( a );
   else
     decode_generic_kernel<T, 8><<<grid, kThreads, 0, st>>>( a );
-  return cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if ( e == cudaSuccess && a.n_split_ctx > 0 )
+    e = launch_merge_partials<T>( a.sh, a.ctx, a.split_ctx, a.n_split_ctx, a.part_o, a.part_ml, static_cast<T*>( a.xb ), st );
+  return e;
 }
 
 } // namespace
@@ -137,7 +139,7 @@ cudaError_t launch_decode_generic( const DecodeArgs& a, cudaStream_t st, uint64_
     case DT_BF16: e = launch_t<__nv_bfloat16>( a, st ); break;
     default: return cudaErrorInvalidValue;
   }
-  ( *launches )++;
+  *launches += a.n_split_ctx > 0 ? 2 : 1;
   return e;
 }
 

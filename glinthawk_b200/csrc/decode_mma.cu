@@ -1,5 +1,5 @@
 // Fused ragged-batch decode attention for 16-bit KV with head size 128: TMA-staged K/V tiles, warp-level
-// tensor-core products with fp32 accumulation, online softmax, GQA sharing, split-K with an in-kernel merge.
+// tensor-core products with fp32 accumulation, online softmax, GQA sharing, split-K with a warp-level merge inside a block and a tiny merge kernel across blocks.
 //
 // One launch per layer-step replaces, for the whole batch, the reference's per-context cuBLAS QK^T call, four
 // softmax kernels and cuBLAS AV call (src/arch/cuda/llama2/ops.cuh:272-411) and the `att` score matrix between
@@ -17,7 +17,7 @@
 //     are the M rows, padded to 16), online softmax in the log2 domain with quad shuffles, O += P V with the
 //     probabilities re-used from registers.  The warps keep independent (m, l, O) states that are combined
 //     through shared memory at the end ("warp-level merge"); contexts cut into several items are then combined by
-//     the last block to finish (gh_merge.cuh).
+//     a small second kernel (gh_merge.cuh).
 // The path is HBM-bound: 512 B of K+V per (token, kv head) against 2 x 16 x 128 x 2 tensor flops.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a sticky error word and leaves.
@@ -172,7 +172,6 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   __shared__ float sm_wl[kConsumerWarps][16];
   __shared__ float sm_m[16];
   __shared__ float sm_l[16];
-  __shared__ int sm_flag;
 
   uint8_t* ring = reinterpret_cast<uint8_t*>( ( reinterpret_cast<uintptr_t>( smem_raw ) + 1023 ) & ~uintptr_t( 1023 ) );
 
@@ -413,8 +412,8 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   }
   asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
 
-  finish_item<T>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
-                  a.counters, it.ctx * (int)sh.n_heads + kvh * group, &sm_flag, threadIdx.x, kConsumers, 1 );
+  store_item<T>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
+                 threadIdx.x, kConsumers );
 }
 
 template<typename T, typename G>
@@ -430,9 +429,11 @@ cudaError_t launch_g( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t 
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if ( a.sh.group > 8 )
-    return cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G>, a, *map );
-  return cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, false, G>, a, *map );
+  cudaError_t e = a.sh.group > 8 ? cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G>, a, *map )
+                                 : cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, false, G>, a, *map );
+  if ( e == cudaSuccess && a.n_split_ctx > 0 )
+    e = launch_merge_partials<T>( a.sh, a.ctx, a.split_ctx, a.n_split_ctx, a.part_o, a.part_ml, static_cast<T*>( a.xb ), st );
+  return e;
 }
 
 // Kernel geometries that are built.  Variant 0 is the default (fastest measured on B200: four small blocks per SM
@@ -523,7 +524,7 @@ cudaError_t launch_decode_mma( const DecodeArgs& a, const CUtensorMap* kv_map, c
     case DT_BF16: e = launch_t<__nv_bfloat16>( a, kv_map, st ); break;
     default: return cudaErrorInvalidValue;
   }
-  ( *launches )++;
+  *launches += a.n_split_ctx > 0 ? 2 : 1;
   return e;
 }
 

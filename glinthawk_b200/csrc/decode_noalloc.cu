@@ -5,7 +5,7 @@
 // treats a failed device allocation as fatal.  Code that runs inside such a process after start-up — or inside a
 // serving loop that cannot afford the device-wide synchronisation cudaMalloc and cudaFree imply — has no safe way to
 // obtain the scratch memory that split-K decode attention needs (partial results of contexts cut into several
-// work items, arrival counters, the batch description).  This entry point needs no handle and never calls
+// work items and the batch description).  This entry point needs no handle and never calls
 // cudaMalloc, cudaFree or any allocating library routine: its scratch is a fixed array that is part of the library
 // image, so every GPU that loads the library holds GH_NOALLOC_SCRATCH_BYTES of it until the process exits.
 //
@@ -17,10 +17,10 @@
 //     message from gh_decode_noalloc_error().
 //   * The first call on each device looks up the device address of the array.  Make that first call during
 //     set-up, before any stream capture begins on that device.
-//   * All calls on a device share the one array, which still holds whatever the previous call left there.  The
-//     entry point clears the arrival counters itself on `stream` before every launch; everything else is fully
-//     rewritten before it is read.  Two calls whose kernels could overlap on the GPU (different streams, no
-//     dependency between them) race on the array: serialise them.
+//   * All calls on a device share the one array, which still holds whatever the previous call left there.
+//     Nothing in it has to start at zero: the batch description is uploaded on `stream` before the launch, and
+//     every partial record that is read was written earlier in the same call.  Two calls whose kernels could
+//     overlap on the GPU (different streams, no dependency between them) race on the array: serialise them.
 #include "../../include/glinthawk_attn.h"
 
 #include <cstdio>
@@ -41,8 +41,8 @@ constexpr uint32_t kNaMaxQElems = GH_NOALLOC_MAX_Q_ELEMS;
 // Layout of the scratch array (byte offsets).
 constexpr size_t kOffCtx = 0;                                                     // CtxMeta[kNaMaxBatch]
 constexpr size_t kOffItems = kOffCtx + sizeof( CtxMeta ) * kNaMaxBatch;             // WorkItem[kNaMaxItems]
-constexpr size_t kOffCounters = kOffItems + sizeof( WorkItem ) * kNaMaxItems;       // int[kNaMaxBatch * kNaMaxHeads]
-constexpr size_t kOffPartMl = kOffCounters + sizeof( int ) * kNaMaxBatch * kNaMaxHeads; // float[kNaMaxItems*kNaMaxHeads*2]
+constexpr size_t kOffSplit = kOffItems + sizeof( WorkItem ) * kNaMaxItems;          // int32[kNaMaxBatch] cut contexts
+constexpr size_t kOffPartMl = kOffSplit + sizeof( int32_t ) * kNaMaxBatch;          // float[kNaMaxItems*kNaMaxHeads*2]
 constexpr size_t kOffPartO = 256 * 1024;                                          // float[kNaMaxItems * kNaMaxQElems]
 constexpr size_t kScratchBytes = kOffPartO + sizeof( float ) * kNaMaxItems * kNaMaxQElems;
 static_assert( kOffPartMl + sizeof( float ) * kNaMaxItems * kNaMaxHeads * 2 <= kOffPartO, "scratch layout overlaps" );
@@ -67,7 +67,7 @@ constexpr int kThreads = kWarps * 32;
 
 // Same algorithm as the CUDA-core decode kernel: 4 warps share one (work item, query head); warp w takes every 4th
 // token, lanes split the head dimension, online softmax in fp32 (log2 domain), states combined through shared
-// memory, then the result is written or a partial record is left for the last block of the context to combine.
+// memory, then the result is written or a partial record is left for the merge kernel that follows.
 template<typename T, int DPL>
 __global__ void __launch_bounds__( kThreads ) decode_noalloc_kernel( const DecodeArgs a )
 {
@@ -77,7 +77,6 @@ __global__ void __launch_bounds__( kThreads ) decode_noalloc_kernel( const Decod
   __shared__ float sm_fo[DPL * 32];
   __shared__ float sm_fm[1];
   __shared__ float sm_fl[1];
-  __shared__ int sm_flag;
 
   const Shape& sh = a.sh;
   const WorkItem it = a.items[blockIdx.x];
@@ -156,8 +155,8 @@ __global__ void __launch_bounds__( kThreads ) decode_noalloc_kernel( const Decod
   }
   __syncthreads();
 
-  finish_item<T>( sh, c, it, head, 1, sm_fo, sm_fm, sm_fl, static_cast<T*>( a.xb ), a.part_o, a.part_ml, a.counters,
-                  it.ctx * (int)sh.n_heads + head, &sm_flag, threadIdx.x, kThreads, 0 );
+  store_item<T>( sh, c, it, head, 1, sm_fo, sm_fm, sm_fl, static_cast<T*>( a.xb ), a.part_o, a.part_ml, threadIdx.x,
+                 kThreads );
 }
 
 template<typename T>
@@ -170,7 +169,10 @@ cudaError_t launch_t( const DecodeArgs& a, cudaStream_t st )
     decode_noalloc_kernel<T, 4><<<grid, kThreads, 0, st>>>( a );
   else
     decode_noalloc_kernel<T, 8><<<grid, kThreads, 0, st>>>( a );
-  return cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if ( e == cudaSuccess && a.n_split_ctx > 0 ) // combine the records of the contexts that were cut
+    e = launch_merge_partials<T>( a.sh, a.ctx, a.split_ctx, a.n_split_ctx, a.part_o, a.part_ml, static_cast<T*>( a.xb ), st );
+  return e;
 }
 
 // Device address of the scratch array on the current device, looked up once per device with that device current.
@@ -255,15 +257,19 @@ int gh_decode_noalloc( const gh_noalloc_shape* shape,
   uint64_t chunk = ( total * shape->n_heads + 148 * 16 - 1 ) / ( 148 * 16 );
   chunk = ( ( chunk < 256 ? 256 : chunk ) + 63 ) / 64 * 64;
   for ( ;; ) {
-    uint64_t n = 0;
+    uint64_t n = 0, most = 0;
     for ( uint64_t i = 0; i < batch; i++ )
-      if ( ctx[i].kv_off != kInactive )
-        n += ( (uint64_t)ctx[i].pos + chunk ) / chunk;
-    if ( n <= kNaMaxItems )
+      if ( ctx[i].kv_off != kInactive ) {
+        const uint64_t k = ( (uint64_t)ctx[i].pos + chunk ) / chunk;
+        n += k;
+        most = k > most ? k : most;
+      }
+    if ( n <= kNaMaxItems && most <= (uint64_t)kMaxSplits )
       break;
     chunk *= 2;
   }
-  uint32_t n_items = 0, records = 0;
+  int32_t split_ctx[kNaMaxBatch];
+  uint32_t n_items = 0, records = 0, n_split = 0;
   for ( uint64_t i = 0; i < batch; i++ ) {
     if ( ctx[i].kv_off == kInactive )
       continue;
@@ -280,8 +286,10 @@ int gh_decode_noalloc( const gh_noalloc_shape* shape,
     }
     ctx[i].nsplits = made;
     ctx[i].partial_base = static_cast<int32_t>( records );
-    if ( made > 1 )
+    if ( made > 1 ) {
       records += made;
+      split_ctx[n_split++] = static_cast<int32_t>( i );
+    }
   }
 
   unsigned char* scratch = nullptr;
@@ -292,9 +300,8 @@ int gh_decode_noalloc( const gh_noalloc_shape* shape,
   cudaError_t e = cudaMemcpyAsync( scratch + kOffCtx, ctx, sizeof( CtxMeta ) * batch, cudaMemcpyHostToDevice, st );
   if ( e == cudaSuccess )
     e = cudaMemcpyAsync( scratch + kOffItems, items, sizeof( WorkItem ) * n_items, cudaMemcpyHostToDevice, st );
-  // the arrival counters must start at zero; the array keeps whatever the previous call left
-  if ( e == cudaSuccess )
-    e = cudaMemsetAsync( scratch + kOffCounters, 0, sizeof( int ) * batch * shape->n_heads, st );
+  if ( e == cudaSuccess && n_split > 0 )
+    e = cudaMemcpyAsync( scratch + kOffSplit, split_ctx, sizeof( int32_t ) * n_split, cudaMemcpyHostToDevice, st );
   if ( e != cudaSuccess ) {
     (void)cudaGetLastError();
     std::snprintf( g_error, sizeof( g_error ), "uploading the batch description failed: %s", cudaGetErrorString( e ) );
@@ -318,7 +325,8 @@ int gh_decode_noalloc( const gh_noalloc_shape* shape,
   a.xb = xb;
   a.part_o = reinterpret_cast<float*>( scratch + kOffPartO );
   a.part_ml = reinterpret_cast<float*>( scratch + kOffPartMl );
-  a.counters = reinterpret_cast<int*>( scratch + kOffCounters );
+  a.split_ctx = reinterpret_cast<const int32_t*>( scratch + kOffSplit );
+  a.n_split_ctx = n_split;
 
   switch ( shape->dtype ) {
     case GH_F32: e = launch_t<float>( a, st ); break;

@@ -38,7 +38,8 @@ struct DecodeArgs
   void* xb;
   float* part_o;
   float* part_ml;
-  int* counters;
+  const int32_t* split_ctx; // batch indices of the contexts that were cut into several items
+  uint32_t n_split_ctx;
   uint32_t* dev_error;
   uint32_t sm_count;
 };

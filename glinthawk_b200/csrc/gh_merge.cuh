@@ -1,50 +1,46 @@
-// Epilogue shared by the decode kernels: write the result of a work item, or, for a context that was cut into
-// several items, store a partial record and let whichever thread block finishes last combine the records.
-// Nothing here waits on another block: the last arriver is found with one atomic increment
-// (fence -> atomic -> fence), so there is no spin loop that could hang.
+// Epilogue shared by the decode kernels, and the kernel that combines the pieces of contexts that were cut.
+//
+// A context that fits one work item is finished by the block that processed it.  A context cut into several items
+// leaves one partial record per (item, query head); a second, tiny, massively parallel kernel then combines the
+// records of each such context.  It is launched only when the batch has cut contexts, as a programmatic dependent
+// of the decode kernel, so its launch latency hides behind the decode kernel's tail.  Nothing waits on another
+// block anywhere: no flags, no counters, no spinning.
 #pragma once
 
 #include "gh_common.cuh"
 
 namespace gh {
 
+constexpr int kMaxSplits = 64; // a context is never cut into more work items than this
+
 // Partial record r = ( partial_base + split ) * n_heads + head:
 //   part_o[r][head_size]  sum_t 2^(s_t - m) * V_t   (fp32, not normalised)
 //   part_ml[r][2]         m (running maximum of the log2-scaled scores), l = sum_t 2^(s_t - m)
 //
-// `sm_o` [nrows][head_size], `sm_m` [nrows], `sm_l` [nrows] hold this block's result for query heads
-// head0 .. head0+nrows-1 in shared memory.  All `nthreads` threads of the calling group take part; `bar_id`
-// names the hardware barrier that group synchronises on (0 = the whole block).
+// `sm_o` [nrows][head_size], `sm_m` [nrows], `sm_l` [nrows] hold the calling block's result for query heads
+// head0 .. head0+nrows-1 in shared memory; threads tid, tid + nthreads, ... of the calling group take part.
 template<typename T>
-__device__ __forceinline__ void finish_item( const Shape& sh,
-                                             const CtxMeta& c,
-                                             const WorkItem& it,
-                                             const int head0,
-                                             const int nrows,
-                                             const float* sm_o,
-                                             const float* sm_m,
-                                             const float* sm_l,
-                                             T* __restrict__ xb,
-                                             float* __restrict__ part_o,
-                                             float* __restrict__ part_ml,
-                                             int* __restrict__ counters,
-                                             const int counter_idx,
-                                             int* sm_flag,
-                                             const int tid,
-                                             const int nthreads,
-                                             const int bar_id )
+__device__ __forceinline__ void store_item( const Shape& sh,
+                                            const CtxMeta& c,
+                                            const WorkItem& it,
+                                            const int head0,
+                                            const int nrows,
+                                            const float* sm_o,
+                                            const float* sm_m,
+                                            const float* sm_l,
+                                            T* __restrict__ xb,
+                                            float* __restrict__ part_o,
+                                            float* __restrict__ part_ml,
+                                            const int tid,
+                                            const int nthreads )
 {
   const int hs = sh.head_size;
-  T* out = xb + (size_t)it.ctx * sh.n_heads * hs + (size_t)head0 * hs;
-
   if ( c.nsplits == 1 ) {
-    for ( int e = tid; e < nrows * hs; e += nthreads ) {
-      const int r = e / hs;
-      out[e] = Conv<T>::from_f32( sm_o[e] / sm_l[r] );
-    }
+    T* out = xb + (size_t)it.ctx * sh.n_heads * hs + (size_t)head0 * hs;
+    for ( int e = tid; e < nrows * hs; e += nthreads )
+      out[e] = Conv<T>::from_f32( sm_o[e] / sm_l[e / hs] );
     return;
   }
-
   const size_t rec0 = ( (size_t)( c.partial_base + it.split ) * sh.n_heads + head0 );
   for ( int e = tid; e < nrows * hs; e += nthreads )
     part_o[rec0 * hs + e] = sm_o[e];
@@ -52,36 +48,85 @@ __device__ __forceinline__ void finish_item( const Shape& sh,
     part_ml[( rec0 + r ) * 2 + 0] = sm_m[r];
     part_ml[( rec0 + r ) * 2 + 1] = sm_l[r];
   }
-  __threadfence();
-  asm volatile( "bar.sync %0, %1;" ::"r"( bar_id ), "r"( nthreads ) : "memory" );
-  if ( tid == 0 ) {
-    const int prev = atomicAdd( &counters[counter_idx], 1 );
-    *sm_flag = ( prev == c.nsplits - 1 ) ? 1 : 0;
-  }
-  asm volatile( "bar.sync %0, %1;" ::"r"( bar_id ), "r"( nthreads ) : "memory" );
-  if ( *sm_flag == 0 )
-    return;
-  __threadfence();
+}
 
-  // This block arrived last: every record of the context is visible.  Combine them.
-  for ( int e = tid; e < nrows * hs; e += nthreads ) {
-    const int r = e / hs;
-    float M = -INFINITY;
-    for ( int s = 0; s < c.nsplits; s++ ) {
-      const size_t rec = (size_t)( c.partial_base + s ) * sh.n_heads + head0 + r;
-      M = fmaxf( M, __ldcg( &part_ml[rec * 2] ) );
+// Combines the partial records of cut contexts: block (x, y) = (entry of split_ctx, query head), one thread per
+// head dimension (looping when head_size > blockDim.x).  Every thread's loads are independent of each other.
+template<typename T>
+__global__ void __launch_bounds__( 128 ) merge_partials_kernel( const Shape sh,
+                                                                const CtxMeta* __restrict__ ctx,
+                                                                const int32_t* __restrict__ split_ctx,
+                                                                const float* __restrict__ part_o,
+                                                                const float* __restrict__ part_ml,
+                                                                T* __restrict__ xb )
+{
+  __shared__ float sm_w[kMaxSplits];
+  __shared__ float sm_L;
+  asm volatile( "griddepcontrol.wait;" ::: "memory" ); // the records come from the kernel before this one
+  const int ci = split_ctx[blockIdx.x];
+  const CtxMeta c = ctx[ci];
+  const int head = blockIdx.y;
+  const int ns = c.nsplits;
+  const int hs = sh.head_size;
+  const size_t rec0 = (size_t)c.partial_base * sh.n_heads + head;
+  const size_t rec_stride = sh.n_heads;
+
+  if ( threadIdx.x < 32 ) { // one warp turns the records' (m, l) into weights and the total
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int s0 = threadIdx.x, s1 = threadIdx.x + 32;
+    if ( s0 < ns ) {
+      m0 = part_ml[( rec0 + s0 * rec_stride ) * 2];
+      l0 = part_ml[( rec0 + s0 * rec_stride ) * 2 + 1];
     }
-    float L = 0.f, O = 0.f;
-    for ( int s = 0; s < c.nsplits; s++ ) {
-      const size_t rec = (size_t)( c.partial_base + s ) * sh.n_heads + head0 + r;
-      const float w = exp2f( __ldcg( &part_ml[rec * 2] ) - M );
-      L += w * __ldcg( &part_ml[rec * 2 + 1] );
-      O += w * __ldcg( &part_o[rec * hs + ( e - r * hs )] );
+    if ( s1 < ns ) {
+      m1 = part_ml[( rec0 + s1 * rec_stride ) * 2];
+      l1 = part_ml[( rec0 + s1 * rec_stride ) * 2 + 1];
     }
-    out[e] = Conv<T>::from_f32( O / L );
+    const float M = warp_max( fmaxf( m0, m1 ) );
+    const float w0 = s0 < ns ? exp2f( m0 - M ) : 0.f;
+    const float w1 = s1 < ns ? exp2f( m1 - M ) : 0.f;
+    const float L = warp_sum( w0 * l0 + w1 * l1 );
+    if ( s0 < ns )
+      sm_w[s0] = w0;
+    if ( s1 < ns )
+      sm_w[s1] = w1;
+    if ( threadIdx.x == 0 )
+      sm_L = L;
   }
-  if ( tid == 0 )
-    counters[counter_idx] = 0; // leave the counter ready for the next launch
+  __syncthreads();
+
+  T* out = xb + (size_t)ci * sh.n_heads * hs + (size_t)head * hs;
+  for ( int d = threadIdx.x; d < hs; d += blockDim.x ) {
+    const float* src = part_o + rec0 * hs + d;
+    float O = 0.f;
+#pragma unroll 8
+    for ( int sp = 0; sp < ns; sp++ )
+      O += sm_w[sp] * src[(size_t)sp * rec_stride * hs];
+    out[d] = Conv<T>::from_f32( O / sm_L );
+  }
+}
+
+// Launches merge_partials_kernel behind the kernel that wrote the records (same stream).
+template<typename T>
+inline cudaError_t launch_merge_partials( const Shape& sh,
+                                          const CtxMeta* ctx,
+                                          const int32_t* split_ctx,
+                                          uint32_t n_split_ctx,
+                                          const float* part_o,
+                                          const float* part_ml,
+                                          T* xb,
+                                          cudaStream_t st )
+{
+  cudaLaunchConfig_t cfg {};
+  cfg.gridDim = dim3( n_split_ctx, sh.n_heads );
+  cfg.blockDim = dim3( 128 );
+  cfg.stream = st;
+  cudaLaunchAttribute attr {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx( &cfg, merge_partials_kernel<T>, sh, ctx, split_ctx, part_o, part_ml, xb );
 }
 
 } // namespace gh

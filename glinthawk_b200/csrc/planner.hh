@@ -2,10 +2,10 @@
 //
 // A batch is ragged: context i attends over pos[i] + 1 tokens.  Work items are ordered longest-first so that the
 // hardware block scheduler approximates longest-processing-time-first, and long contexts are cut along the token
-// axis only as far as that pays: every extra item costs a pipeline fill and drain, and an item of a cut context
-// also costs a partial record, a fence, an atomic and a share of the final merge (measured on B200: about 2 us
-// for a whole context, about 8 us for a piece, against 23 ns per token).  The split length is therefore chosen by
-// simulating the launch for a few candidate lengths and keeping the one with the shortest makespan.  The
+// axis only as far as that pays: every extra item costs a pipeline fill and drain (about 2 us on B200, against
+// roughly 23-45 ns per token per block slot), and an item of a cut context also writes a partial record that the
+// merge kernel reads back.  The split length is therefore chosen by simulating the launch for a few candidate
+// lengths and keeping the one with the shortest makespan.  The
 // reference has no counterpart: it loops over the batch on the host and launches per context
 // (src/arch/cuda/llama2/ops.cuh:272-453).
 #pragma once
@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "gh_common.cuh"
+#include "gh_merge.cuh"
 
 namespace gh {
 
@@ -30,12 +31,13 @@ struct PlanParams
   uint32_t blocks_per_sm = 2;       // thread blocks resident per SM
   uint32_t min_chunk = 256;
   uint32_t whole_overhead = 90;     // cost of an uncut context's item beyond its tokens, in token-times
-  uint32_t piece_overhead = 350;    // the same for an item of a cut context
+  uint32_t piece_overhead = 200;    // the same for an item of a cut context (partial record + its share of the merge)
 };
 
 struct Plan
 {
   std::vector<WorkItem> items;
+  std::vector<int32_t> split_ctx; // batch indices of the contexts that were cut
   uint32_t chunk = 0;
   uint32_t partial_records = 0;
 };
@@ -58,6 +60,7 @@ inline bool plan_batch( const PlanParams& p, std::vector<CtxMeta>& ctx, Plan& ou
     }
   }
   out.items.clear();
+  out.split_ctx.clear();
   out.partial_records = 0;
   out.chunk = 0;
   if ( active == 0 )
@@ -70,11 +73,14 @@ inline bool plan_batch( const PlanParams& p, std::vector<CtxMeta>& ctx, Plan& ou
     if ( c.kv_off != kInactive )
       max_len = std::max( max_len, c.pos + 1 );
 
-  auto item_count = [&]( uint32_t chunk ) {
+  // number of work items for a split length; "too many" when a context would be cut into more than kMaxSplits
+  auto item_count = [&]( uint32_t chunk ) -> uint64_t {
     uint64_t n = 0;
     for ( const auto& c : ctx )
       if ( c.kv_off != kInactive )
         n += ( static_cast<uint64_t>( c.pos ) + chunk ) / chunk; // ceil( (pos+1) / chunk )
+    if ( ( static_cast<uint64_t>( max_len ) + chunk - 1 ) / chunk > static_cast<uint64_t>( kMaxSplits ) )
+      return ~uint64_t( 0 );
     return n;
   };
 
@@ -156,8 +162,10 @@ inline bool plan_batch( const PlanParams& p, std::vector<CtxMeta>& ctx, Plan& ou
     }
     c.nsplits = static_cast<int32_t>( made );
     c.partial_base = static_cast<int32_t>( out.partial_records );
-    if ( made > 1 )
+    if ( made > 1 ) {
       out.partial_records += made;
+      out.split_ctx.push_back( static_cast<int32_t>( i ) );
+    }
   }
 
   std::stable_sort( out.items.begin(), out.items.end(), []( const WorkItem& a, const WorkItem& b ) {

@@ -266,15 +266,16 @@ typedef struct gh_noalloc_shape
  * through any library.  It is for code that runs where device allocation is off the table: inside a worker that
  * gave all of its GPU memory to weights and context slots at start-up and treats a failed allocation as fatal, or
  * inside a serving loop that must not trigger the device-wide synchronisation an allocation implies.  The scratch it
- * needs (split partial results, arrival counters, the batch description) lives in a fixed array of
+ * needs (split partial results and the batch description) lives in a fixed array of
  * GH_NOALLOC_SCRATCH_BYTES inside the library image; every GPU the library is used on holds that array until the
  * process exits.
  *
  * `layer_bases` is a host array of device pointers to the first token row of each context's layer (null = skip),
  * `pos` a host array, q and xb device pointers, exactly as for gh_op_attention_fused; the current CUDA device is
  * used.  The first call on a device resolves the array's device address; make it before any stream capture on
- * that device.  Every call reuses the same array and clears the counters in it on `stream` before launching, so
- * calls whose kernels could run concurrently on one GPU race with each other and must be ordered by the caller.
+ * that device.  Every call reuses the same array (nothing in it needs clearing: all that a call reads it has written
+ * first), so calls whose kernels could run concurrently on one GPU race with each other and must be ordered by the
+ * caller.
  * Returns GH_ERR_INVALID when a limit above is exceeded; gh_decode_noalloc_error() then names the limit. */
 int gh_decode_noalloc( const gh_noalloc_shape* shape,
                        uint64_t batch,
