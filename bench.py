@@ -219,6 +219,7 @@ def main():
     import torch
     import torch.distributed as dist
 
+    from glinthawk_b200 import dist_util
     from glinthawk_b200.rope import rope_tables
     from glinthawk_b200.stage import AttentionStage
 
@@ -237,7 +238,7 @@ def main():
     W, K = args.warmup, args.steps
     E = min(K, 5) if args.e2e_steps < 0 else args.e2e_steps
     headroom = W + K + E + 2
-    lens0 = wl.lengths(args.seed + rank, headroom)[:batch]  # every rank draws its own contexts
+    lens0 = dist_util.weak_scaling_lengths(wl, args.seed, rank, headroom, batch)  # every rank draws its own contexts
 
     # ---- set-up (untimed): slots, cached KV, inputs ----
     t_setup = time.perf_counter()
@@ -306,10 +307,7 @@ def main():
         barrier()
     ms = ev0.elapsed_time(ev1)
     launches = stage.stats().kernel_launches - launches0
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = dist_util.max_over_ranks(ms, dev)
     ms_per_step = ms / K
     value = batch * world / (ms_per_step / 1e3)
 
@@ -357,10 +355,7 @@ def main():
         h1.record(stream)
         barrier()
         e2e_ms = h0.elapsed_time(h1)
-        if world > 1:
-            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
+        e2e_ms = dist_util.max_over_ranks(e2e_ms, dev)
         checksum = float(xb_h[-1].float().abs().mean())
         e2e = {"value": batch * world / (e2e_ms / E / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": n_layers * batch * (sh.dim + row_elems) * elem + batch * 32,

@@ -1,0 +1,49 @@
+"""Multi-process helpers: one process per GPU, contexts sharded by request, no collective on the attention path.
+
+``torch.distributed`` is used for exactly two things: a barrier around timed regions and the maximum over ranks
+of a device-measured duration.  Everything here also runs on CPU ranks (gloo), which is how it is tested.
+"""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .workload import Workload, assign_contexts
+
+
+def rank_world() -> tuple[int, int, int]:
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def max_over_ranks(value: float, device: torch.device | str = "cpu") -> float:
+    """The slowest rank decides: every multi-GPU duration is reported as the maximum over ranks."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(value: float, device: torch.device | str = "cpu") -> float:
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def weak_scaling_lengths(wl: Workload, seed: int, rank: int, headroom: int, batch: int | None = None) -> np.ndarray:
+    """Every rank draws its own contexts (per-GPU work fixed as ranks are added)."""
+    return wl.lengths(seed + rank, headroom)[: batch or wl.batch]
+
+
+def strong_scaling_lengths(wl: Workload, seed: int, rank: int, world: int, headroom: int) -> tuple[np.ndarray, np.ndarray]:
+    """One fixed set of requests divided among the ranks: returns (global indices, lengths) of this rank's share.
+    Every rank computes the same assignment from the same seed, so no communication is needed."""
+    lens = wl.lengths(seed, headroom)
+    mine = assign_contexts(lens, world)[rank]
+    return mine, lens[mine]

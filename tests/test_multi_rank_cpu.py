@@ -1,0 +1,82 @@
+"""The N > 1 path on CPU ranks (gloo, world size 2): request sharding and the rank reductions bench.py relies on."""
+import os
+import socket
+
+import numpy as np
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from glinthawk_b200 import dist_util
+from glinthawk_b200.stage import plan_batch
+from glinthawk_b200.workload import WORKLOADS, algorithmic_bytes, assign_contexts
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        wl = WORKLOADS["llama2_70b_gqa"]
+        assert dist_util.rank_world() == (rank, world, rank)
+        # weak scaling: every rank has its own 256 contexts
+        weak = dist_util.weak_scaling_lengths(wl, 20240, rank, headroom=16)
+        # strong scaling: one request set, divided without communication
+        idx, lens = dist_util.strong_scaling_lengths(wl, 20240, rank, world, headroom=16)
+        items, chunk = plan_batch(lens.astype(np.uint32), blocks_per_item=wl.shape.n_kv_heads)
+        covered = sum(int(e - b) for _, b, e, _ in items)
+        total_tokens = dist_util.sum_over_ranks(float((lens + 1).sum()))
+        total_ctx = dist_util.sum_over_ranks(float(len(idx)))
+        slowest = dist_util.max_over_ranks(10.0 + rank)  # the slowest rank decides the reported time
+        dist.barrier()
+        out.put((rank, weak[:4].tolist(), idx.tolist(), int((lens + 1).sum()), covered, total_tokens, total_ctx, slowest))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_shard_requests_without_overlap():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(out.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    wl = WORKLOADS["llama2_70b_gqa"]
+    lens = wl.lengths(20240, 16)
+    (r0, weak0, idx0, tok0, cov0, total_tokens, total_ctx, slowest), (r1, weak1, idx1, tok1, cov1, *_rest) = results
+    assert weak0 != weak1, "weak scaling: ranks draw different contexts"
+    assert sorted(idx0 + idx1) == list(range(wl.batch)) and not set(idx0) & set(idx1)
+    assert tok0 == cov0 and tok1 == cov1, "every cached token is covered by exactly one work item"
+    assert total_tokens == float((lens + 1).sum()) and total_ctx == wl.batch
+    assert abs(tok0 - tok1) <= lens.max() + 1, "token load is balanced to within one context"
+    assert slowest == 11.0
+
+
+def test_assign_contexts_balances_tokens_not_counts():
+    rng = np.random.default_rng(5)
+    lens = np.clip(np.rint(np.exp(rng.normal(np.log(1024), 0.8, 256))), 16, 4096).astype(np.int64)
+    for n in (1, 2, 4, 8):
+        parts = assign_contexts(lens, n)
+        assert sorted(np.concatenate(parts).tolist()) == list(range(256))
+        loads = [int((lens[p] + 1).sum()) for p in parts]
+        assert max(loads) - min(loads) <= lens.max() + 1
+    # degenerate: more ranks than contexts leaves some ranks empty but loses nothing
+    parts = assign_contexts([5, 9], 4)
+    assert sorted(np.concatenate(parts).tolist()) == [0, 1] and sum(len(p) == 0 for p in parts) == 2
+
+
+def test_algorithmic_bytes_formula():
+    sh = WORKLOADS["llama2_70b_gqa"].shape
+    b = algorithmic_bytes([1, 100], sh, 2)
+    row = 2 * 1024 * 2
+    assert b["kv_read"] == 101 * row and b["appended"] == 2 * row
+    assert b["decode_kernel"] == 101 * row + 2 * 2 * 8192 * 2
