@@ -38,7 +38,9 @@ template<typename T>
 __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
 {
   constexpr int N = Vec16<T>::N;
-  const int i = blockIdx.x;
+  const int i = blockIdx.x / a.tokens_per_ctx;   // context
+  const int tk = blockIdx.x - i * a.tokens_per_ctx; // token of a prefill chunk (0 for a decode step)
+  const int in_row = blockIdx.x;                  // row of q and kv_new: [context][token]
   const Shape& sh = a.sh;
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
 
@@ -53,12 +55,12 @@ __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
     const CtxMeta c = a.ctx[i];
     if ( c.kv_off == kInactive )
       return;
-    pos = c.pos;
+    pos = c.pos + tk;
     row = reinterpret_cast<T*>( a.arena + c.kv_off + a.layer_off ) + (size_t)pos * sh.row_elems;
   }
 
-  const T* src = a.kv_new != nullptr ? static_cast<const T*>( a.kv_new ) + (size_t)i * sh.row_elems : nullptr;
-  T* q = a.q != nullptr ? static_cast<T*>( a.q ) + (size_t)i * sh.n_heads * sh.head_size : nullptr;
+  const T* src = a.kv_new != nullptr ? static_cast<const T*>( a.kv_new ) + (size_t)in_row * sh.row_elems : nullptr;
+  T* q = a.q != nullptr ? static_cast<T*>( a.q ) + (size_t)in_row * sh.n_heads * sh.head_size : nullptr;
   const bool rotate = a.rope_cos != nullptr;
   const T* cs_row = rotate ? static_cast<const T*>( a.rope_cos ) + (size_t)pos * ( sh.head_size / 2 ) : nullptr;
   const T* sn_row = rotate ? static_cast<const T*>( a.rope_sin ) + (size_t)pos * ( sh.head_size / 2 ) : nullptr;
@@ -95,14 +97,18 @@ __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
 
 } // namespace
 
-cudaError_t launch_append( const AppendArgs& a, cudaStream_t st, uint64_t* launches )
+cudaError_t launch_append( const AppendArgs& args, cudaStream_t st, uint64_t* launches )
 {
-  if ( a.batch == 0 )
+  if ( args.batch == 0 )
     return cudaSuccess;
+  AppendArgs a = args;
+  if ( a.tokens_per_ctx == 0 )
+    a.tokens_per_ctx = 1;
   // chunk operations per context: K chunks (each with the group's q chunks) + V chunks
   const unsigned n16 = a.dtype == DT_F32 ? 4 : 8;
   const unsigned units = ( a.sh.kv_dim / n16 ) * ( 2 + a.sh.group );
-  const dim3 grid( a.batch, ( units + 255 ) / 256 );
+  const unsigned tokens = a.tokens_per_ctx > 0 ? a.tokens_per_ctx : 1;
+  const dim3 grid( a.batch * tokens, ( units + 255 ) / 256 );
   switch ( a.dtype ) {
     case DT_F32: append_kernel<float><<<grid, 256, 0, st>>>( a ); break;
     case DT_F16: append_kernel<__half><<<grid, 256, 0, st>>>( a ); break;

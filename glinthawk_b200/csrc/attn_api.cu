@@ -1,6 +1,7 @@
 // C ABI of the attention stage (see include/glinthawk_attn.h for the contract of every entry point).
 #include "../../include/glinthawk_attn.h"
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -679,6 +680,99 @@ int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new
   if ( const int rc = gh_attn_append( h, layer, q_inout, kv_new, stream ); rc != GH_OK )
     return rc;
   return gh_attn_decode( h, layer, q_inout, xb, stream );
+}
+
+int gh_attn_prefill_chunk( gh_attn_t h,
+                           uint32_t layer,
+                           uint64_t n_ctx,
+                           const int32_t* slots,
+                           const uint32_t* pos0,
+                           uint32_t n_tokens,
+                           void* q_inout,
+                           const void* kv_new,
+                           void* xb,
+                           void* stream )
+{
+  if ( h == nullptr || slots == nullptr || pos0 == nullptr || q_inout == nullptr || kv_new == nullptr || xb == nullptr
+       || n_ctx == 0 || n_ctx > h->cfg.max_batch || n_tokens == 0 )
+    return fail( h, GH_ERR_INVALID, "bad prefill arguments" );
+  if ( layer >= h->sh.n_layers )
+    return fail( h, GH_ERR_INVALID, "layer is not hosted" );
+  if ( h->rope_cos == nullptr )
+    return fail( h, GH_ERR_STATE, "RoPE tables not set" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+
+  // the chunk's rows must fit the slots; map pages up to the chunk's last token
+  std::vector<CtxMeta> base( n_ctx );
+  for ( uint64_t i = 0; i < n_ctx; i++ ) {
+    base[i] = CtxMeta {};
+    base[i].pos = pos0[i];
+    if ( slots[i] == -1 ) {
+      base[i].kv_off = kInactive;
+      continue;
+    }
+    if ( !h->pool.valid_slot( slots[i] ) )
+      return fail( h, GH_ERR_INVALID, "slot out of range at index " + std::to_string( i ) );
+    if ( static_cast<uint64_t>( pos0[i] ) + n_tokens > h->sh.seq_len )
+      return fail( h, GH_ERR_CAPACITY, "chunk runs past the slot capacity at index " + std::to_string( i ) );
+    base[i].kv_off = h->pool.slot_offset( slots[i] );
+    if ( const int rc = h->pool.prepare( slots[i], layer, pos0[i] + n_tokens - 1, false, h->err ); rc != GH_OK )
+      return rc;
+  }
+
+  // 1. one append launch for every (context, token) of the chunk
+  {
+    int idx;
+    if ( const int rc = ring_claim( h, &idx ); rc != GH_OK )
+      return rc;
+    RingEntry& r = h->ring[idx];
+    std::memcpy( entry_ctx( h, r.host ), base.data(), n_ctx * sizeof( CtxMeta ) );
+    GH_CUDA( h, cudaMemcpyAsync( r.dev, r.host, n_ctx * sizeof( CtxMeta ), cudaMemcpyHostToDevice, st ) );
+    AppendArgs a {};
+    a.sh = h->sh;
+    a.dtype = h->cfg.dtype;
+    a.batch = static_cast<uint32_t>( n_ctx );
+    a.tokens_per_ctx = n_tokens;
+    a.ctx = entry_ctx( h, r.dev );
+    a.arena = h->pool.arena();
+    a.layer_off = h->pool.layer_offset( layer );
+    a.q = q_inout;
+    a.kv_new = kv_new;
+    a.rope_cos = h->rope_cos;
+    a.rope_sin = h->rope_sin;
+    if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
+      return cuda_fail( h, "prefill append launch", e );
+    if ( const int rc = ring_touch( h, idx, st ); rc != GH_OK )
+      return rc;
+  }
+
+  // 2. causal attention: every (context, token) is a decode problem over its own prefix, launched in slices of at
+  //    most max_batch problems
+  const size_t q_row_bytes = static_cast<size_t>( h->sh.n_heads ) * h->sh.head_size * h->elem;
+  const uint64_t total = n_ctx * n_tokens;
+  std::vector<CtxMeta> slice;
+  for ( uint64_t v0 = 0; v0 < total; v0 += h->cfg.max_batch ) {
+    const uint64_t v1 = std::min<uint64_t>( total, v0 + h->cfg.max_batch );
+    slice.assign( v1 - v0, CtxMeta {} );
+    for ( uint64_t v = v0; v < v1; v++ ) {
+      const uint64_t i = v / n_tokens, t = v - i * n_tokens;
+      slice[v - v0] = base[i];
+      slice[v - v0].pos = base[i].pos + static_cast<uint32_t>( t );
+    }
+    int entry;
+    uint32_t n_items, n_split;
+    if ( const int rc = plan_and_upload( h, slice, st, &entry, &n_items, &n_split ); rc != GH_OK )
+      return rc;
+    const DecodeArgs a = decode_args( h, entry, n_items, n_split, h->pool.layer_offset( layer ),
+                                      static_cast<const char*>( q_inout ) + v0 * q_row_bytes,
+                                      static_cast<char*>( xb ) + v0 * q_row_bytes );
+    if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
+      return rc;
+    if ( const int rc = ring_touch( h, entry, st ); rc != GH_OK )
+      return rc;
+  }
+  return GH_OK;
 }
 
 int gh_attn_forward_attention_host( gh_attn_t h,

@@ -14,6 +14,7 @@ struct AppendArgs
   Shape sh;
   uint32_t dtype;
   uint32_t batch;
+  uint32_t tokens_per_ctx; // 1 for a decode step; T for a prefill chunk (token t of context i goes to pos + t)
   const CtxMeta* ctx;   // device, [batch]; used when token_rows == nullptr
   void* const* token_rows; // device array of row pointers (the reference's token contexts), or nullptr
   const uint32_t* pos;  // device, [batch]; used together with token_rows

@@ -176,6 +176,13 @@ class AttentionStage:
     def step(self, layer: int, q_inout: torch.Tensor, kv_new: torch.Tensor, xb: torch.Tensor, stream=None) -> None:
         self._ck(lib.gh_attn_step(self._h, layer, _ptr(q_inout), _ptr(kv_new), _ptr(xb), _stream(stream)))
 
+    def prefill_chunk(self, layer: int, slots, pos0, n_tokens: int, q_inout, kv_new, xb, stream=None) -> None:
+        """n_tokens prompt tokens per context in one call; equals n_tokens consecutive step() calls."""
+        slots = np.ascontiguousarray(slots, dtype=np.int32)
+        pos0 = np.ascontiguousarray(pos0, dtype=np.uint32)
+        self._ck(lib.gh_attn_prefill_chunk(self._h, layer, len(slots), _ptr(slots), _ptr(pos0), n_tokens,
+                                           _ptr(q_inout), _ptr(kv_new), _ptr(xb), _stream(stream)))
+
     def forward_attention_host(self, layer: int, io_dtype, q_host, kv_host, xb_host, stream=None) -> None:
         self._ck(lib.gh_attn_forward_attention_host(self._h, layer, dtype_code(io_dtype), _ptr(q_host), _ptr(kv_host),
                                                     _ptr(xb_host), _stream(stream)))

@@ -169,6 +169,23 @@ int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* 
  * (src/models/llama2/model.hh:345-387). */
 int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new, void* xb, void* stream );
 
+/* A chunk of n_tokens consecutive prompt tokens per context in one call: token t of context i is appended at
+ * position pos0[i] + t and attends causally over positions 0 .. pos0[i] + t.  q_inout and xb are
+ * [n_ctx][n_tokens][n_heads*head_size], kv_new is [n_ctx][n_tokens][2*kv_dim] (device pointers); slots and pos0 are
+ * host arrays.  The result equals n_tokens consecutive gh_attn_step calls.  The reference has no multi-token
+ * operation: it feeds prompts one token per forward pass (src/worker/worker.hh:789-796,
+ * src/frontend/infer.cc:124-126).  Does not disturb the batch set up by gh_attn_batch_begin. */
+int gh_attn_prefill_chunk( gh_attn_t h,
+                           uint32_t layer,
+                           uint64_t n_ctx,
+                           const int32_t* slots,
+                           const uint32_t* pos0,
+                           uint32_t n_tokens,
+                           void* q_inout,
+                           const void* kv_new,
+                           void* xb,
+                           void* stream );
+
 /* Llama2::forward_attention for one layer with HOST buffers (src/models/llama2/model.hh:630-722): q_host
  * [batch][n_heads*head_size] and kv_host [batch][2*kv_dim] of dtype `io_dtype` are converted and copied in
  * (convert_and_copy, src/arch/cuda/llama2/ops.cuh:455-492), the stage runs, and xb is converted and copied

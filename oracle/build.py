@@ -117,6 +117,29 @@ def build_ref(force: bool = False) -> list[Path]:
     return list(outs.values())
 
 
+def build_adapter_check(force: bool = False) -> Path | None:
+    """Compiles oracle/adapter_check.cc — the C++ adapter header instantiated with the reference's own view types
+    and concepts — against the reference tree and links it with the attention library.  The binary travels in
+    oracle/_ref like the reference libraries; a GPU test runs it."""
+    out = REF_OUT / "adapter_check"
+    src = HERE / "adapter_check.cc"
+    adapter = HERE.parent / "glinthawk_b200" / "cpp" / "glinthawk_b200_ops.hh"
+    lib_dir = HERE.parent / "glinthawk_b200"
+    if not ref_available() or not (lib_dir / "libglinthawk_attn.so").exists():
+        return out if out.exists() else None
+    if not force and _newer(out, src, adapter, HERE.parent / "include" / "glinthawk_attn.h"):
+        return out
+    REF_OUT.mkdir(exist_ok=True)
+    cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    cmd = ["g++", "-std=c++20", "-O1", "-DNDEBUG", "-DTARGET_PLATFORM_AMD64", "-fopenmp", "-w",
+           f"-I{HERE / 'shim'}", f"-I{REF_ROOT / 'src'}", f"-I{HERE.parent / 'include'}", f"-I{adapter.parent}",
+           f"-I{cuda / 'include'}", str(src), str(REF_ROOT / "src" / "util" / "demangle.cc"), "-o", str(out),
+           f"-L{lib_dir}", "-lglinthawk_attn", f"-L{cuda / 'lib64'}", "-lcudart",
+           "-Wl,-rpath,$ORIGIN/../../glinthawk_b200", f"-Wl,-rpath,{cuda / 'lib64'}"]
+    subprocess.run(cmd, check=True)
+    return out
+
+
 def load_oracle() -> ctypes.CDLL:
     return ctypes.CDLL(str(build_oracle()))
 
@@ -142,3 +165,4 @@ def load_ref() -> ctypes.CDLL | None:
 if __name__ == "__main__":
     print("oracle:", build_oracle(force=True))
     print("reference:", [str(p) for p in build_ref(force=True)] or "reference tree absent, nothing built")
+    print("adapter check:", build_adapter_check(force=True))

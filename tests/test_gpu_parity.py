@@ -225,3 +225,53 @@ def test_layers_in_flight_on_several_streams(oracle):
                                        atol=cases.TOL_XB[cases.F16], err_msg=f"layer {l}, repetition {rep}")
     assert st.stats().device_error == 0
     st.close()
+
+
+@pytest.mark.parametrize("shape_name,dtype", [("mini_g4", cases.BF16), ("mini_g8", cases.F16), ("tiny15m", cases.F32)])
+def test_prefill_chunk_equals_token_by_token_reference_steps(oracle, shape_name, dtype):
+    """A multi-token prompt chunk in one call.  The reference has no such operation — it feeds prompts one token
+    per forward pass — so the oracle is n_tokens consecutive reference layer-steps on a growing cache."""
+    sh = cases.SHAPES[shape_name]
+    T, pos0 = 37, [0, 5, 100]  # fresh slot, short prefix, longer prefix
+    rng = np.random.default_rng(321)
+    B = len(pos0)
+    base = cases.make_case("pf", shape_name, dtype, [p + T - 1 for p in pos0], seed=9)
+    q = cases.store(rng.standard_normal((B, T, sh.dim), dtype=np.float32), dtype)
+    kv = cases.store(rng.standard_normal((B, T, 2 * sh.kv_dim), dtype=np.float32), dtype)
+
+    # oracle: token by token
+    cache = [c.copy() for c in base.cache]
+    want_xb = np.zeros_like(q)
+    want_q = np.zeros_like(q)
+    for t in range(T):
+        step = cases.Case("pf", sh, dtype, np.array([p + t for p in pos0], dtype=np.uint32), base.active,
+                          [c[: p + t + 1] for c, p in zip(cache, pos0)], np.ascontiguousarray(q[:, t]),
+                          np.ascontiguousarray(kv[:, t]), base.fcr, base.fci)
+        res = oracle.layer_step(step)
+        for i, p in enumerate(pos0):
+            cache[i][p + t] = res.rows[i]
+        want_xb[:, t], want_q[:, t] = res.xb, res.q
+
+    st = gpu_util.make_stage(base, layers=2, paged=True)
+    slots = st.get_contexts(np.arange(1, B + 1, dtype=np.uint32))
+    for i, p in enumerate(pos0):
+        st.prepare(int(slots[i]), 1, max(p, 1) - 1, False)
+        if p > 0:
+            st.layer_view(int(slots[i]), 1, p).copy_(gpu_util.to_dev(base.cache[i][:p], dtype))
+    q_d, kv_d = gpu_util.to_dev(q, dtype), gpu_util.to_dev(kv, dtype)
+    xb_d = torch.zeros_like(q_d)
+    st.prefill_chunk(1, slots, pos0, T, q_d, kv_d, xb_d)
+    torch.cuda.synchronize()
+    assert st.stats().device_error == 0
+    tol = cases.TOL_XB[dtype]
+    np.testing.assert_allclose(cases.as_f32(gpu_util.to_host(xb_d, dtype), dtype), cases.as_f32(want_xb, dtype), rtol=0,
+                               atol=tol)
+    np.testing.assert_allclose(cases.as_f32(gpu_util.to_host(q_d, dtype), dtype), cases.as_f32(want_q, dtype),
+                               rtol=cases.TOL_K_REL, atol=1e-3 if dtype != cases.BF16 else 8e-3)
+    for i, p in enumerate(pos0):
+        got = gpu_util.to_host(st.layer_view(int(slots[i]), 1, p + T), dtype)
+        kvd = sh.kv_dim
+        assert np.array_equal(got[p:, kvd:].view(np.uint8), cache[i][p:p + T, kvd:].view(np.uint8)), "V rows bit-exact"
+        np.testing.assert_allclose(cases.as_f32(got[p:, :kvd], dtype), cases.as_f32(cache[i][p:p + T, :kvd], dtype),
+                                   rtol=cases.TOL_K_REL, atol=1e-3 if dtype != cases.BF16 else 8e-3)
+    st.close()
