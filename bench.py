@@ -264,6 +264,18 @@ def main():
     pos = lens0.astype(np.uint32).copy()  # position of the token appended next = tokens cached so far
     stream = torch.cuda.current_stream()
 
+    import ctypes as C
+
+    from glinthawk_b200._lib import lib as ghlib
+
+    # raw pointers per layer, computed once: the per-layer host work inside the timed loop is one C call
+    esz = q_all.element_size()
+    q_ptr = [C.c_void_p(q_all.data_ptr() + l * batch * sh.dim * esz) for l in range(n_layers)]
+    kv_ptr = [C.c_void_p(kv_all.data_ptr() + l * batch * row_elems * esz) for l in range(n_layers)]
+    xb_ptr = [C.c_void_p(xb_all.data_ptr() + l * batch * sh.dim * esz) for l in range(n_layers)]
+    st_ptr = C.c_void_p(stream.cuda_stream)
+    handle = stage._h
+
     def device_step(record=None):
         """One token for every context through all layers.  With `record`, every 8th layer's decode launch is
         bracketed by events (the append and decode launches of the other layers stay back to back, which is what
@@ -277,8 +289,8 @@ def main():
                 stage.decode(l, q_all[l], xb_all[l])
                 e1.record(stream)
                 record.append((e0, e1))
-            else:
-                stage.step(l, q_all[l], kv_all[l], xb_all[l])
+            elif ghlib.gh_attn_step(handle, l, q_ptr[l], kv_ptr[l], xb_ptr[l], st_ptr) != 0:
+                raise RuntimeError(ghlib.gh_attn_last_error(handle).decode())
         pos[:] += 1
 
     def barrier():

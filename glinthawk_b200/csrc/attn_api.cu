@@ -47,8 +47,9 @@ struct RingEntry
   char* host = nullptr; // pinned
   char* dev = nullptr;
   cudaEvent_t last_use = nullptr;
-  cudaStream_t last_stream = nullptr;
-  bool used = false, multi_stream = false;
+  cudaStream_t streams[4] = {}; // streams that have work referring to this entry
+  int n_streams = 0;
+  bool many_streams = false;
 };
 
 // Scratch of one decode launch: the partial records of contexts cut into several work items.
@@ -142,33 +143,50 @@ bool dtype_ok( uint32_t dt )
   return dt == GH_F16 || dt == GH_F32 || dt == GH_BF16;
 }
 
-// Claims the next batch-description buffer, waiting (on the host) only if the device still reads it.
+// Waits (on the host) until everything submitted so far to `st` has finished.  No event is recorded while work is
+// being submitted; the wait is paid only when a buffer is about to be recycled, many launches later.
+int drain_stream( gh_attn* h, cudaEvent_t ev, cudaStream_t st )
+{
+  cudaError_t e = cudaEventRecord( ev, st );
+  if ( e == cudaSuccess )
+    e = cudaEventSynchronize( ev );
+  if ( e != cudaSuccess ) { // e.g. the caller destroyed the stream in the meantime
+    (void)cudaGetLastError();
+    GH_CUDA( h, cudaDeviceSynchronize() );
+  }
+  return GH_OK;
+}
+
+// Claims the next batch-description buffer, waiting (on the host) only if the device may still read it.
 int ring_claim( gh_attn* h, int* idx )
 {
   const uint32_t k = h->ring_next;
   h->ring_next = ( k + 1 ) % kRing;
   RingEntry& r = h->ring[k];
-  if ( r.used ) {
-    if ( r.multi_stream )
-      GH_CUDA( h, cudaDeviceSynchronize() );
-    else
-      GH_CUDA( h, cudaEventSynchronize( r.last_use ) );
+  if ( r.many_streams ) {
+    GH_CUDA( h, cudaDeviceSynchronize() );
+  } else {
+    for ( int i = 0; i < r.n_streams; i++ )
+      if ( const int rc = drain_stream( h, r.last_use, r.streams[i] ); rc != GH_OK )
+        return rc;
   }
-  r.used = false;
-  r.multi_stream = false;
-  r.last_stream = nullptr;
+  r.n_streams = 0;
+  r.many_streams = false;
   *idx = static_cast<int>( k );
   return GH_OK;
 }
 
+// Notes that work referring to ring entry `idx` was submitted to `st` (no CUDA call).
 int ring_touch( gh_attn* h, int idx, cudaStream_t st )
 {
   RingEntry& r = h->ring[idx];
-  if ( r.used && r.last_stream != st )
-    r.multi_stream = true;
-  r.used = true;
-  r.last_stream = st;
-  GH_CUDA( h, cudaEventRecord( r.last_use, st ) );
+  for ( int i = 0; i < r.n_streams; i++ )
+    if ( r.streams[i] == st )
+      return GH_OK;
+  if ( r.n_streams < 4 )
+    r.streams[r.n_streams++] = st;
+  else
+    r.many_streams = true;
   return GH_OK;
 }
 
@@ -235,17 +253,25 @@ int scratch_claim( gh_attn* h, cudaStream_t st, ScratchSet** out )
 {
   ScratchSet& s = h->scratch[h->scratch_next];
   h->scratch_next = ( h->scratch_next + 1 ) % kScratchSets;
-  if ( s.used && s.stream != st )
-    GH_CUDA( h, cudaStreamWaitEvent( st, s.done, 0 ) );
+  if ( s.used && s.stream != st ) {
+    // everything submitted to the set's previous stream so far includes its last launch
+    cudaError_t e = cudaEventRecord( s.done, s.stream );
+    if ( e == cudaSuccess )
+      e = cudaStreamWaitEvent( st, s.done, 0 );
+    if ( e != cudaSuccess ) {
+      (void)cudaGetLastError();
+      GH_CUDA( h, cudaDeviceSynchronize() );
+    }
+  }
   *out = &s;
   return GH_OK;
 }
 
 int scratch_release( gh_attn* h, ScratchSet* s, cudaStream_t st )
 {
+  (void)h;
   s->used = true;
   s->stream = st;
-  GH_CUDA( h, cudaEventRecord( s->done, st ) );
   return GH_OK;
 }
 
