@@ -61,6 +61,7 @@ struct ScratchSet
   cudaEvent_t done = nullptr;
   cudaStream_t stream = nullptr;
   bool used = false;
+  bool done_recorded = false; // `done` marks exactly the end of the set's last launch
 };
 
 struct HostStage
@@ -102,6 +103,7 @@ struct gh_attn
   // split partials
   ScratchSet scratch[kScratchSets];
   uint32_t scratch_next = 0;
+  bool several_streams = false; // decode launches have been seen on more than one stream
   uint32_t* dev_error = nullptr;
 
   bool use_mma = false;
@@ -254,8 +256,10 @@ int scratch_claim( gh_attn* h, cudaStream_t st, ScratchSet** out )
   ScratchSet& s = h->scratch[h->scratch_next];
   h->scratch_next = ( h->scratch_next + 1 ) % kScratchSets;
   if ( s.used && s.stream != st ) {
-    // everything submitted to the set's previous stream so far includes its last launch
-    cudaError_t e = cudaEventRecord( s.done, s.stream );
+    // From now on the end of every launch is marked, so that streams wait for exactly what they must.  This
+    // first time, everything submitted to the set's previous stream so far stands in for its last launch.
+    h->several_streams = true;
+    cudaError_t e = s.done_recorded ? cudaSuccess : cudaEventRecord( s.done, s.stream );
     if ( e == cudaSuccess )
       e = cudaStreamWaitEvent( st, s.done, 0 );
     if ( e != cudaSuccess ) {
@@ -269,9 +273,13 @@ int scratch_claim( gh_attn* h, cudaStream_t st, ScratchSet** out )
 
 int scratch_release( gh_attn* h, ScratchSet* s, cudaStream_t st )
 {
-  (void)h;
   s->used = true;
   s->stream = st;
+  s->done_recorded = false;
+  if ( h->several_streams ) { // single-stream callers never pay for this
+    GH_CUDA( h, cudaEventRecord( s->done, st ) );
+    s->done_recorded = true;
+  }
   return GH_OK;
 }
 
