@@ -48,6 +48,7 @@ _PROTOS = {
     "gh_attn_last_error": (C.c_char_p, [_P]),
     "gh_status_string": (C.c_char_p, [C.c_int]),
     "gh_attn_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
+    "gh_attn_synchronize": (C.c_int, [_P, _P]),
     "gh_attn_set_rope_tables": (C.c_int, [_P, _P, _P]),
     "gh_slot_acquire": (C.c_int, [_P, _U32, C.POINTER(_I32)]),
     "gh_slots_acquire_batch": (C.c_int, [_P, _U64, _P, _P]),

@@ -176,6 +176,7 @@ class LlamaOperations : public Base
 private:
   gh_attn_t h_;
   bool fused_ { true };
+  bool blocking_ { false };
   mutable const DType* pending_query_ { nullptr };
   mutable std::vector<void*> ptrs_;
 
@@ -208,6 +209,19 @@ public:
   // false = run the three attention operations one by one and materialise `att`, exactly like the reference
   void set_fused( const bool fused ) { fused_ = fused; }
 
+  // true = every attention-stage operation returns only after the GPU has finished it.  Needed when `Base`'s
+  // operations run on the host (on managed or mapped memory) and therefore are not ordered by the CUDA stream.
+  void set_blocking( const bool blocking ) { blocking_ = blocking; }
+
+private:
+  void done() const
+  {
+    if ( blocking_ )
+      GH_B200_CHECK( h_, gh_attn_synchronize( h_, nullptr ) );
+  }
+
+public:
+
   void attention_0_gemm( const DType* query,
                          const typename ContextType::LayerContextType layer_contexts[],
                          DType* att,
@@ -220,6 +234,7 @@ public:
     }
     GH_B200_CHECK( h_, gh_op_attention_0_gemm( h_, query, pointers( layer_contexts, batch_size, false ), att,
                                                batch_size, token_positions, nullptr ) );
+    done();
   }
 
   void attention_softmax( DType* att, const uint32_t* token_positions, DType* temp_buffer, const uint64_t batch_size )
@@ -228,6 +243,7 @@ public:
     if ( fused_ )
       return;
     GH_B200_CHECK( h_, gh_op_attention_softmax( h_, att, token_positions, temp_buffer, batch_size, nullptr ) );
+    done();
   }
 
   void attention_2_gemm( const DType* att,
@@ -241,10 +257,12 @@ public:
       GH_B200_CHECK( h_, gh_op_attention_fused( h_, pending_query_, pointers( layer_contexts, batch_size, false ), xb,
                                                 batch_size, token_positions, nullptr ) );
       pending_query_ = nullptr;
+      done();
       return;
     }
     GH_B200_CHECK( h_, gh_op_attention_2_gemm( h_, att, pointers( layer_contexts, batch_size, false ), xb, batch_size,
                                                token_positions, nullptr ) );
+    done();
   }
 
   void apply_rope( const uint64_t curr_batch_size,
@@ -256,6 +274,7 @@ public:
   {
     GH_B200_CHECK( h_, gh_op_apply_rope( h_, curr_batch_size, token_positions, freq_cis_real, freq_cis_imag, state_q,
                                          pointers( token_contexts, curr_batch_size, true ), nullptr ) );
+    done();
   }
 
   void copy_kv_cache( typename ContextType::TokenContextType token_contexts[],
@@ -264,6 +283,7 @@ public:
   {
     GH_B200_CHECK( h_, gh_op_copy_kv_cache( h_, pointers( token_contexts, batch_size, true ), state_kv, batch_size,
                                             nullptr ) );
+    done();
   }
 
   template<typename DTypeDst, typename DTypeSrc>

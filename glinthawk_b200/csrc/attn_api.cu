@@ -541,6 +541,15 @@ int gh_attn_get_stats( gh_attn_t h, gh_attn_stats* out )
   return GH_OK;
 }
 
+int gh_attn_synchronize( gh_attn_t h, void* stream )
+{
+  if ( h == nullptr )
+    return GH_ERR_INVALID;
+  DeviceGuard guard( h->device );
+  GH_CUDA( h, cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) ) );
+  return GH_OK;
+}
+
 int gh_attn_set_rope_tables( gh_attn_t h, const void* freq_cis_real, const void* freq_cis_imag )
 {
   if ( h == nullptr || freq_cis_real == nullptr || freq_cis_imag == nullptr )

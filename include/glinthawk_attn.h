@@ -117,6 +117,11 @@ const char* gh_attn_last_error( gh_attn_t h );
 const char* gh_status_string( int status );
 int gh_attn_get_stats( gh_attn_t h, gh_attn_stats* out );
 
+/* Blocks the host until everything submitted to `stream` has finished (cudaStreamSynchronize).  For callers whose
+ * other operations run on the host and are therefore not ordered by the stream; the reference's CUDA backend gets
+ * the same effect from its blocking cudaMemcpy calls (src/arch/cuda/llama2/ops.cuh:455-492). */
+int gh_attn_synchronize( gh_attn_t h, void* stream );
+
 /* RoPE tables [seq_len][head_size/2] of the handle's dtype, device pointers, not owned.  They are what
  * `apply_rope` receives as freq_cis_real / freq_cis_imag (src/models/llama2/base.hh:110-112). */
 int gh_attn_set_rope_tables( gh_attn_t h, const void* freq_cis_real, const void* freq_cis_imag );

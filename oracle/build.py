@@ -66,21 +66,50 @@ def build_oracle(force: bool = False) -> Path:
     return ORACLE_SO
 
 
-def _patched_include_dir(scratch: Path) -> Path:
-    """A scratch include root holding the one header GCC 13 needs adjusted; everything else resolves
-    to the reference tree through the second -I."""
-    src = REF_ROOT / "src" / "arch" / "amd64" / "llama2" / "ops.hh"
-    text = src.read_text()
-    patched, n = re.subn(re.escape(_TEMPLATE_HEAD) + r"\n(?!requires)",
-                         _TEMPLATE_HEAD + "\nrequires ModelConfig<Config>\n", text)
-    # the class declaration itself already carries the clause (the look-ahead skips it)
+_MODEL_HEAD = "template<typename Config, typename DType, typename LlamaOperations, typename Context>"
+_MODEL_CLAUSE = ("requires ModelConfig<Config> && LlamaOperationsConcept<LlamaOperations, DType, ConfigRuntime<Config>>\n"
+                 "         && ContextConcept<Context, DType>")
+
+
+def _mirror(scratch: Path, rel_dir: str, patched: dict[str, str]) -> None:
+    """scratch/<rel_dir> = the reference directory with the given files replaced by adjusted copies; every other
+    entry is a symlink, because quoted includes are resolved relative to the including file first."""
+    src_dir, dst_dir = REF_ROOT / "src" / rel_dir, scratch / rel_dir
+    dst_dir.mkdir(parents=True, exist_ok=True)
+    for entry in src_dir.iterdir():
+        target = dst_dir / entry.name
+        if entry.name in patched:
+            target.write_text(patched[entry.name])
+        elif not target.exists():
+            os.symlink(entry, target)
+
+
+def _patched_include_dir(scratch: Path, with_model: bool = False) -> Path:
+    """A scratch include root holding the headers GCC 13 needs adjusted; everything else resolves to the
+    reference tree.  The only edit is the insertion of the class's own `requires` clause after the template head
+    of out-of-class member definitions (GCC 13: "redeclaration with different constraints")."""
+    ops = (REF_ROOT / "src" / "arch" / "amd64" / "llama2" / "ops.hh").read_text()
+    ops, n = re.subn(re.escape(_TEMPLATE_HEAD) + r"\n(?!requires)", _TEMPLATE_HEAD + "\nrequires ModelConfig<Config>\n", ops)
     if n < 6:
-        raise RuntimeError(f"expected at least 6 out-of-class definitions to adjust, found {n}")
-    dst_dir = scratch / "arch" / "amd64" / "llama2"
-    dst_dir.mkdir(parents=True)
-    (dst_dir / "ops.hh").write_text(patched)
-    # "../common/ops.hh" is resolved relative to the including file first
-    os.symlink(REF_ROOT / "src" / "arch" / "amd64" / "common", scratch / "arch" / "amd64" / "common")
+        raise RuntimeError(f"expected at least 6 out-of-class definitions to adjust in ops.hh, found {n}")
+    _mirror(scratch, "arch/amd64/llama2", {"ops.hh": ops})
+    os.symlink(REF_ROOT / "src" / "arch" / "amd64" / "common", scratch / "arch" / "amd64" / "common")  # "../common/ops.hh"
+    if with_model:
+        model = (REF_ROOT / "src" / "models" / "llama2" / "model.hh").read_text()
+        # member definitions only: the head is followed by the member template's own head or by `void Llama2<`
+        model, n = re.subn(re.escape(_MODEL_HEAD) + r"\n(?=template<StateConcept StateType>|void Llama2<)",
+                           _MODEL_HEAD + "\n" + _MODEL_CLAUSE + "\n", model)
+        if n < 13:
+            raise RuntimeError(f"expected 13 member definitions to adjust in model.hh, found {n}")
+        _mirror(scratch, "models/llama2", {"model.hh": model})
+        state = (REF_ROOT / "src" / "models" / "common" / "state.hh").read_text()
+        head, marker, impl = state.partition("/*** Implementations ***/")
+        impl, n = re.subn(r"template<typename Config>\n(?!requires)",
+                          "template<typename Config>\nrequires llama2::ModelConfig<Config>\n", impl)
+        if not marker or n < 21:
+            raise RuntimeError(f"expected 21 member definitions to adjust in state.hh, found {n}")
+        _mirror(scratch, "models/common", {"state.hh": head + marker + impl})
+        _mirror(scratch, "models", {})  # "../types.hh"
     return scratch
 
 
@@ -140,6 +169,37 @@ def build_adapter_check(force: bool = False) -> Path | None:
     return out
 
 
+def build_model_harness(force: bool = False) -> Path | None:
+    """Compiles oracle/model_harness.cc: the reference's own Llama2 model class, once with its amd64 backend and
+    once with the adapter (attention stage on the GPU through the C ABI).  Travels in oracle/_ref."""
+    out = REF_OUT / "model_harness"
+    src = HERE / "model_harness.cc"
+    adapter = HERE.parent / "glinthawk_b200" / "cpp" / "glinthawk_b200_ops.hh"
+    lib_dir = HERE.parent / "glinthawk_b200"
+    if not ref_available() or not (lib_dir / "libglinthawk_attn.so").exists():
+        return out if out.exists() else None
+    if not force and _newer(out, src, adapter, HERE.parent / "include" / "glinthawk_attn.h"):
+        return out
+    REF_OUT.mkdir(exist_ok=True)
+    cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    scratch = Path(tempfile.mkdtemp(prefix="ghref_model_"))
+    try:
+        inc = _patched_include_dir(scratch, with_model=True)
+        ref_src = REF_ROOT / "src"
+        units = [ref_src / "util" / n for n in ("demangle.cc", "ring_buffer.cc", "file_descriptor.cc", "digest.cc")]
+        units.append(ref_src / "models" / "types.cc")
+        cmd = ["g++", "-std=c++20", "-O3", "-DNDEBUG", "-ffast-math", "-fsingle-precision-constant", "-march=x86-64-v3",
+               "-fopenmp", "-DTARGET_PLATFORM_AMD64", "-w",
+               f"-I{HERE / 'shim'}", f"-I{inc}", f"-I{ref_src}", f"-I{HERE.parent / 'include'}", f"-I{adapter.parent}",
+               f"-I{cuda / 'include'}", str(src), *map(str, units), "-o", str(out),
+               f"-L{lib_dir}", "-lglinthawk_attn", f"-L{cuda / 'lib64'}", "-lcudart", "-lcrypto", "-lpthread",
+               "-Wl,-rpath,$ORIGIN/../../glinthawk_b200", f"-Wl,-rpath,{cuda / 'lib64'}"]
+        subprocess.run(cmd, check=True)
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)
+    return out
+
+
 def load_oracle() -> ctypes.CDLL:
     return ctypes.CDLL(str(build_oracle()))
 
@@ -166,3 +226,4 @@ if __name__ == "__main__":
     print("oracle:", build_oracle(force=True))
     print("reference:", [str(p) for p in build_ref(force=True)] or "reference tree absent, nothing built")
     print("adapter check:", build_adapter_check(force=True))
+    print("model harness:", build_model_harness(force=True))
