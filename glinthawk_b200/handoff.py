@@ -59,33 +59,37 @@ def wait_all(reqs) -> None:
 
 
 def run_attention_rank(link: AttentionLink, n_layers: int, step_fn) -> None:
-    """Attention side of one decode step: for every layer receive (q, kv_new), run ``step_fn(layer, q, kv_new) -> xb``
-    and send xb back.  The next layer's inputs are received while the current layer computes."""
-    q, kv, reqs = link.recv_inputs()
-    sends = []
-    for layer in range(n_layers):
-        wait_all(reqs)
-        cur_q, cur_kv = q, kv
-        if layer + 1 < n_layers:
-            q, kv, reqs = link.recv_inputs()
-        xb = step_fn(layer, cur_q, cur_kv)
-        sends.append((xb, link.send_output(xb)))
-    for _, r in sends:
-        wait_all(r)
+    """Attention side of one decode step.  Both ranks walk through the same sequence of transfer groups — group g
+    carries layer g's inputs one way and layer g-1's output the other way — because NCCL matches point-to-point
+    operations between two ranks strictly in the order they were issued."""
+    xb = None
+    q = kv = None
+    for g in range(n_layers + 1):
+        ops, nq, nkv = [], None, None
+        if g < n_layers:
+            nq, nkv = link._buf(link.s.dim), link._buf(link.s.row_elems)
+            ops += [dist.P2POp(dist.irecv, nq, link.peer), dist.P2POp(dist.irecv, nkv, link.peer)]
+        if g >= 1:
+            xb = step_fn(g - 1, q, kv)  # enqueued on the current stream; the send below is ordered after it
+            ops.append(dist.P2POp(dist.isend, xb, link.peer))
+        wait_all(dist.batch_isend_irecv(ops))
+        q, kv = nq, nkv
 
 
 def run_dense_rank(link: AttentionLink, n_layers: int, make_inputs, consume_output) -> None:
-    """Dense-stage side: ``make_inputs(layer) -> (q, kv_new)``, ``consume_output(layer, xb)``."""
-    pending = []
-    for layer in range(n_layers):
-        q, kv = make_inputs(layer)
-        sends = link.send_inputs(q, kv)
-        xb, recv = link.recv_output()
-        pending.append((layer, xb, recv, sends, q, kv))
-    for layer, xb, recv, sends, _q, _kv in pending:
-        wait_all(recv)
-        wait_all(sends)
-        consume_output(layer, xb)
+    """Dense-stage side: ``make_inputs(layer) -> (q, kv_new)``, ``consume_output(layer, xb)``; mirrors
+    run_attention_rank group by group."""
+    for g in range(n_layers + 1):
+        ops, xb, keep = [], None, None
+        if g < n_layers:
+            keep = make_inputs(g)
+            ops += [dist.P2POp(dist.isend, keep[0], link.peer), dist.P2POp(dist.isend, keep[1], link.peer)]
+        if g >= 1:
+            xb = link._buf(link.s.dim)
+            ops.append(dist.P2POp(dist.irecv, xb, link.peer))
+        wait_all(dist.batch_isend_irecv(ops))
+        if g >= 1:
+            consume_output(g - 1, xb)
 
 
 def main() -> None:
@@ -111,7 +115,9 @@ def main() -> None:
     rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    from datetime import timedelta
+
+    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=60))  # fail fast, never hang
     wl = WORKLOADS[args.workload]
     sh = wl.shape
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[wl.dtype]
