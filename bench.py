@@ -251,7 +251,7 @@ def main():
     for i in range(batch):
         for l in range(n_layers):
             stage.prepare(int(slots[i]), l, int(lens0[i]) + headroom - 1)
-            stage.fill_normal(stage.layer_ptr(int(slots[i]), l), int(lens0[i]) * row_elems, tdt, args.seed,
+            stage.fill_normal(stage.layer_ptr(int(slots[i]), l), int(lens0[i]) * row_elems, tdt, args.seed + 1000 * rank,
                               offset=(i * n_layers + l) * sh.seq_len * row_elems)
     q_all = torch.empty((n_layers, batch, sh.dim), dtype=tdt, device=dev)
     kv_all = torch.empty((n_layers, batch, row_elems), dtype=tdt, device=dev)

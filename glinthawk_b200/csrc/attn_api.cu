@@ -790,7 +790,46 @@ int gh_attn_prefill_chunk( gh_attn_t h,
       return rc;
   }
 
-  // 2. causal attention: every (context, token) is a decode problem over its own prefix, launched in slices of at
+  // 2a. tensor-core kernel in chunk mode: 16 / group consecutive tokens of a context share one block per kv head,
+  //     so they share every K/V fetch.  Work item = (context, token group), never cut, longest prefix first.
+  if ( h->use_mma && decode_mma_chunk_supported( h->sh ) ) {
+    const uint32_t per_item = 16 / h->sh.group;
+    std::vector<WorkItem> items;
+    for ( uint64_t i = 0; i < n_ctx; i++ ) {
+      if ( base[i].kv_off == kInactive )
+        continue;
+      for ( uint32_t g = 0; g * per_item < n_tokens; g++ ) {
+        WorkItem w;
+        w.ctx = static_cast<int32_t>( i );
+        w.t_begin = 0;
+        w.t_end = static_cast<int32_t>( pos0[i] + std::min( n_tokens, ( g + 1 ) * per_item ) ); // last token's prefix
+        w.split = static_cast<int32_t>( g );
+        items.push_back( w );
+      }
+    }
+    std::stable_sort( items.begin(), items.end(), []( const WorkItem& x, const WorkItem& y ) { return x.t_end > y.t_end; } );
+    for ( auto& c : base )
+      c.nsplits = 1;
+    for ( size_t i0 = 0; i0 < items.size(); i0 += h->max_items ) {
+      const size_t n = std::min<size_t>( h->max_items, items.size() - i0 );
+      int idx;
+      if ( const int rc = ring_claim( h, &idx ); rc != GH_OK )
+        return rc;
+      RingEntry& r = h->ring[idx];
+      std::memcpy( entry_ctx( h, r.host ), base.data(), n_ctx * sizeof( CtxMeta ) );
+      std::memcpy( entry_items( h, r.host ), items.data() + i0, n * sizeof( WorkItem ) );
+      GH_CUDA( h, cudaMemcpyAsync( r.dev, r.host, h->off_items + n * sizeof( WorkItem ), cudaMemcpyHostToDevice, st ) );
+      DecodeArgs a = decode_args( h, idx, static_cast<uint32_t>( n ), 0, h->pool.layer_offset( layer ), q_inout, xb );
+      a.chunk_tokens = n_tokens;
+      if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
+        return rc;
+      if ( const int rc = ring_touch( h, idx, st ); rc != GH_OK )
+        return rc;
+    }
+    return GH_OK;
+  }
+
+  // 2b. otherwise every (context, token) is a decode problem over its own prefix, launched in slices of at
   //    most max_batch problems
   const size_t q_row_bytes = static_cast<size_t>( h->sh.n_heads ) * h->sh.head_size * h->elem;
   const uint64_t total = n_ctx * n_tokens;

@@ -159,10 +159,16 @@ __device__ __forceinline__ float fast_exp2( float x )
 }
 
 // G16: the group has more than 8 query heads, so rows 8..15 of the M=16 tile are live too.
-template<typename T, bool G16, typename G>
+//
+// CHUNK: prefill-chunk mode.  The 16 rows of the tile are (token, head) pairs of 16/group consecutive prompt tokens
+// of one context instead of up to 16 heads of one token, so the tokens of a group share every K/V fetch.  A work
+// item is then (context, token group): `split` is the group's index, t_end the prefix length of the group's last
+// token; row r attends causally over the prefix of ITS token, which is shorter by (last token - its token).
+template<typename T, bool G16, typename G, bool CHUNK>
 __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   decode_mma_kernel( const DecodeArgs a, const __grid_constant__ CUtensorMap kv_map )
 {
+  constexpr bool ROWS16 = G16 || CHUNK;
   constexpr int kTile = G::kTile, kConsumerWarps = G::kConsumerWarps, kConsumers = G::kConsumers;
   constexpr int kBoxBytes = G::kBoxBytes, kStageBytes = G::kStageBytes, kStages = G::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -232,20 +238,31 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   const int group = sh.group;
   const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f; // 1/sqrt(128) * log2(e)
 
-  // Q fragments (A operand), 8 k-steps of 16 dims; rows >= group are zero.
+  // Q fragments (A operand), 8 k-steps of 16 dims; rows that stand for no (token, head) are zero.
   uint32_t qf[8][4];
+  // chunk mode: which prompt token and head each of this thread's two rows stands for
+  const int tok_per_item = CHUNK ? 16 / group : 1;
+  const int tok0 = CHUNK ? it.split * tok_per_item : 0;                          // first token of the group
+  const int n_tok = CHUNK ? min( tok_per_item, (int)a.chunk_tokens - tok0 ) : 1; // tokens the group really has
+  const int row_tok[2] = { CHUNK ? quad_row / group : 0, CHUNK ? ( quad_row + 8 ) / group : 0 };
+  const int row_head[2] = { CHUNK ? quad_row % group : quad_row, CHUNK ? ( quad_row + 8 ) % group : quad_row + 8 };
+  // tokens by which a row's prefix is shorter than the item's (the last token's) prefix
+  const int row_short[2] = { CHUNK ? max( 0, n_tok - 1 - row_tok[0] ) : 0, CHUNK ? max( 0, n_tok - 1 - row_tok[1] ) : 0 };
   asm volatile( "griddepcontrol.wait;" ::: "memory" ); // q was rotated by the kernel before this one
   {
-    const T* qbase = static_cast<const T*>( a.q ) + (size_t)it.ctx * sh.n_heads * kHS + (size_t)kvh * group * kHS;
+    const size_t q_ctx_row = CHUNK ? (size_t)it.ctx * a.chunk_tokens + tok0 : (size_t)it.ctx;
+    const T* qbase = static_cast<const T*>( a.q ) + q_ctx_row * sh.n_heads * kHS + (size_t)kvh * group * kHS;
+    const bool live[2] = { CHUNK ? row_tok[0] < n_tok : quad_row < group,
+                           CHUNK ? row_tok[1] < n_tok : ( G16 && quad_row + 8 < group ) };
+    const T* rowp[2] = { qbase + ( (size_t)row_tok[0] * sh.n_heads + row_head[0] ) * kHS,
+                         qbase + ( (size_t)row_tok[1] * sh.n_heads + row_head[1] ) * kHS };
 #pragma unroll
     for ( int ks = 0; ks < 8; ks++ ) {
       const int d = ks * 16 + quad_col;
-      const bool lo = quad_row < group;
-      const bool hi = G16 && ( quad_row + 8 < group );
-      qf[ks][0] = lo ? *reinterpret_cast<const uint32_t*>( qbase + quad_row * kHS + d ) : 0u;
-      qf[ks][2] = lo ? *reinterpret_cast<const uint32_t*>( qbase + quad_row * kHS + d + 8 ) : 0u;
-      qf[ks][1] = hi ? *reinterpret_cast<const uint32_t*>( qbase + ( quad_row + 8 ) * kHS + d ) : 0u;
-      qf[ks][3] = hi ? *reinterpret_cast<const uint32_t*>( qbase + ( quad_row + 8 ) * kHS + d + 8 ) : 0u;
+      qf[ks][0] = live[0] ? *reinterpret_cast<const uint32_t*>( rowp[0] + d ) : 0u;
+      qf[ks][2] = live[0] ? *reinterpret_cast<const uint32_t*>( rowp[0] + d + 8 ) : 0u;
+      qf[ks][1] = live[1] ? *reinterpret_cast<const uint32_t*>( rowp[1] + d ) : 0u;
+      qf[ks][3] = live[1] ? *reinterpret_cast<const uint32_t*>( rowp[1] + d + 8 ) : 0u;
     }
   }
 
@@ -306,7 +323,8 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       // each 8-token tile.
       float p[2][4];
 #pragma unroll
-      for ( int half = 0; half < ( G16 ? 2 : 1 ); half++ ) {
+      for ( int half = 0; half < ( ROWS16 ? 2 : 1 ); half++ ) {
+        const int lim = valid - row_short[half]; // this row's own causal limit inside the tile
         float sv[4];
 #pragma unroll
         for ( int nt = 0; nt < 2; nt++ )
@@ -314,7 +332,7 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
           for ( int j = 0; j < 2; j++ ) {
             const int tok = w0 + nt * 8 + quad_col + j;
             const float v = sacc[nt][half * 2 + j] * scale_log2;
-            sv[nt * 2 + j] = tok < valid ? v : -INFINITY;
+            sv[nt * 2 + j] = tok < lim ? v : -INFINITY;
           }
         float mx = fmaxf( fmaxf( sv[0], sv[1] ), fmaxf( sv[2], sv[3] ) );
         mx = fmaxf( mx, __shfl_xor_sync( 0xffffffffu, mx, 1 ) );
@@ -341,8 +359,8 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       uint32_t pf[4];
       pf[0] = pack2<T>( p[0][0], p[0][1] );
       pf[2] = pack2<T>( p[0][2], p[0][3] );
-      pf[1] = G16 ? pack2<T>( p[1][0], p[1][1] ) : 0u;
-      pf[3] = G16 ? pack2<T>( p[1][2], p[1][3] ) : 0u;
+      pf[1] = ROWS16 ? pack2<T>( p[1][0], p[1][1] ) : 0u;
+      pf[3] = ROWS16 ? pack2<T>( p[1][2], p[1][3] ) : 0u;
 
       // ---- O += P V
 #pragma unroll
@@ -369,12 +387,12 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
     __nanosleep( 1000000 );
     return;
   }
-  constexpr int kRows = G16 ? 16 : 8;
+  constexpr int kRows = ROWS16 ? 16 : 8;
   static_assert( ( kConsumerWarps + 1 ) * kRows * kHS * 4 <= kStages * kStageBytes, "merge scratch must fit the ring" );
   float* sm_wo = reinterpret_cast<float*>( ring );                 // [warp][kRows][128]
   float* sm_o = sm_wo + kConsumerWarps * kRows * kHS;               // [kRows][128] merged
 #pragma unroll
-  for ( int half = 0; half < ( G16 ? 2 : 1 ); half++ ) {
+  for ( int half = 0; half < ( ROWS16 ? 2 : 1 ); half++ ) {
     float l = l_run[half];
     l += __shfl_xor_sync( 0xffffffffu, l, 1 );
     l += __shfl_xor_sync( 0xffffffffu, l, 2 );
@@ -390,8 +408,9 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   }
   asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
 
+  const int live_rows = CHUNK ? n_tok * group : group;
   for ( int d = threadIdx.x; d < kHS; d += kConsumers ) {
-    for ( int r = 0; r < group; r++ ) {
+    for ( int r = 0; r < live_rows; r++ ) {
       float M = -INFINITY;
 #pragma unroll
       for ( int w = 0; w < kConsumerWarps; w++ )
@@ -412,8 +431,17 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   }
   asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
 
-  store_item<T>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
-                 threadIdx.x, kConsumers );
+  if constexpr ( CHUNK ) {
+    // row r = (token r / group, head r % group) of the group; a chunk item is never cut, so this is the result
+    T* out = static_cast<T*>( a.xb ) + ( (size_t)it.ctx * a.chunk_tokens + tok0 ) * sh.n_heads * kHS + (size_t)kvh * group * kHS;
+    for ( int e = threadIdx.x; e < live_rows * kHS; e += kConsumers ) {
+      const int r = e / kHS, d = e - r * kHS;
+      out[( (size_t)( r / group ) * sh.n_heads + ( r % group ) ) * kHS + d] = Conv<T>::from_f32( sm_o[e] / sm_l[r] );
+    }
+  } else {
+    store_item<T>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
+                   threadIdx.x, kConsumers );
+  }
 }
 
 template<typename T, typename G>
@@ -429,8 +457,10 @@ cudaError_t launch_g( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t 
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = a.sh.group > 8 ? cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G>, a, *map )
-                                 : cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, false, G>, a, *map );
+  if ( a.chunk_tokens > 0 )
+    return cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G, true>, a, *map );
+  cudaError_t e = a.sh.group > 8 ? cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G, false>, a, *map )
+                                 : cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, false, G, false>, a, *map );
   if ( e == cudaSuccess && a.n_split_ctx > 0 )
     e = launch_merge_partials<T>( a.sh, a.ctx, a.split_ctx, a.n_split_ctx, a.part_o, a.part_ml, static_cast<T*>( a.xb ), st );
   return e;
@@ -468,7 +498,12 @@ cudaError_t launch_t( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t 
 template<typename T, bool G16, typename G>
 cudaError_t allow_smem()
 {
-  return cudaFuncSetAttribute( decode_mma_kernel<T, G16, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes );
+  cudaError_t e = cudaFuncSetAttribute( decode_mma_kernel<T, G16, G, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        G::kSmemBytes );
+  if ( e == cudaSuccess && G16 )
+    e = cudaFuncSetAttribute( decode_mma_kernel<T, true, G, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              G::kSmemBytes );
+  return e;
 }
 
 template<typename G>
@@ -500,6 +535,11 @@ bool decode_mma_supported( const Shape& sh, uint32_t dtype )
 {
   return ( dtype == DT_F16 || dtype == DT_BF16 ) && sh.head_size == kHS && sh.group <= 16
          && sh.seq_len % kPlanTile == 0;
+}
+
+bool decode_mma_chunk_supported( const Shape& sh )
+{
+  return sh.group == 1 || sh.group == 2 || sh.group == 4 || sh.group == 8;
 }
 
 cudaError_t decode_mma_prepare()

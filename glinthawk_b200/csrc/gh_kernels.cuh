@@ -43,6 +43,7 @@ struct DecodeArgs
   uint32_t n_split_ctx;
   uint32_t* dev_error;
   uint32_t sm_count;
+  uint32_t chunk_tokens; // 0 = decode step; T = prefill chunk of T tokens per context (tensor-core kernel only)
 };
 
 struct ScoreArgs // the reference's three unfused operations
@@ -61,6 +62,7 @@ cudaError_t launch_append( const AppendArgs& a, cudaStream_t st, uint64_t* launc
 cudaError_t launch_decode_generic( const DecodeArgs& a, cudaStream_t st, uint64_t* launches );
 // TMA + tensor-core decode kernel; `kv_map` describes the whole arena as [rows][2 * kv_dim].
 bool decode_mma_supported( const Shape& sh, uint32_t dtype );
+bool decode_mma_chunk_supported( const Shape& sh ); // prefill-chunk mode packs 16 / group tokens into a tile
 cudaError_t decode_mma_prepare(); // one-time function attributes
 cudaError_t launch_decode_mma( const DecodeArgs& a, const CUtensorMap* kv_map, cudaStream_t st, uint64_t* launches );
 uint32_t decode_mma_tile_tokens(); // work items start on multiples of this

@@ -37,8 +37,11 @@ def sum_over_ranks(value: float, device: torch.device | str = "cpu") -> float:
 
 
 def weak_scaling_lengths(wl: Workload, seed: int, rank: int, headroom: int, batch: int | None = None) -> np.ndarray:
-    """Every rank draws its own contexts (per-GPU work fixed as ranks are added)."""
-    return wl.lengths(seed + rank, headroom)[: batch or wl.batch]
+    """Weak scaling: every rank serves its own contexts, and the per-GPU work is exactly the same on every rank —
+    the same multiset of cached lengths (so that the maximum over ranks measures the machine, not the luck of
+    the draw), in a rank-specific order; the cached values themselves differ by rank (seeded by the caller)."""
+    lens = wl.lengths(seed, headroom)[: batch or wl.batch]
+    return np.random.default_rng(seed + 7919 * (rank + 1)).permutation(lens) if rank > 0 else lens
 
 
 def strong_scaling_lengths(wl: Workload, seed: int, rank: int, world: int, headroom: int) -> tuple[np.ndarray, np.ndarray]:

@@ -227,7 +227,8 @@ def test_layers_in_flight_on_several_streams(oracle):
     st.close()
 
 
-@pytest.mark.parametrize("shape_name,dtype", [("mini_g4", cases.BF16), ("mini_g8", cases.F16), ("tiny15m", cases.F32)])
+@pytest.mark.parametrize("shape_name,dtype", [("mini_g4", cases.BF16), ("mini_g8", cases.F16), ("tiny15m", cases.F32),
+                                              ("mini_mha", cases.F16), ("mini_g16", cases.F16), ("mini_g4", cases.F16)])
 def test_prefill_chunk_equals_token_by_token_reference_steps(oracle, shape_name, dtype):
     """A multi-token prompt chunk in one call.  The reference has no such operation — it feeds prompts one token
     per forward pass — so the oracle is n_tokens consecutive reference layer-steps on a growing cache."""

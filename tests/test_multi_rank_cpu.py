@@ -53,7 +53,7 @@ def test_two_gloo_ranks_shard_requests_without_overlap():
     wl = WORKLOADS["llama2_70b_gqa"]
     lens = wl.lengths(20240, 16)
     (r0, weak0, idx0, tok0, cov0, total_tokens, total_ctx, slowest), (r1, weak1, idx1, tok1, cov1, *_rest) = results
-    assert weak0 != weak1, "weak scaling: ranks draw different contexts"
+    assert weak0 != weak1, "weak scaling: every rank has its own contexts (same lengths, different order)"
     assert sorted(idx0 + idx1) == list(range(wl.batch)) and not set(idx0) & set(idx1)
     assert tok0 == cov0 and tok1 == cov1, "every cached token is covered by exactly one work item"
     assert total_tokens == float((lens + 1).sum()) and total_ctx == wl.batch
