@@ -291,7 +291,8 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       break;
     }
     const uint32_t st = smem_u32( ring + s * kStageBytes );
-    const int valid = min( kTile, it.t_end - it.t_begin - t * kTile ); // live tokens in this tile
+    const int remaining = it.t_end - it.t_begin - t * kTile; // tokens of the item from this tile's start on
+    const int valid = min( kTile, remaining );               // live tokens in this tile
     const int w0 = warp * 16;
 
     if ( w0 < valid ) {
@@ -324,7 +325,7 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       float p[2][4];
 #pragma unroll
       for ( int half = 0; half < ( ROWS16 ? 2 : 1 ); half++ ) {
-        const int lim = valid - row_short[half]; // this row's own causal limit inside the tile
+        const int lim = remaining - row_short[half]; // this row's own causal limit, counted from the tile's start
         float sv[4];
 #pragma unroll
         for ( int nt = 0; nt < 2; nt++ )
@@ -338,11 +339,14 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
         mx = fmaxf( mx, __shfl_xor_sync( 0xffffffffu, mx, 1 ) );
         mx = fmaxf( mx, __shfl_xor_sync( 0xffffffffu, mx, 2 ) );
         const float m_new = fmaxf( m_run[half], mx );
-        const float corr = fast_exp2( m_run[half] - m_new );
+        // In chunk mode a row can have no visible token among THIS warp's 16 (its prefix ends earlier): keep the
+        // exponent arguments finite so that such a row carries zeros, not NaNs, until the warps are combined.
+        const float m_use = ( CHUNK && m_new == -INFINITY ) ? 0.f : m_new;
+        const float corr = fast_exp2( m_run[half] - m_use );
         float psum = 0.f;
 #pragma unroll
         for ( int e = 0; e < 4; e++ ) {
-          const float pe = fast_exp2( sv[e] - m_new );
+          const float pe = fast_exp2( sv[e] - m_use );
           p[half][e] = pe;
           psum += pe;
         }
