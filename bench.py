@@ -237,17 +237,28 @@ def main():
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[wl.dtype]
     W, K = args.warmup, args.steps
     E = min(K, 5) if args.e2e_steps < 0 else args.e2e_steps
+    if wl.prefill_contexts:
+        E = 0  # the host-buffer entry point covers decode steps only
     headroom = W + K + E + 2
     lens0 = dist_util.weak_scaling_lengths(wl, args.seed, rank, headroom, batch)  # every rank draws its own contexts
 
     # ---- set-up (untimed): slots, cached KV, inputs ----
     t_setup = time.perf_counter()
-    stage = AttentionStage(sh, tdt, n_layers_hosted=n_layers, max_batch=batch, max_contexts=batch,
+    n_pf, t_pf = wl.prefill_contexts, wl.prefill_tokens
+    stage = AttentionStage(sh, tdt, n_layers_hosted=n_layers, max_batch=max(batch, n_pf), max_contexts=batch + n_pf,
                            paged=not args.static, device=local_rank, decode_chunk=args.decode_chunk)
     cos, sin = rope_tables(sh.head_size, sh.seq_len, sh.rope_theta)
     stage.set_rope_tables(torch.from_numpy(cos).to(dev).to(tdt), torch.from_numpy(sin).to(dev).to(tdt))
     slots = stage.get_contexts(np.arange(1, batch + 1, dtype=np.uint32))
     row_elems = 2 * sh.kv_dim
+    if n_pf:  # prompt chunks go into slots of their own, rewritten from position 0 every step
+        pf_slots = stage.get_contexts(np.arange(batch + 1, batch + n_pf + 1, dtype=np.uint32))
+        pf_pos0 = np.zeros(n_pf, dtype=np.uint32)
+        pf_q = torch.empty((n_layers, n_pf, t_pf, sh.dim), dtype=tdt, device=dev)
+        pf_kv = torch.empty((n_layers, n_pf, t_pf, row_elems), dtype=tdt, device=dev)
+        pf_xb = torch.zeros_like(pf_q)
+        stage.fill_normal(pf_q, pf_q.numel(), tdt, args.seed + 11)
+        stage.fill_normal(pf_kv, pf_kv.numel(), tdt, args.seed + 12)
     for i in range(batch):
         for l in range(n_layers):
             stage.prepare(int(slots[i]), l, int(lens0[i]) + headroom - 1)
@@ -291,6 +302,8 @@ def main():
                 record.append((e0, e1))
             elif ghlib.gh_attn_step(handle, l, q_ptr[l], kv_ptr[l], xb_ptr[l], st_ptr) != 0:
                 raise RuntimeError(ghlib.gh_attn_last_error(handle).decode())
+            if n_pf:
+                stage.prefill_chunk(l, pf_slots, pf_pos0, t_pf, pf_q[l], pf_kv[l], pf_xb[l])
         pos[:] += 1
 
     def barrier():
@@ -321,7 +334,7 @@ def main():
     launches = stage.stats().kernel_launches - launches0
     ms = dist_util.max_over_ranks(ms, dev)
     ms_per_step = ms / K
-    value = batch * world / (ms_per_step / 1e3)
+    value = (batch + n_pf * t_pf) * world / (ms_per_step / 1e3)  # tokens advanced per second, prompt tokens included
 
     decode_ms = [a.elapsed_time(b) for a, b in decode_events]
     decode_ms_mean = sum(decode_ms) / len(decode_ms)

@@ -24,6 +24,8 @@ class Workload:
     batch: int          # contexts decoding one token each
     length_dist: str    # how the cached lengths are drawn
     description: str
+    prefill_contexts: int = 0   # additional contexts that append a prompt chunk into a fresh slot every step
+    prefill_tokens: int = 0     # tokens per prompt chunk
 
     def lengths(self, seed: int, headroom: int = 0) -> np.ndarray:
         """Cached tokens per context before the first step; every context keeps `headroom` free positions."""
@@ -50,6 +52,10 @@ WORKLOADS = {w.name: w for w in [
              "Llama2-13B attention stage, 40 layers, fp16, 40 heads (MHA), 128 contexts, lengths uniform 512..4096"),
     Workload("llama3_8b_decode", SHAPES["l3_8b_8k"], "bf16", 1, 448, "uniform_256_8191",
              "Llama3-8B GQA decode part, one layer, bf16, 32 q / 8 kv heads, 448 contexts, lengths uniform 256..8192"),
+    Workload("llama3_8b_mixed", SHAPES["l3_8b_8k"], "bf16", 1, 448, "uniform_256_8191",
+             "Llama3-8B GQA mixed prefill + decode, one layer, bf16, 32 q / 8 kv heads, head 128, slots of 8192: "
+             "448 contexts decode one token each (lengths uniform 256..8192), 64 contexts append a 512-token prompt "
+             "chunk into fresh slots", prefill_contexts=64, prefill_tokens=512),
 ]}
 
 
