@@ -276,3 +276,66 @@ def test_prefill_chunk_equals_token_by_token_reference_steps(oracle, shape_name,
         np.testing.assert_allclose(cases.as_f32(got[p:, :kvd], dtype), cases.as_f32(cache[i][p:p + T, :kvd], dtype),
                                    rtol=cases.TOL_K_REL, atol=1e-3 if dtype != cases.BF16 else 8e-3)
     st.close()
+
+
+@pytest.mark.parametrize("force_generic", [False, True])
+def test_garbage_beyond_the_current_position_is_never_read_into_the_result(oracle, force_generic):
+    """A slot keeps whatever its previous owner left behind the current position (the reference never clears
+    contexts either).  NaNs and infinities planted in every row after `pos` must not reach the output, although
+    the tensor-core kernel fetches whole 32-token tiles that include those rows."""
+    pos = [0, 5, 30, 31, 32, 33, 63, 64, 100, 254]
+    case = cases.make_case("nan", "mini_g8", cases.F16, pos, seed=71)
+    want = oracle.layer_step(case)
+    st = gpu_util.make_stage(case, force_generic=force_generic)
+    slots = gpu_util.load_case(st, case, layer=0)
+    for i, p in enumerate(pos):
+        tail = st.layer_view(int(slots[i]), 0, case.shape.seq_len)[p + 1:]
+        tail[0::3] = float("nan")
+        tail[1::3] = float("inf")
+        tail[2::3] = -float("inf")
+    res = gpu_util.run_step(st, case, slots, layer=0)
+    assert np.isfinite(cases.as_f32(res.xb, cases.F16)).all()
+    gpu_util.assert_step_close(res, want, case)
+    st.close()
+
+
+def test_largest_batch_and_all_inactive_batch(oracle):
+    """MAX_BATCH_SIZE (1024, src/models/llama2/base.hh:26) contexts in one call, a third of them inactive; then a
+    batch with no active prompt at all, which must leave every buffer untouched."""
+    rng = np.random.default_rng(8)
+    B = 1024
+    pos = rng.integers(0, 48, size=B)
+    pos[:4] = [0, 47, 31, 32]
+    inactive = list(range(2, B, 3))
+    case = cases.make_case("big", "mini_g4", cases.F16, pos, seed=72, inactive=inactive)
+    want = oracle.layer_step(case)
+    st = gpu_util.make_stage(case, layers=1)
+    slots = gpu_util.load_case(st, case, layer=0)
+    res = gpu_util.run_step(st, case, slots, layer=0)
+    gpu_util.assert_step_close(res, want, case)
+    q = gpu_util.to_dev(case.q, cases.F16)
+    xb = torch.full_like(q, 3.0)
+    q0 = q.clone()
+    none = np.full(B, -1, dtype=np.int32)
+    st.batch_begin(none, case.pos)
+    st.step(0, q, gpu_util.to_dev(case.kv_new, cases.F16), xb)
+    torch.cuda.synchronize()
+    assert torch.equal(q, q0) and bool((xb == 3.0).all())
+    st.close()
+
+
+def test_slot_reuse_after_release_starts_clean(oracle):
+    """A released slot is handed to the next context (contextman.hh:193-195 recycles contexts the same way); the new
+    context's results depend only on what it appended itself."""
+    first = cases.make_case("a", "mini_g8", cases.F16, [400], seed=81)
+    second = cases.make_case("b", "mini_g8", cases.F16, [37], seed=82)
+    for paged in (False, True):
+        st = gpu_util.make_stage(first, paged=paged, max_contexts=1)
+        slots = gpu_util.load_case(st, first, layer=0, first_id=10)
+        gpu_util.run_step(st, first, slots, layer=0)
+        assert st.release_context(10)
+        slots2 = gpu_util.load_case(st, second, layer=0, first_id=11)
+        assert slots2[0] == slots[0]
+        res = gpu_util.run_step(st, second, slots2, layer=0)
+        gpu_util.assert_step_close(res, oracle.layer_step(second), second)
+        st.close()
