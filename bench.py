@@ -113,6 +113,12 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+# DRAM traffic of one decode launch relative to its algorithmic bytes, from the ncu capture summarised in
+# profiles/decode_mma_kernel_llama2_70b.md (dram__bytes_read.sum + dram__bytes_write.sum = 1.378 GB against 1.361 GB
+# algorithmic on this very batch; traffic grows in proportion to the cached tokens).  Other workloads: not captured.
+NCU_TRAFFIC_RATIO = {"llama2_70b_gqa": 1.0123}
+
+
 def measured_peak() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -412,7 +418,9 @@ def main():
             "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if stats.last_kernel else "decode_generic_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"of {peak_src}", "frac_of_nominal_8tbs": achieved / 8000.0,
-                         "bytes_per_launch": decode_bytes, "ms_per_launch": decode_ms_mean, "traffic": None},
+                         "bytes_per_launch": decode_bytes, "ms_per_launch": decode_ms_mean,
+                         "traffic": (decode_bytes * NCU_TRAFFIC_RATIO[wl.name]
+                                     if wl.name in NCU_TRAFFIC_RATIO and batch == wl.batch and stats.last_kernel else None)},
             "clocks": clocks.summary(),
             "e2e": e2e,
             "gpu_launches": int(launches),
