@@ -387,7 +387,12 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
     return GH_ERR_CUDA; // no CPU path exists: without a usable device the stage cannot be created
   }
 
-  std::unique_ptr<gh_attn> h( new gh_attn() );
+  // every early return below releases whatever has been allocated so far
+  struct Destroyer
+  {
+    void operator()( gh_attn* p ) const { gh_attn_destroy( p ); }
+  };
+  std::unique_ptr<gh_attn, Destroyer> h( new gh_attn() );
   h->cfg = *cfg;
   h->device = cfg->device;
   DeviceGuard guard( h->device );
@@ -434,10 +439,10 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
   h->off_ptrs = h->off_items + sizeof( WorkItem ) * h->max_items;
   h->off_pos = h->off_ptrs + sizeof( void* ) * cfg->max_batch;
   h->entry_bytes = ( h->off_pos + sizeof( uint32_t ) * cfg->max_batch + 255 ) / 256 * 256;
-  char* host_all = nullptr;
-  char* dev_all = nullptr;
-  GH_CUDA( h.get(), cudaMallocHost( reinterpret_cast<void**>( &host_all ), h->entry_bytes * kRing ) );
-  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &dev_all ), h->entry_bytes * kRing ) );
+  GH_CUDA( h.get(), cudaMallocHost( reinterpret_cast<void**>( &h->ring[0].host ), h->entry_bytes * kRing ) );
+  GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->ring[0].dev ), h->entry_bytes * kRing ) );
+  char* host_all = h->ring[0].host;
+  char* dev_all = h->ring[0].dev;
   for ( uint32_t k = 0; k < kRing; k++ ) {
     h->ring[k].host = host_all + k * h->entry_bytes;
     h->ring[k].dev = dev_all + k * h->entry_bytes;

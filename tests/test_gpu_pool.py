@@ -137,3 +137,19 @@ def test_fill_normal_statistics():
     torch.cuda.synchronize()
     assert torch.equal(z, x[1 << 19:])
     st.close()
+
+
+def test_create_that_cannot_fit_reports_out_of_memory_and_leaks_nothing():
+    """Static slots for 4096 Llama2-70B contexts would need 5 TB: creation fails with a status (the reference aborts
+    the process, src/arch/cuda/llama2/ops.cuh:113-115), and what had been allocated before the failure is released."""
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        with pytest.raises(GlinthawkAttnError) as e:
+            AttentionStage(SHAPES["l70b_4k"], torch.float16, n_layers_hosted=80, max_batch=8, max_contexts=4096)
+        assert e.value.status == _lib.GH_ERR_OOM
+    free1, _ = torch.cuda.mem_get_info()
+    assert free0 - free1 < (64 << 20)
+    # the same shape with paged slots only reserves address space
+    st = AttentionStage(SHAPES["l70b_4k"], torch.float16, n_layers_hosted=80, max_batch=8, max_contexts=512, paged=True)
+    assert st.stats().bytes_mapped == 0 and st.stats().bytes_reserved >= 512 * st.slot_bytes()
+    st.close()
