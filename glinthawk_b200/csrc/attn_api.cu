@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -483,6 +484,7 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
         return GH_ERR_CUDA;
       }
       GH_CUDA( h.get(), decode_mma_prepare() );
+      GH_CUDA( h.get(), prefill_umma_prepare() );
     }
   }
 
@@ -795,10 +797,17 @@ int gh_attn_prefill_chunk( gh_attn_t h,
       return rc;
   }
 
-  // 2a. tensor-core kernel in chunk mode: 16 / group consecutive tokens of a context share one block per kv head,
-  //     so they share every K/V fetch.  Work item = (context, token group), never cut, longest prefix first.
-  if ( h->use_mma && decode_mma_chunk_supported( h->sh ) ) {
-    const uint32_t per_item = 16 / h->sh.group;
+  // 2a. tensor-core kernels: consecutive tokens of a context share one block per kv head, so they share every K/V
+  //     fetch.  Work item = (context, token group), never cut, longest prefix first.  The tcgen05 kernel packs
+  //     128 / group tokens into a block; the warp-level kernel in chunk mode packs 16 / group (kept for comparison
+  //     runs: GLINTHAWK_PREFILL=mma).
+  static const bool prefer_warp_mma = [] {
+    const char* e = std::getenv( "GLINTHAWK_PREFILL" );
+    return e != nullptr && std::string( e ) == "mma";
+  }();
+  const bool umma = h->use_mma && prefill_umma_supported( h->sh, h->cfg.dtype ) && !prefer_warp_mma;
+  if ( umma || ( h->use_mma && decode_mma_chunk_supported( h->sh ) ) ) {
+    const uint32_t per_item = umma ? prefill_umma_tokens_per_item( h->sh ) : 16 / h->sh.group;
     std::vector<WorkItem> items;
     for ( uint64_t i = 0; i < n_ctx; i++ ) {
       if ( base[i].kv_off == kInactive )
@@ -826,8 +835,13 @@ int gh_attn_prefill_chunk( gh_attn_t h,
       GH_CUDA( h, cudaMemcpyAsync( r.dev, r.host, h->off_items + n * sizeof( WorkItem ), cudaMemcpyHostToDevice, st ) );
       DecodeArgs a = decode_args( h, idx, static_cast<uint32_t>( n ), 0, h->pool.layer_offset( layer ), q_inout, xb );
       a.chunk_tokens = n_tokens;
-      if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
+      if ( umma ) {
+        if ( const cudaError_t e = launch_prefill_umma( a, &h->kv_map, st, &h->stats.kernel_launches ); e != cudaSuccess )
+          return cuda_fail( h, "prefill kernel launch", e );
+        h->stats.last_kernel = 2;
+      } else if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK ) {
         return rc;
+      }
       if ( const int rc = ring_touch( h, idx, st ); rc != GH_OK )
         return rc;
     }

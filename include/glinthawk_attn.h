@@ -102,7 +102,7 @@ typedef struct gh_attn_stats
   uint32_t slots_allocated;
   uint32_t last_items;      /* work items (context splits) of the most recent batch */
   uint32_t last_chunk;      /* split length used by the most recent batch */
-  uint32_t last_kernel;     /* 0 = CUDA-core decode kernel, 1 = TMA + tensor-core decode kernel */
+  uint32_t last_kernel;     /* 0 = CUDA-core decode kernel, 1 = TMA + warp tensor-core kernel, 2 = tcgen05 prefill kernel */
   uint32_t device_error;    /* sticky flag written by kernels whose bounded waits ran out */
 } gh_attn_stats;
 
