@@ -7,16 +7,17 @@
 //
 // One thread block = (context, kv head, query block).  A query block is 128 rows of the score matrix: 128 / group
 // consecutive prompt tokens x the group's query heads, so every K/V byte fetched serves 128 rows.  Keys are walked in
-// tiles of 128 tokens, staged by TMA (same arena descriptor and 128-byte swizzle as the decode kernel):
+// tiles of 64 tokens, staged by TMA (same arena descriptor and 128-byte swizzle as the decode kernel):
 //
-//   S[128 x 128]  = Q[128 x 128 dims] . K_tile^T      tcgen05.mma, both operands K-major in shared memory -> TMEM
+//   S[128 x 64]   = Q[128 x 128 dims] . K_tile^T      tcgen05.mma, both operands K-major in shared memory -> TMEM
 //   P             = 2^(S * scale - m), causal mask    one thread per row (tcgen05.ld), no shuffles; written to shared
 //                                                     memory as the next MMA's A operand
-//   O[128 x 128] += P[128 x 128 keys] . V_tile        tcgen05.mma, V is the MN-major B operand straight from the tile
+//   O[128 x 128] += P[128 x 64 keys] . V_tile         tcgen05.mma, V is the MN-major B operand straight from the tile
 //
 // Two passes over the keys: the first only finds each row's maximum m, the second accumulates with that final
 // maximum, so O in TMEM never has to be rescaled.  Tensor work doubles for S, which costs little here; K is read
 // twice, through L2.  fp32 accumulation throughout; P is rounded to the storage type (as in the decode kernel).
+// 96 KiB of shared memory and 256 TMEM columns per block: two blocks per SM overlap each other's phases.
 //
 // Every wait is bounded; on expiry the kernel raises the sticky error word, frees its TMEM and leaves.
 #include <type_traits>
@@ -29,12 +30,16 @@ namespace {
 
 constexpr int kHS = 128;
 constexpr int kRows = 128;                 // rows of a query block = TMEM lanes
-constexpr int kKeys = 128;                 // keys per tile
+constexpr int kKeys = 64;                  // keys per tile
 constexpr int kBoxRows = 32;               // token rows per TMA box of the arena descriptor
-constexpr int kHalf = kRows * 128;         // one [128 rows x 128 B] swizzled region = 16 KiB
-constexpr int kTileBytes = 2 * kHalf;      // a K or V tile, a Q block, a P block: 32 KiB
-constexpr int kSmemBytes = 6 * kTileBytes + 1024; // Q, P, K x2, V x2 (+ alignment slack)
-constexpr int kTmemCols = 256;             // S: columns 0..127, O: columns 128..255
+constexpr int kQRegion = kRows * 128;      // [128 rows x 128 B] swizzled region (Q: two of them, P: one) = 16 KiB
+constexpr int kKRegion = kKeys * 128;      // [64 keys x 128 B] swizzled region (K and V tiles: two each) = 8 KiB
+constexpr int kKTile = 2 * kKRegion;       // 16 KiB
+constexpr int kOffP = 2 * kQRegion;        // shared-memory map: Q | P | K stage 0 | K stage 1 | V
+constexpr int kOffK = kOffP + kQRegion;
+constexpr int kOffV = kOffK + 2 * kKTile;
+constexpr int kSmemBytes = kOffV + kKTile + 1024; // 96 KiB + alignment slack: two blocks per SM
+constexpr int kTmemCols = 256;             // S: columns 0..63, O: columns 128..255 (two blocks fill the SM's 512)
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32( const void* p )
@@ -82,11 +87,10 @@ __device__ __forceinline__ uint64_t desc_kmajor( uint32_t saddr )
 {
   return umma_desc( saddr, 16, 1024 );
 }
-// MN-major operand (V: [tokens][64 dims] regions): the next 64 dims are one region (16 KiB) further, the next 8
-// tokens 1024 B further.
+// MN-major operand (V: [keys][64 dims] regions): the next 64 dims are one region further, the next 8 keys 1024 B.
 __device__ __forceinline__ uint64_t desc_mnmajor( uint32_t saddr )
 {
-  return umma_desc( saddr, kHalf, 1024 );
+  return umma_desc( saddr, kKRegion, 1024 );
 }
 
 __device__ __forceinline__ void umma_f16( uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate )
@@ -145,21 +149,22 @@ __device__ __forceinline__ float fast_exp2( float x )
 // One work item = (context, query block): `split` is the query block's index, t_end the number of keys its last
 // token sees.  Thread r of the block owns row r = (token r / group, head r % group) of the query block.
 template<typename T>
-__global__ void __launch_bounds__( kRows, 1 )
+__global__ void __launch_bounds__( kRows, 2 )
   prefill_umma_kernel( const DecodeArgs a, const __grid_constant__ CUtensorMap kv_map )
 {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_kv[2]; // K (and V) tile landed in stage s
-  __shared__ uint64_t bar_s;     // S = Q K^T of the current tile is in TMEM
-  __shared__ uint64_t bar_pv;    // O += P V of the current tile has finished (P, V stage and S may be reused)
+  __shared__ uint64_t bar_k[2]; // K tile landed in stage s
+  __shared__ uint64_t bar_v;    // V tile landed
+  __shared__ uint64_t bar_s;    // S = Q K^T of the current tile is in TMEM
+  __shared__ uint64_t bar_pv;   // O += P V of the current tile has finished (P, V and S may be reused)
   __shared__ uint32_t tmem_base;
   __shared__ int sm_fail;
 
   uint8_t* base = reinterpret_cast<uint8_t*>( ( reinterpret_cast<uintptr_t>( smem_raw ) + 1023 ) & ~uintptr_t( 1023 ) );
   uint8_t* sQ = base;
-  uint8_t* sP = base + kTileBytes;
-  uint8_t* sK = base + 2 * kTileBytes; // two stages
-  uint8_t* sV = base + 4 * kTileBytes; // two stages
+  uint8_t* sP = base + kOffP;
+  uint8_t* sK = base + kOffK; // two stages
+  uint8_t* sV = base + kOffV;
 
   const Shape& sh = a.sh;
   const int group = sh.group;
@@ -182,8 +187,9 @@ __global__ void __launch_bounds__( kRows, 1 )
 
   if ( r == 0 ) {
     sm_fail = 0;
-    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_kv[0] ) ) );
-    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_kv[1] ) ) );
+    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_k[0] ) ) );
+    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_k[1] ) ) );
+    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_v ) ) );
     asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_s ) ) );
     asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_pv ) ) );
     asm volatile( "fence.mbarrier_init.release.cluster;" ::: "memory" );
@@ -206,7 +212,7 @@ __global__ void __launch_bounds__( kRows, 1 )
       uint4 v = make_uint4( 0, 0, 0, 0 );
       if ( row_live )
         v = *reinterpret_cast<const uint4*>( qrow + ch * 8 );
-      *reinterpret_cast<uint4*>( sQ + ( ch >> 3 ) * kHalf + r * 128 + ( ( ( ch & 7 ) ^ ( r & 7 ) ) << 4 ) ) = v;
+      *reinterpret_cast<uint4*>( sQ + ( ch >> 3 ) * kQRegion + r * 128 + ( ( ( ch & 7 ) ^ ( r & 7 ) ) << 4 ) ) = v;
     }
   }
   asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" );
@@ -217,69 +223,69 @@ __global__ void __launch_bounds__( kRows, 1 )
   const uint32_t tmem_o = tmem_base + 128;
   const uint32_t lane_off = static_cast<uint32_t>( warp * 32 ) << 16; // this warp's quarter of the TMEM lanes
 
-  constexpr uint32_t fmt = sizeof( T ) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-  // instruction descriptors: fp32 accumulate, A/B format, M = 128, N = 128; V is the MN-major B operand
-  const uint32_t idesc_s = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( ( 128u >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
-  const uint32_t idesc_pv = idesc_s | ( 1u << 16 );
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  // instruction descriptors: fp32 accumulate, A/B format, M = 128; S has N = 64 keys, O has N = 128 dims with V as
+  // the MN-major B operand
+  const uint32_t idesc_s = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( ( (uint32_t)kKeys >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
+  const uint32_t idesc_pv = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( 1u << 16 ) | ( ( 128u >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
 
   const long long row_bytes = (long long)sh.row_elems * (long long)sizeof( T );
   const int arena_row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / row_bytes );
   const int xk = kvh * kHS, xv = (int)sh.kv_dim + kvh * kHS;
 
-  // Issues the TMA loads of key tile t into stage t & 1 (thread 0 only).  Only boxes holding at least one live key
-  // are fetched: rows beyond may lie in pages that are not mapped.
-  auto load_tile = [&]( int t, bool with_v ) {
-    const int s = t & 1;
+  // TMA loads of key tile t (thread 0 only).  Only boxes holding at least one live key are fetched: rows beyond may
+  // lie in pages that are not mapped.
+  auto load_tile = [&]( int t, uint8_t* dst, int x, uint64_t* bar ) {
     const int live = min( kKeys, n_keys - t * kKeys );
     const int boxes = ( live + kBoxRows - 1 ) / kBoxRows;
-    const uint32_t bytes = static_cast<uint32_t>( boxes ) * kBoxRows * 128 * 2 * ( with_v ? 2 : 1 );
-    asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( &bar_kv[s] ) ), "r"( bytes )
+    asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar ) ),
+                  "r"( (uint32_t)boxes * kBoxRows * 128 * 2 )
                   : "memory" );
     for ( int j = 0; j < boxes; j++ ) {
       const int y = arena_row0 + t * kKeys + j * kBoxRows;
-      uint8_t* k_dst = sK + s * kTileBytes + j * kBoxRows * 128;
-      tma_load_2d( k_dst, &kv_map, xk, y, &bar_kv[s] );
-      tma_load_2d( k_dst + kHalf, &kv_map, xk + 64, y, &bar_kv[s] );
-      if ( with_v ) {
-        uint8_t* v_dst = sV + s * kTileBytes + j * kBoxRows * 128;
-        tma_load_2d( v_dst, &kv_map, xv, y, &bar_kv[s] );
-        tma_load_2d( v_dst + kHalf, &kv_map, xv + 64, y, &bar_kv[s] );
-      }
+      tma_load_2d( dst + j * kBoxRows * 128, &kv_map, x, y, bar );
+      tma_load_2d( dst + kKRegion + j * kBoxRows * 128, &kv_map, x + 64, y, bar );
     }
   };
+  auto load_k = [&]( int t ) { load_tile( t, sK + ( t & 1 ) * kKTile, xk, &bar_k[t & 1] ); };
+  auto load_v = [&]( int t ) { load_tile( t, sV, xv, &bar_v ); };
   // S = Q K_tile^T: 8 MMAs of 16 dims each (thread 0 only)
   auto issue_s = [&]( int s ) {
 #pragma unroll
     for ( int k = 0; k < 8; k++ ) {
-      const uint32_t off = ( k >> 2 ) * kHalf + ( k & 3 ) * 32;
-      umma_f16( tmem_s, desc_kmajor( smem_u32( sQ + off ) ), desc_kmajor( smem_u32( sK + s * kTileBytes + off ) ), idesc_s,
-                k > 0 ? 1u : 0u );
+      const uint64_t da = desc_kmajor( smem_u32( sQ + ( k >> 2 ) * kQRegion + ( k & 3 ) * 32 ) );
+      const uint64_t db = desc_kmajor( smem_u32( sK + s * kKTile + ( k >> 2 ) * kKRegion + ( k & 3 ) * 32 ) );
+      umma_f16( tmem_s, da, db, idesc_s, k > 0 ? 1u : 0u );
     }
     umma_commit( &bar_s );
   };
+  // thread 0: wait for K tile t, then S; on a timeout raise the flag and release the waiters
+  auto k_then_s = [&]( int t, uint32_t parity ) {
+    if ( mbar_wait( &bar_k[t & 1], parity ) ) {
+      asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+      issue_s( t & 1 );
+    } else {
+      sm_fail = 1;
+      asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_s ) ) : "memory" );
+    }
+  };
 
-  uint32_t kv_uses[2] = { 0, 0 }; // completed phases of bar_kv[s], tracked identically by every thread
-  uint32_t s_phase = 0, pv_phase = 0;
+  uint32_t k_uses[2] = { 0, 0 }; // completed phases of the barriers, tracked identically by every thread
+  uint32_t v_uses = 0, s_phase = 0, pv_phase = 0;
   bool ok = true;
 
   // ================= pass 1: row maxima =================
   float m = -INFINITY;
   if ( r == 0 )
-    load_tile( 0, false );
+    load_k( 0 );
   for ( int t = 0; t < n_tiles && ok; t++ ) {
     const int s = t & 1;
     if ( r == 0 ) {
       if ( t + 1 < n_tiles )
-        load_tile( t + 1, false ); // its stage was last read by tile t-1's MMAs, which have completed
-      if ( mbar_wait( &bar_kv[s], kv_uses[s] & 1 ) ) {
-        asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-        issue_s( s );
-      } else {
-        sm_fail = 1;
-        asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_s ) ) : "memory" );
-      }
+        load_k( t + 1 ); // its stage was last read by tile t-1's MMAs, which have completed
+      k_then_s( t, k_uses[s] & 1 );
     }
-    kv_uses[s]++;
+    k_uses[s]++;
     ok = mbar_wait( &bar_s, s_phase & 1 );
     s_phase++;
     asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
@@ -288,7 +294,7 @@ __global__ void __launch_bounds__( kRows, 1 )
       // tcgen05.ld is a warp-wide instruction: the decision to load a column block is made per warp
       const int warp_lim = __reduce_max_sync( 0xffffffffu, lim );
 #pragma unroll 1
-      for ( int cb = 0; cb < 4; cb++ ) {
+      for ( int cb = 0; cb < kKeys / 32; cb++ ) {
         if ( cb * 32 >= warp_lim )
           break;
         float v[32];
@@ -306,27 +312,22 @@ __global__ void __launch_bounds__( kRows, 1 )
   const float m_use = ( m == -INFINITY ) ? 0.f : m; // a row that sees nothing carries zeros, not NaNs
   float l = 0.f;
   if ( ok && r == 0 )
-    load_tile( 0, true );
+    load_k( 0 );
   for ( int t = 0; t < n_tiles && ok; t++ ) {
     const int s = t & 1;
-    // P, the other V stage and S are free once tile t-1's P.V has finished
+    // P, V and S are free once tile t-1's P.V has finished
     if ( t > 0 ) {
       ok = mbar_wait( &bar_pv, pv_phase & 1 );
       pv_phase++;
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
     }
     if ( r == 0 && ok ) {
+      load_v( t );
       if ( t + 1 < n_tiles )
-        load_tile( t + 1, true );
-      if ( mbar_wait( &bar_kv[s], kv_uses[s] & 1 ) ) {
-        asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-        issue_s( s );
-      } else {
-        sm_fail = 1;
-        asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_s ) ) : "memory" );
-      }
+        load_k( t + 1 );
+      k_then_s( t, k_uses[s] & 1 );
     }
-    kv_uses[s]++;
+    k_uses[s]++;
     if ( ok ) {
       ok = mbar_wait( &bar_s, s_phase & 1 );
       s_phase++;
@@ -335,18 +336,8 @@ __global__ void __launch_bounds__( kRows, 1 )
     if ( __all_sync( 0xffffffffu, ok && sm_fail == 0 ) ) {
       const int lim = row_limit - t * kKeys;
       const int warp_lim = __reduce_max_sync( 0xffffffffu, lim );
-      const int live = min( kKeys, n_keys - t * kKeys ); // keys of this tile that exist at all
-      // V rows past the last key hold stale or foreign data: clear them so that 0 * garbage cannot make a NaN
-      if ( r >= live ) {
-        uint8_t* v0 = sV + s * kTileBytes + r * 128;
-#pragma unroll
-        for ( int ch = 0; ch < 8; ch++ ) {
-          *reinterpret_cast<uint4*>( v0 + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
-          *reinterpret_cast<uint4*>( v0 + kHalf + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
-        }
-      }
 #pragma unroll 1
-      for ( int cb = 0; cb < 4; cb++ ) {
+      for ( int cb = 0; cb < kKeys / 32; cb++ ) {
         float v[32];
         if ( cb * 32 < warp_lim ) {
           tmem_ld32( tmem_s + lane_off + cb * 32, v );
@@ -366,21 +357,33 @@ __global__ void __launch_bounds__( kRows, 1 )
         // 32 keys = 4 chunks of 8 keys (16 B) of row r in P's K-major swizzled layout
 #pragma unroll
         for ( int q4 = 0; q4 < 4; q4++ ) {
-          const int ch = cb * 4 + q4; // chunk index 0..15 along the 128 keys
-          *reinterpret_cast<uint4*>( sP + ( ch >> 3 ) * kHalf + r * 128 + ( ( ( ch & 7 ) ^ ( r & 7 ) ) << 4 ) )
+          const int ch = cb * 4 + q4; // chunk index 0..7 along the 64 keys
+          *reinterpret_cast<uint4*>( sP + r * 128 + ( ( ch ^ ( r & 7 ) ) << 4 ) )
             = make_uint4( pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3] );
         }
       }
+      // V rows past the last key hold stale or foreign data: clear them so that 0 * garbage cannot make a NaN
+      ok = mbar_wait( &bar_v, v_uses & 1 );
+      const int live = min( kKeys, n_keys - t * kKeys ); // keys of this tile that exist at all
+      if ( ok && r >= live && r < kKeys ) {
+        uint8_t* v0 = sV + r * 128;
+#pragma unroll
+        for ( int ch = 0; ch < 8; ch++ ) {
+          *reinterpret_cast<uint4*>( v0 + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
+          *reinterpret_cast<uint4*>( v0 + kKRegion + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
+        }
+      }
     }
+    v_uses++;
     asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" ); // P and the cleared V rows -> tensor-core proxy
     asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
     ok = __syncthreads_and( ok && sm_fail == 0 ) != 0;
     if ( ok && r == 0 ) {
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
 #pragma unroll
-      for ( int k = 0; k < 8; k++ ) { // 16 keys per MMA
-        const uint64_t da = desc_kmajor( smem_u32( sP + ( k >> 2 ) * kHalf + ( k & 3 ) * 32 ) );
-        const uint64_t db = desc_mnmajor( smem_u32( sV + s * kTileBytes + k * 16 * 128 ) );
+      for ( int k = 0; k < kKeys / 16; k++ ) { // 16 keys per MMA
+        const uint64_t da = desc_kmajor( smem_u32( sP + k * 32 ) );
+        const uint64_t db = desc_mnmajor( smem_u32( sV + k * 16 * 128 ) );
         umma_f16( tmem_o, da, db, idesc_pv, ( t > 0 || k > 0 ) ? 1u : 0u );
       }
       umma_commit( &bar_pv );
