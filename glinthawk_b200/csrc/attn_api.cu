@@ -798,7 +798,7 @@ int gh_attn_prefill_chunk( gh_attn_t h,
   }
 
   // 2a. tensor-core kernels: consecutive tokens of a context share one block per kv head, so they share every K/V
-  //     fetch.  Work item = (context, token group), never cut, longest prefix first.  The tcgen05 kernel packs
+  //     fetch.  Work item = (context, token group), never cut.  The tcgen05 kernel packs
   //     128 / group tokens into a block; the warp-level kernel in chunk mode packs 16 / group (kept for comparison
   //     runs: GLINTHAWK_PREFILL=mma).
   static const bool prefer_warp_mma = [] {
@@ -821,7 +821,15 @@ int gh_attn_prefill_chunk( gh_attn_t h,
         items.push_back( w );
       }
     }
-    std::stable_sort( items.begin(), items.end(), []( const WorkItem& x, const WorkItem& y ) { return x.t_end > y.t_end; } );
+    // Contexts with the longest prefix first, and the query blocks of one context next to each other (longest
+    // first): blocks that run at the same time then read the same few contexts' K/V rows, which stay in L2.
+    std::stable_sort( items.begin(), items.end(), [&]( const WorkItem& x, const WorkItem& y ) {
+      if ( x.ctx != y.ctx ) {
+        const uint32_t px = pos0[x.ctx], py = pos0[y.ctx];
+        return px != py ? px > py : x.ctx < y.ctx;
+      }
+      return x.t_end > y.t_end;
+    } );
     for ( auto& c : base )
       c.nsplits = 1;
     for ( size_t i0 = 0; i0 < items.size(); i0 += h->max_items ) {

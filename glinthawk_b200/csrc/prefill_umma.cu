@@ -14,10 +14,15 @@
 //                                                     memory as the next MMA's A operand
 //   O[128 x 128] += P[128 x 64 keys] . V_tile         tcgen05.mma, V is the MN-major B operand straight from the tile
 //
-// Two passes over the keys: the first only finds each row's maximum m, the second accumulates with that final
-// maximum, so O in TMEM never has to be rescaled.  Tensor work doubles for S, which costs little here; K is read
-// twice, through L2.  fp32 accumulation throughout; P is rounded to the storage type (as in the decode kernel).
-// 96 KiB of shared memory and 256 TMEM columns per block: two blocks per SM overlap each other's phases.
+// One pass over the keys with a running row maximum m.  O lives in TMEM, so raising m means rescaling O there
+// (tcgen05.ld, multiply, tcgen05.st); that is done lazily, only when some row of a warp has outgrown its m by more
+// than 2^8, so P stays below 256 (exact enough in fp16 and bf16, harmless in the fp32 accumulator) and on typical data
+// only the first tiles rescale.  The pipeline per block:
+//   * K and V tiles are double-buffered; S has two TMEM buffers: S of tile t+1 is issued before the threads start
+//     the softmax of tile t, and the P.V MMAs of tile t run while they work on tile t+1;
+//   * P is single-buffered: its store waits for the P.V of the previous tile, after the exponentials are done.
+// fp32 accumulation throughout; P is rounded to the storage type (as in the decode kernel).
+// 112 KiB of shared memory and 256 TMEM columns per block: two blocks per SM overlap each other's phases.
 //
 // Every wait is bounded; on expiry the kernel raises the sticky error word, frees its TMEM and leaves.
 #include <type_traits>
@@ -35,11 +40,13 @@ constexpr int kBoxRows = 32;               // token rows per TMA box of the aren
 constexpr int kQRegion = kRows * 128;      // [128 rows x 128 B] swizzled region (Q: two of them, P: one) = 16 KiB
 constexpr int kKRegion = kKeys * 128;      // [64 keys x 128 B] swizzled region (K and V tiles: two each) = 8 KiB
 constexpr int kKTile = 2 * kKRegion;       // 16 KiB
-constexpr int kOffP = 2 * kQRegion;        // shared-memory map: Q | P | K stage 0 | K stage 1 | V
+constexpr int kOffP = 2 * kQRegion;        // shared-memory map: Q | P | K stages 0, 1 | V stages 0, 1 | barriers
 constexpr int kOffK = kOffP + kQRegion;
 constexpr int kOffV = kOffK + 2 * kKTile;
-constexpr int kSmemBytes = kOffV + kKTile + 1024; // 96 KiB + alignment slack: two blocks per SM
-constexpr int kTmemCols = 256;             // S: columns 0..63, O: columns 128..255 (two blocks fill the SM's 512)
+constexpr int kOffBar = kOffV + 2 * kKTile;
+constexpr int kSmemBytes = kOffBar + 64;   // 112 KiB + barriers; no static shared memory, so two blocks fit an SM
+constexpr int kTmemCols = 256;             // S buffers: columns 0..63 and 64..127, O: columns 128..255
+constexpr float kGrowLog2 = 8.f;           // a row's maximum may lag its true maximum by this much (log2 units)
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32( const void* p )
@@ -123,6 +130,24 @@ __device__ __forceinline__ void tmem_ld32( uint32_t taddr, float ( &v )[32] )
     v[i] = __uint_as_float( r[i] );
 }
 
+// Write 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st32( uint32_t taddr, const float ( &v )[32] )
+{
+  uint32_t r[32];
+#pragma unroll
+  for ( int i = 0; i < 32; i++ )
+    r[i] = __float_as_uint( v[i] );
+  asm volatile( "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                ::"r"( taddr ),
+                "r"( r[0] ), "r"( r[1] ), "r"( r[2] ), "r"( r[3] ), "r"( r[4] ), "r"( r[5] ), "r"( r[6] ), "r"( r[7] ), "r"( r[8] ),
+                "r"( r[9] ), "r"( r[10] ), "r"( r[11] ), "r"( r[12] ), "r"( r[13] ), "r"( r[14] ), "r"( r[15] ), "r"( r[16] ),
+                "r"( r[17] ), "r"( r[18] ), "r"( r[19] ), "r"( r[20] ), "r"( r[21] ), "r"( r[22] ), "r"( r[23] ), "r"( r[24] ),
+                "r"( r[25] ), "r"( r[26] ), "r"( r[27] ), "r"( r[28] ), "r"( r[29] ), "r"( r[30] ), "r"( r[31] )
+                : "memory" );
+  asm volatile( "tcgen05.wait::st.sync.aligned;" ::: "memory" );
+}
+
 template<typename T>
 __device__ __forceinline__ uint32_t pack2( float lo, float hi );
 template<>
@@ -152,19 +177,26 @@ template<typename T>
 __global__ void __launch_bounds__( kRows, 2 )
   prefill_umma_kernel( const DecodeArgs a, const __grid_constant__ CUtensorMap kv_map )
 {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_k[2]; // K tile landed in stage s
-  __shared__ uint64_t bar_v;    // V tile landed
-  __shared__ uint64_t bar_s;    // S = Q K^T of the current tile is in TMEM
-  __shared__ uint64_t bar_pv;   // O += P V of the current tile has finished (P, V and S may be reused)
-  __shared__ uint32_t tmem_base;
-  __shared__ int sm_fail;
+  extern __shared__ __align__( 1024 ) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sP = smem + kOffP;
+  uint8_t* sK = smem + kOffK; // two stages
+  uint8_t* sV = smem + kOffV; // two stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>( smem + kOffBar );
+  uint64_t* bar_k = bars;      // [2] K tile landed in stage s
+  uint64_t* bar_v = bars + 2;  // [2] V tile landed in stage s
+  uint64_t* bar_s = bars + 4;  // [2] S = Q K^T is complete in TMEM buffer b
+  uint64_t* bar_pv = bars + 6; // O += P V of a tile has finished: P, that tile's V stage and O may be touched
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>( bars + 7 );
 
-  uint8_t* base = reinterpret_cast<uint8_t*>( ( reinterpret_cast<uintptr_t>( smem_raw ) + 1023 ) & ~uintptr_t( 1023 ) );
-  uint8_t* sQ = base;
-  uint8_t* sP = base + kOffP;
-  uint8_t* sK = base + kOffK; // two stages
-  uint8_t* sV = base + kOffV;
+  const int r = threadIdx.x;
+  const int warp = r >> 5;
+  // the swizzled tiles need a 1024-byte aligned base; with no static shared memory the dynamic region starts on one
+  if ( ( smem_u32( smem ) & 1023u ) != 0 ) {
+    if ( r == 0 )
+      atomicOr( a.dev_error, 8u );
+    return;
+  }
 
   const Shape& sh = a.sh;
   const int group = sh.group;
@@ -172,8 +204,6 @@ __global__ void __launch_bounds__( kRows, 2 )
   const int kvh = blockIdx.x - item_idx * sh.n_kv_heads;
   const WorkItem it = a.items[item_idx];
   const CtxMeta c = a.ctx[it.ctx];
-  const int r = threadIdx.x;
-  const int warp = r >> 5;
 
   const int tok_per_block = kRows / group;
   const int tok0 = it.split * tok_per_block;                                // first chunk token of the query block
@@ -186,42 +216,45 @@ __global__ void __launch_bounds__( kRows, 2 )
   const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;      // 1/sqrt(128) * log2(e)
 
   if ( r == 0 ) {
-    sm_fail = 0;
-    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_k[0] ) ) );
-    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_k[1] ) ) );
-    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_v ) ) );
-    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_s ) ) );
-    asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bar_pv ) ) );
+#pragma unroll
+    for ( int i = 0; i < 7; i++ )
+      asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bars[i] ) ) );
     asm volatile( "fence.mbarrier_init.release.cluster;" ::: "memory" );
     asm volatile( "prefetch.tensormap [%0];" ::"l"( reinterpret_cast<uint64_t>( &kv_map ) ) : "memory" );
   }
   if ( warp == 0 ) {
-    asm volatile( "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"( smem_u32( &tmem_base ) ),
+    __syncwarp();
+    asm volatile( "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"( smem_u32( tmem_base_p ) ),
                   "r"( kTmemCols ) );
     asm volatile( "tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" );
   }
   // the append kernel (the kernel before this one in the stream) rotated q and wrote the chunk's K/V rows
   asm volatile( "griddepcontrol.wait;" ::: "memory" );
 
-  // ---- Q block into shared memory, K-major with the 128-byte swizzle the MMA descriptors expect
+  // ---- Q block into shared memory, K-major with the 128-byte swizzle the MMA descriptors expect.  16 threads
+  //      fetch one row (256 contiguous bytes), 8 rows per step.
   {
-    const T* qrow = static_cast<const T*>( a.q )
-                    + ( ( (size_t)it.ctx * a.chunk_tokens + tok0 + row_tok ) * sh.n_heads + (size_t)kvh * group + row_head ) * kHS;
-#pragma unroll
-    for ( int ch = 0; ch < 16; ch++ ) { // 16 chunks of 8 elements
+    const T* qbase = static_cast<const T*>( a.q )
+                     + ( ( (size_t)it.ctx * a.chunk_tokens + tok0 ) * sh.n_heads + (size_t)kvh * group ) * kHS;
+    const int ch = r & 15; // chunk of 8 elements within the row
+#pragma unroll 4
+    for ( int i = 0; i < 16; i++ ) {
+      const int row = i * 8 + ( r >> 4 );
+      const int rt = row / group, rh = row - rt * group;
       uint4 v = make_uint4( 0, 0, 0, 0 );
-      if ( row_live )
-        v = *reinterpret_cast<const uint4*>( qrow + ch * 8 );
-      *reinterpret_cast<uint4*>( sQ + ( ch >> 3 ) * kQRegion + r * 128 + ( ( ( ch & 7 ) ^ ( r & 7 ) ) << 4 ) ) = v;
+      if ( rt < n_tok )
+        v = *reinterpret_cast<const uint4*>( qbase + ( (size_t)rt * sh.n_heads + rh ) * kHS + ch * 8 );
+      *reinterpret_cast<uint4*>( sQ + ( ch >> 3 ) * kQRegion + row * 128 + ( ( ( ch & 7 ) ^ ( row & 7 ) ) << 4 ) ) = v;
     }
   }
   asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" );
   asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
   __syncthreads();
   asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-  const uint32_t tmem_s = tmem_base;
-  const uint32_t tmem_o = tmem_base + 128;
+  const uint32_t tmem_base = *tmem_base_p;
   const uint32_t lane_off = static_cast<uint32_t>( warp * 32 ) << 16; // this warp's quarter of the TMEM lanes
+  const uint32_t tmem_s = tmem_base + lane_off;                       // + 64 for the second buffer
+  const uint32_t tmem_o = tmem_base + lane_off + 128;
 
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   // instruction descriptors: fp32 accumulate, A/B format, M = 128; S has N = 64 keys, O has N = 128 dims with V as
@@ -248,154 +281,177 @@ __global__ void __launch_bounds__( kRows, 2 )
     }
   };
   auto load_k = [&]( int t ) { load_tile( t, sK + ( t & 1 ) * kKTile, xk, &bar_k[t & 1] ); };
-  auto load_v = [&]( int t ) { load_tile( t, sV, xv, &bar_v ); };
-  // S = Q K_tile^T: 8 MMAs of 16 dims each (thread 0 only)
-  auto issue_s = [&]( int s ) {
+  auto load_v = [&]( int t ) { load_tile( t, sV + ( t & 1 ) * kKTile, xv, &bar_v[t & 1] ); };
+  // S(t) = Q K_tile^T into S buffer t & 1: 8 MMAs of 16 dims each (thread 0 only)
+  auto issue_s = [&]( int t ) {
+    const int b = t & 1;
 #pragma unroll
     for ( int k = 0; k < 8; k++ ) {
       const uint64_t da = desc_kmajor( smem_u32( sQ + ( k >> 2 ) * kQRegion + ( k & 3 ) * 32 ) );
-      const uint64_t db = desc_kmajor( smem_u32( sK + s * kKTile + ( k >> 2 ) * kKRegion + ( k & 3 ) * 32 ) );
-      umma_f16( tmem_s, da, db, idesc_s, k > 0 ? 1u : 0u );
+      const uint64_t db = desc_kmajor( smem_u32( sK + b * kKTile + ( k >> 2 ) * kKRegion + ( k & 3 ) * 32 ) );
+      umma_f16( tmem_base + b * kKeys, da, db, idesc_s, k > 0 ? 1u : 0u );
     }
-    umma_commit( &bar_s );
-  };
-  // thread 0: wait for K tile t, then S; on a timeout raise the flag and release the waiters
-  auto k_then_s = [&]( int t, uint32_t parity ) {
-    if ( mbar_wait( &bar_k[t & 1], parity ) ) {
-      asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-      issue_s( t & 1 );
-    } else {
-      sm_fail = 1;
-      asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_s ) ) : "memory" );
-    }
+    umma_commit( &bar_s[b] );
   };
 
-  uint32_t k_uses[2] = { 0, 0 }; // completed phases of the barriers, tracked identically by every thread
-  uint32_t v_uses = 0, s_phase = 0, pv_phase = 0;
+  constexpr unsigned kFull = 0xffffffffu;
+  const bool t0 = r == 0;
   bool ok = true;
-
-  // ================= pass 1: row maxima =================
-  float m = -INFINITY;
-  if ( r == 0 )
+  if ( t0 ) {
     load_k( 0 );
-  for ( int t = 0; t < n_tiles && ok; t++ ) {
-    const int s = t & 1;
-    if ( r == 0 ) {
-      if ( t + 1 < n_tiles )
-        load_k( t + 1 ); // its stage was last read by tile t-1's MMAs, which have completed
-      k_then_s( t, k_uses[s] & 1 );
-    }
-    k_uses[s]++;
-    ok = mbar_wait( &bar_s, s_phase & 1 );
-    s_phase++;
-    asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-    if ( __all_sync( 0xffffffffu, ok && sm_fail == 0 ) ) {
-      const int lim = row_limit - t * kKeys; // keys of this tile the row sees
-      // tcgen05.ld is a warp-wide instruction: the decision to load a column block is made per warp
-      const int warp_lim = __reduce_max_sync( 0xffffffffu, lim );
-#pragma unroll 1
-      for ( int cb = 0; cb < kKeys / 32; cb++ ) {
-        if ( cb * 32 >= warp_lim )
-          break;
-        float v[32];
-        tmem_ld32( tmem_s + lane_off + cb * 32, v );
-#pragma unroll
-        for ( int j = 0; j < 32; j++ )
-          m = fmaxf( m, ( cb * 32 + j < lim ) ? v[j] * scale_log2 : -INFINITY );
-      }
-    }
-    asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
-    ok = __syncthreads_and( ok && sm_fail == 0 ) != 0; // everyone has read S before the next MMA overwrites it
+    if ( n_tiles > 1 )
+      load_k( 1 );
+    load_v( 0 );
+    if ( mbar_wait( &bar_k[0], 0 ) )
+      issue_s( 0 );
+    else
+      ok = false;
   }
 
-  // ================= pass 2: P and O =================
-  const float m_use = ( m == -INFINITY ) ? 0.f : m; // a row that sees nothing carries zeros, not NaNs
-  float l = 0.f;
-  if ( ok && r == 0 )
-    load_k( 0 );
-  for ( int t = 0; t < n_tiles && ok; t++ ) {
-    const int s = t & 1;
-    // P, V and S are free once tile t-1's P.V has finished
+  float m = -INFINITY; // the maximum the row's exponentials are taken against (log2 units); may lag the true one
+  float l = 0.f;       // row sum of P
+#pragma unroll 1
+  for ( int t = 0; t < n_tiles; t++ ) {
+    const int b = t & 1;
+    const uint32_t ph = ( t >> 1 ) & 1;
+
+    // ---- tensor work for the next tile first: its S buffer was last read during tile t-1
+    if ( t0 && t + 1 < n_tiles ) {
+      if ( mbar_wait( &bar_k[b ^ 1], ( ( t + 1 ) >> 1 ) & 1 ) )
+        issue_s( t + 1 );
+      else
+        ok = false;
+    }
+    ok = mbar_wait( &bar_s[b], ph ) && ok;
+    asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+    if ( t0 && t + 2 < n_tiles )
+      load_k( t + 2 ); // S(t) is complete: its K stage is free
+    __syncwarp();
+
+    // ---- scores of this thread's row; tcgen05.ld is warp-wide, so whether to load a column block is decided per warp
+    const int lim = row_limit - t * kKeys; // keys of this tile the row sees
+    const int warp_lim = __reduce_max_sync( kFull, lim );
+    const bool full_tile = __all_sync( kFull, lim >= kKeys );
+    float s0[32], s1[32];
+    if ( warp_lim > 0 ) {
+      tmem_ld32( tmem_s + b * kKeys, s0 );
+    } else {
+#pragma unroll
+      for ( int j = 0; j < 32; j++ )
+        s0[j] = 0.f;
+    }
+    if ( warp_lim > 32 ) {
+      tmem_ld32( tmem_s + b * kKeys + 32, s1 );
+    } else {
+#pragma unroll
+      for ( int j = 0; j < 32; j++ )
+        s1[j] = 0.f;
+    }
+    float tmax = -INFINITY;
+    if ( full_tile ) {
+#pragma unroll
+      for ( int j = 0; j < 32; j++ )
+        tmax = fmaxf( tmax, fmaxf( s0[j], s1[j] ) );
+    } else {
+#pragma unroll
+      for ( int j = 0; j < 32; j++ ) {
+        tmax = fmaxf( tmax, j < lim ? s0[j] : -INFINITY );
+        tmax = fmaxf( tmax, 32 + j < lim ? s1[j] : -INFINITY );
+      }
+    }
+    // raise m only when some row of the warp has outgrown it by more than 2^kGrowLog2: then every row of the warp
+    // adopts its true maximum and O is rescaled below
+    const float m_new = fmaxf( m, tmax * scale_log2 );
+    const bool warp_grow = __any_sync( kFull, m_new > m + kGrowLog2 );
+    float f = 1.f;
+    if ( warp_grow ) {
+      if ( m_new > m )
+        f = fast_exp2( m - m_new ); // 0 for a row that had seen nothing
+      m = m_new;
+      l *= f;
+    }
+    const float neg_m = ( m == -INFINITY ) ? 0.f : -m; // a row that sees nothing carries zeros, not NaNs
+    uint32_t pk[32];
+    if ( full_tile ) {
+#pragma unroll
+      for ( int j = 0; j < 32; j += 2 ) {
+        const float a0 = fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ), a1 = fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) );
+        const float b0 = fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ), b1 = fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) );
+        l += ( a0 + a1 ) + ( b0 + b1 );
+        pk[j >> 1] = pack2<T>( a0, a1 );
+        pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
+      }
+    } else {
+#pragma unroll
+      for ( int j = 0; j < 32; j += 2 ) {
+        const float a0 = j < lim ? fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ) : 0.f;
+        const float a1 = j + 1 < lim ? fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) ) : 0.f;
+        const float b0 = 32 + j < lim ? fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ) : 0.f;
+        const float b1 = 33 + j < lim ? fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) ) : 0.f;
+        l += ( a0 + a1 ) + ( b0 + b1 );
+        pk[j >> 1] = pack2<T>( a0, a1 );
+        pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
+      }
+    }
+
+    // ---- P, the other V stage and O are free once the previous tile's P.V has finished
     if ( t > 0 ) {
-      ok = mbar_wait( &bar_pv, pv_phase & 1 );
-      pv_phase++;
+      ok = mbar_wait( bar_pv, ( t - 1 ) & 1 ) && ok;
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
     }
-    if ( r == 0 && ok ) {
-      load_v( t );
-      if ( t + 1 < n_tiles )
-        load_k( t + 1 );
-      k_then_s( t, k_uses[s] & 1 );
-    }
-    k_uses[s]++;
-    if ( ok ) {
-      ok = mbar_wait( &bar_s, s_phase & 1 );
-      s_phase++;
-    }
-    asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-    if ( __all_sync( 0xffffffffu, ok && sm_fail == 0 ) ) {
-      const int lim = row_limit - t * kKeys;
-      const int warp_lim = __reduce_max_sync( 0xffffffffu, lim );
+    if ( t0 && t + 1 < n_tiles )
+      load_v( t + 1 );
+    __syncwarp();
+    if ( t > 0 && warp_grow ) { // tile 0 has nothing to rescale: its first MMA overwrites O
 #pragma unroll 1
-      for ( int cb = 0; cb < kKeys / 32; cb++ ) {
-        float v[32];
-        if ( cb * 32 < warp_lim ) {
-          tmem_ld32( tmem_s + lane_off + cb * 32, v );
-        } else {
+      for ( int cb = 0; cb < 4; cb++ ) {
+        float o[32];
+        tmem_ld32( tmem_o + cb * 32, o );
 #pragma unroll
-          for ( int j = 0; j < 32; j++ )
-            v[j] = 0.f;
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for ( int j = 0; j < 32; j += 2 ) {
-          const float p0 = ( cb * 32 + j < lim ) ? fast_exp2( v[j] * scale_log2 - m_use ) : 0.f;
-          const float p1 = ( cb * 32 + j + 1 < lim ) ? fast_exp2( v[j + 1] * scale_log2 - m_use ) : 0.f;
-          l += p0 + p1;
-          pk[j >> 1] = pack2<T>( p0, p1 );
-        }
-        // 32 keys = 4 chunks of 8 keys (16 B) of row r in P's K-major swizzled layout
-#pragma unroll
-        for ( int q4 = 0; q4 < 4; q4++ ) {
-          const int ch = cb * 4 + q4; // chunk index 0..7 along the 64 keys
-          *reinterpret_cast<uint4*>( sP + r * 128 + ( ( ch ^ ( r & 7 ) ) << 4 ) )
-            = make_uint4( pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3] );
-        }
-      }
-      // V rows past the last key hold stale or foreign data: clear them so that 0 * garbage cannot make a NaN
-      ok = mbar_wait( &bar_v, v_uses & 1 );
-      const int live = min( kKeys, n_keys - t * kKeys ); // keys of this tile that exist at all
-      if ( ok && r >= live && r < kKeys ) {
-        uint8_t* v0 = sV + r * 128;
-#pragma unroll
-        for ( int ch = 0; ch < 8; ch++ ) {
-          *reinterpret_cast<uint4*>( v0 + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
-          *reinterpret_cast<uint4*>( v0 + kKRegion + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
-        }
+        for ( int j = 0; j < 32; j++ )
+          o[j] *= f;
+        tmem_st32( tmem_o + cb * 32, o );
       }
     }
-    v_uses++;
+    // 64 keys = 8 chunks of 8 keys (16 B) of row r in P's K-major swizzled layout
+#pragma unroll
+    for ( int ch = 0; ch < 8; ch++ )
+      *reinterpret_cast<uint4*>( sP + r * 128 + ( ( ch ^ ( r & 7 ) ) << 4 ) )
+        = make_uint4( pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3] );
+    // V rows past the last key hold stale or foreign data: clear them so that 0 * garbage cannot make a NaN
+    ok = mbar_wait( &bar_v[b], ph ) && ok;
+    const int live = min( kKeys, n_keys - t * kKeys ); // keys of this tile that exist at all
+    if ( r >= live && r < kKeys ) {
+      uint8_t* v0 = sV + b * kKTile + r * 128;
+#pragma unroll
+      for ( int ch = 0; ch < 8; ch++ ) {
+        *reinterpret_cast<uint4*>( v0 + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
+        *reinterpret_cast<uint4*>( v0 + kKRegion + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
+      }
+    }
     asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" ); // P and the cleared V rows -> tensor-core proxy
     asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
-    ok = __syncthreads_and( ok && sm_fail == 0 ) != 0;
-    if ( ok && r == 0 ) {
+    ok = __syncthreads_and( ok ) != 0;
+    if ( !ok )
+      break;
+    if ( t0 ) {
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
 #pragma unroll
       for ( int k = 0; k < kKeys / 16; k++ ) { // 16 keys per MMA
         const uint64_t da = desc_kmajor( smem_u32( sP + k * 32 ) );
-        const uint64_t db = desc_mnmajor( smem_u32( sV + k * 16 * 128 ) );
-        umma_f16( tmem_o, da, db, idesc_pv, ( t > 0 || k > 0 ) ? 1u : 0u );
+        const uint64_t db = desc_mnmajor( smem_u32( sV + b * kKTile + k * 16 * 128 ) );
+        umma_f16( tmem_base + 128, da, db, idesc_pv, ( t > 0 || k > 0 ) ? 1u : 0u );
       }
-      umma_commit( &bar_pv );
+      umma_commit( bar_pv );
     }
   }
 
   // ================= epilogue: O / l -> xb =================
-  if ( ok && n_tiles > 0 ) {
-    ok = mbar_wait( &bar_pv, pv_phase & 1 );
+  if ( ok ) {
+    ok = mbar_wait( bar_pv, ( n_tiles - 1 ) & 1 );
     asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
   }
-  ok = __all_sync( 0xffffffffu, ok );
+  ok = __all_sync( kFull, ok );
   if ( ok ) { // warp-uniform: the TMEM loads below are warp-wide; only the stores depend on the row
     T* out = static_cast<T*>( a.xb )
              + ( ( (size_t)it.ctx * a.chunk_tokens + tok0 + row_tok ) * sh.n_heads + (size_t)kvh * group + row_head ) * kHS;
@@ -403,7 +459,7 @@ __global__ void __launch_bounds__( kRows, 2 )
 #pragma unroll 1
     for ( int cb = 0; cb < 4; cb++ ) {
       float v[32];
-      tmem_ld32( tmem_o + lane_off + cb * 32, v );
+      tmem_ld32( tmem_o + cb * 32, v );
 #pragma unroll
       for ( int q4 = 0; q4 < 4; q4++ ) {
         uint32_t w[4];
@@ -419,8 +475,10 @@ __global__ void __launch_bounds__( kRows, 2 )
     atomicOr( a.dev_error, 4u );
   asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
   __syncthreads();
-  if ( warp == 0 )
+  if ( warp == 0 ) {
+    __syncwarp();
     asm volatile( "tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"( tmem_base ), "r"( kTmemCols ) );
+  }
 }
 
 } // namespace
@@ -441,6 +499,13 @@ cudaError_t prefill_umma_prepare()
   cudaError_t e = cudaFuncSetAttribute( prefill_umma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
   if ( e == cudaSuccess )
     e = cudaFuncSetAttribute( prefill_umma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
+  // two blocks of 112 KiB each need the largest shared-memory carve-out
+  if ( e == cudaSuccess )
+    e = cudaFuncSetAttribute( prefill_umma_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                              cudaSharedmemCarveoutMaxShared );
+  if ( e == cudaSuccess )
+    e = cudaFuncSetAttribute( prefill_umma_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                              cudaSharedmemCarveoutMaxShared );
   return e;
 }
 
