@@ -805,7 +805,33 @@ int gh_attn_prefill_chunk( gh_attn_t h,
     const char* e = std::getenv( "GLINTHAWK_PREFILL" );
     return e != nullptr && std::string( e ) == "mma";
   }();
-  const bool umma = h->use_mma && prefill_umma_supported( h->sh, h->cfg.dtype ) && !prefer_warp_mma;
+  // the tcgen05 kernel moves q and xb by TMA, which needs 16-byte aligned buffers
+  const bool umma = h->use_mma && prefill_umma_supported( h->sh, h->cfg.dtype ) && !prefer_warp_mma
+                    && ( ( reinterpret_cast<uintptr_t>( q_inout ) | reinterpret_cast<uintptr_t>( xb ) ) & 15 ) == 0;
+  CUtensorMap q_map {}, xb_map {};
+  if ( umma ) {
+    const DriverApi* api = driver_api( h->err );
+    if ( api == nullptr )
+      return GH_ERR_CUDA;
+    // [contexts][chunk tokens][heads][head_size], innermost first; one box = half the head dims of one kv head's
+    // query heads for one query block
+    const uint64_t hb = static_cast<uint64_t>( h->sh.head_size ) * h->elem;
+    const cuuint64_t dims[4] = { h->sh.head_size, h->sh.n_heads, n_tokens, n_ctx };
+    const cuuint64_t strides[3] = { hb, hb * h->sh.n_heads, hb * h->sh.n_heads * n_tokens };
+    const cuuint32_t box[4] = { 64, h->sh.group, prefill_umma_tokens_per_item( h->sh ), 1 };
+    const cuuint32_t estr[4] = { 1, 1, 1, 1 };
+    const CUtensorMapDataType dt = h->cfg.dtype == GH_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    for ( int which = 0; which < 2; which++ ) {
+      const CUresult r = api->TensorMapEncodeTiled( which == 0 ? &q_map : &xb_map, dt, 4, which == 0 ? q_inout : xb, dims,
+                                                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE );
+      if ( r != CUDA_SUCCESS ) {
+        h->err = "cuTensorMapEncodeTiled (prompt chunk): " + driver_error( api, r );
+        return GH_ERR_CUDA;
+      }
+    }
+  }
   if ( umma || ( h->use_mma && decode_mma_chunk_supported( h->sh ) ) ) {
     const uint32_t per_item = umma ? prefill_umma_tokens_per_item( h->sh ) : 16 / h->sh.group;
     std::vector<WorkItem> items;
@@ -844,7 +870,7 @@ int gh_attn_prefill_chunk( gh_attn_t h,
       DecodeArgs a = decode_args( h, idx, static_cast<uint32_t>( n ), 0, h->pool.layer_offset( layer ), q_inout, xb );
       a.chunk_tokens = n_tokens;
       if ( umma ) {
-        if ( const cudaError_t e = launch_prefill_umma( a, &h->kv_map, st, &h->stats.kernel_launches ); e != cudaSuccess )
+        if ( const cudaError_t e = launch_prefill_umma( a, &h->kv_map, &q_map, &xb_map, st, &h->stats.kernel_launches ); e != cudaSuccess )
           return cuda_fail( h, "prefill kernel launch", e );
         h->stats.last_kernel = 2;
       } else if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK ) {

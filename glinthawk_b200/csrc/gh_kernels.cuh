@@ -68,11 +68,14 @@ cudaError_t launch_decode_mma( const DecodeArgs& a, const CUtensorMap* kv_map, c
 uint32_t decode_mma_tile_tokens(); // work items start on multiples of this
 uint32_t decode_mma_box_rows();    // token rows of the TMA box the descriptor must be encoded with
 
-// tcgen05 kernel for prompt chunks: work item = (context, query block of 128 / group tokens)
+// tcgen05 kernel for prompt chunks: work item = (context, query block of 128 / group tokens).  q_map and xb_map
+// describe the chunk's q and xb buffers as [contexts][chunk tokens][heads][128] with the box
+// [1][128 / group][group][64] and the 128-byte swizzle.
 bool prefill_umma_supported( const Shape& sh, uint32_t dtype );
 uint32_t prefill_umma_tokens_per_item( const Shape& sh );
 cudaError_t prefill_umma_prepare();
-cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map, cudaStream_t st, uint64_t* launches );
+cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map, const CUtensorMap* q_map,
+                                 const CUtensorMap* xb_map, cudaStream_t st, uint64_t* launches );
 
 cudaError_t launch_scores( const ScoreArgs& a, cudaStream_t st, uint64_t* launches );  // attention_0_gemm
 cudaError_t launch_softmax( const ScoreArgs& a, cudaStream_t st, uint64_t* launches ); // attention_softmax

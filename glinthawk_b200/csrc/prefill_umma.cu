@@ -34,7 +34,8 @@ namespace gh {
 namespace {
 
 constexpr int kHS = 128;
-constexpr int kRows = 128;                 // rows of a query block = TMEM lanes
+constexpr int kRows = 128;                 // rows of a query block = TMEM lanes = row-owner threads
+constexpr int kThreads = kRows + 64;       // + the TMA warp and the MMA warp
 constexpr int kKeys = 64;                  // keys per tile
 constexpr int kBoxRows = 32;               // token rows per TMA box of the arena descriptor
 constexpr int kQRegion = kRows * 128;      // [128 rows x 128 B] swizzled region (Q: two of them, P: one) = 16 KiB
@@ -44,7 +45,7 @@ constexpr int kOffP = 2 * kQRegion;        // shared-memory map: Q | P | K stage
 constexpr int kOffK = kOffP + kQRegion;
 constexpr int kOffV = kOffK + 2 * kKTile;
 constexpr int kOffBar = kOffV + 2 * kKTile;
-constexpr int kSmemBytes = kOffBar + 64;   // 112 KiB + barriers; no static shared memory, so two blocks fit an SM
+constexpr int kSmemBytes = kOffBar + 128;  // 112 KiB + barriers; no static shared memory, so two blocks fit an SM
 constexpr int kTmemCols = 256;             // S buffers: columns 0..63 and 64..127, O: columns 128..255
 constexpr float kGrowLog2 = 8.f;           // a row's maximum may lag its true maximum by this much (log2 units)
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -54,7 +55,9 @@ __device__ __forceinline__ uint32_t smem_u32( const void* p )
   return static_cast<uint32_t>( __cvta_generic_to_shared( p ) );
 }
 
-__device__ __forceinline__ bool mbar_wait( uint64_t* bar, uint32_t parity )
+// Bounded wait on an mbarrier phase.  Gives up when the limit is reached or another role of the block has
+// raised `fail`.
+__device__ __forceinline__ bool mbar_wait( uint64_t* bar, uint32_t parity, volatile int* fail )
 {
   const uint32_t addr = smem_u32( bar );
   for ( uint32_t it = 0; it < kWaitLimit; it++ ) {
@@ -65,6 +68,8 @@ __device__ __forceinline__ bool mbar_wait( uint64_t* bar, uint32_t parity )
                   : "memory" );
     if ( done )
       return true;
+    if ( ( it & 255u ) == 255u && *fail != 0 )
+      return false;
   }
   return false;
 }
@@ -74,6 +79,22 @@ __device__ __forceinline__ void tma_load_2d( void* dst, const CUtensorMap* map, 
   asm volatile( "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                 ::"r"( smem_u32( dst ) ),
                 "l"( reinterpret_cast<uint64_t>( map ) ), "r"( x ), "r"( y ), "r"( smem_u32( bar ) )
+                : "memory" );
+}
+
+__device__ __forceinline__ void tma_load_4d( void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar )
+{
+  asm volatile( "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                ::"r"( smem_u32( dst ) ),
+                "l"( reinterpret_cast<uint64_t>( map ) ), "r"( c0 ), "r"( c1 ), "r"( c2 ), "r"( c3 ), "r"( smem_u32( bar ) )
+                : "memory" );
+}
+
+// Shared -> global; the part of the box outside the tensor is not written.
+__device__ __forceinline__ void tma_store_4d( const CUtensorMap* map, int c0, int c1, int c2, int c3, const void* src )
+{
+  asm volatile( "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+                ::"l"( reinterpret_cast<uint64_t>( map ) ), "r"( c0 ), "r"( c1 ), "r"( c2 ), "r"( c3 ), "r"( smem_u32( src ) )
                 : "memory" );
 }
 
@@ -171,11 +192,31 @@ __device__ __forceinline__ float fast_exp2( float x )
 }
 
 
+// Developer aid, compiled out unless GH_PREFILL_TRACE is defined: the three roles of one chosen block record
+// (clock, tag) pairs, read back with gh_debug_prefill_trace().
+#ifdef GH_PREFILL_TRACE
+__device__ unsigned long long g_trace[3][1024];
+__device__ int g_trace_block = 0;
+#define GH_TRACE_DECL int trace_n = 0
+#define GH_TRACE( role, tag )                                                                                          \
+  do {                                                                                                                 \
+    if ( (int)blockIdx.x == g_trace_block && trace_n < 1023 ) {                                                       \
+      g_trace[role][trace_n++] = ( static_cast<unsigned long long>( clock64() ) << 8 ) | ( tag );                      \
+      g_trace[role][trace_n] = 0;                                                                                      \
+    }                                                                                                                  \
+  } while ( 0 )
+#else
+#define GH_TRACE_DECL
+#define GH_TRACE( role, tag )
+#endif
+
 // One work item = (context, query block): `split` is the query block's index, t_end the number of keys its last
-// token sees.  Thread r of the block owns row r = (token r / group, head r % group) of the query block.
+// token sees.  Warps 0..3: thread r owns row r = (token r / group, head r % group) of the query block and does its
+// softmax; warp 4: one lane feeds the K/V stages by TMA; warp 5: one lane issues the MMAs.
 template<typename T>
-__global__ void __launch_bounds__( kRows, 2 )
-  prefill_umma_kernel( const DecodeArgs a, const __grid_constant__ CUtensorMap kv_map )
+__global__ void __launch_bounds__( kThreads, 2 )
+  prefill_umma_kernel( const DecodeArgs a, const __grid_constant__ CUtensorMap kv_map,
+                       const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap xb_map )
 {
   extern __shared__ __align__( 1024 ) uint8_t smem[];
   uint8_t* sQ = smem;
@@ -183,11 +224,16 @@ __global__ void __launch_bounds__( kRows, 2 )
   uint8_t* sK = smem + kOffK; // two stages
   uint8_t* sV = smem + kOffV; // two stages
   uint64_t* bars = reinterpret_cast<uint64_t*>( smem + kOffBar );
-  uint64_t* bar_k = bars;      // [2] K tile landed in stage s
-  uint64_t* bar_v = bars + 2;  // [2] V tile landed in stage s
-  uint64_t* bar_s = bars + 4;  // [2] S = Q K^T is complete in TMEM buffer b
-  uint64_t* bar_pv = bars + 6; // O += P V of a tile has finished: P, that tile's V stage and O may be touched
-  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>( bars + 7 );
+  uint64_t* bar_k = bars;          // [2] K tile landed in stage s                      (TMA -> MMA lane)
+  uint64_t* bar_v = bars + 2;      // [2] V tile landed in stage s                      (TMA -> MMA lane, row owners)
+  uint64_t* bar_s = bars + 4;      // [2] S = Q K^T complete in TMEM buffer b           (MMA -> row owners)
+  uint64_t* bar_kfree = bars + 6;  // [2] the MMAs reading K stage s have completed     (MMA -> TMA lane)
+  uint64_t* bar_vfree = bars + 8;  // [2] the MMAs reading V stage s have completed     (MMA -> TMA lane)
+  uint64_t* bar_pv = bars + 10;    // O += P V of a tile has completed: P and O are free (MMA -> row owners)
+  uint64_t* bar_p = bars + 11;     // all 128 row owners have written P (and read S)    (row owners -> MMA lane)
+  uint64_t* bar_q = bars + 12;     // Q block has landed                                (TMA -> MMA lane)
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>( bars + 13 );
+  volatile int* fail = reinterpret_cast<volatile int*>( bars + 14 );
 
   const int r = threadIdx.x;
   const int warp = r >> 5;
@@ -203,279 +249,338 @@ __global__ void __launch_bounds__( kRows, 2 )
   const int item_idx = blockIdx.x / sh.n_kv_heads;
   const int kvh = blockIdx.x - item_idx * sh.n_kv_heads;
   const WorkItem it = a.items[item_idx];
-  const CtxMeta c = a.ctx[it.ctx];
 
   const int tok_per_block = kRows / group;
-  const int tok0 = it.split * tok_per_block;                                // first chunk token of the query block
-  const int n_tok = min( tok_per_block, (int)a.chunk_tokens - tok0 );       // tokens the block really has
-  const int row_tok = r / group, row_head = r - row_tok * group;
-  const bool row_live = row_tok < n_tok;
-  const int n_keys = it.t_end;                                              // keys seen by the block's last token
-  const int row_limit = row_live ? n_keys - ( n_tok - 1 - row_tok ) : 0;    // keys seen by this row's token
+  const int tok0 = it.split * tok_per_block;                          // first chunk token of the query block
+  const int n_tok = min( tok_per_block, (int)a.chunk_tokens - tok0 ); // tokens the block really has
+  const int n_keys = it.t_end;                                        // keys seen by the block's last token
   const int n_tiles = ( n_keys + kKeys - 1 ) / kKeys;
-  const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;      // 1/sqrt(128) * log2(e)
 
   if ( r == 0 ) {
+    *fail = 0;
 #pragma unroll
-    for ( int i = 0; i < 7; i++ )
-      asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bars[i] ) ) );
+    for ( int i = 0; i < 13; i++ )
+      asm volatile( "mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"( smem_u32( &bars[i] ) ), "r"( i == 11 ? kRows : 1 ) );
     asm volatile( "fence.mbarrier_init.release.cluster;" ::: "memory" );
-    asm volatile( "prefetch.tensormap [%0];" ::"l"( reinterpret_cast<uint64_t>( &kv_map ) ) : "memory" );
   }
-  if ( warp == 0 ) {
-    __syncwarp();
+  if ( warp == 4 ) {
     asm volatile( "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"( smem_u32( tmem_base_p ) ),
                   "r"( kTmemCols ) );
     asm volatile( "tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" );
   }
-  // the append kernel (the kernel before this one in the stream) rotated q and wrote the chunk's K/V rows
-  asm volatile( "griddepcontrol.wait;" ::: "memory" );
-
-  // ---- Q block into shared memory, K-major with the 128-byte swizzle the MMA descriptors expect.  16 threads
-  //      fetch one row (256 contiguous bytes), 8 rows per step.
-  {
-    const T* qbase = static_cast<const T*>( a.q )
-                     + ( ( (size_t)it.ctx * a.chunk_tokens + tok0 ) * sh.n_heads + (size_t)kvh * group ) * kHS;
-    const int ch = r & 15; // chunk of 8 elements within the row
-#pragma unroll 4
-    for ( int i = 0; i < 16; i++ ) {
-      const int row = i * 8 + ( r >> 4 );
-      const int rt = row / group, rh = row - rt * group;
-      uint4 v = make_uint4( 0, 0, 0, 0 );
-      if ( rt < n_tok )
-        v = *reinterpret_cast<const uint4*>( qbase + ( (size_t)rt * sh.n_heads + rh ) * kHS + ch * 8 );
-      *reinterpret_cast<uint4*>( sQ + ( ch >> 3 ) * kQRegion + row * 128 + ( ( ( ch & 7 ) ^ ( row & 7 ) ) << 4 ) ) = v;
-    }
-  }
-  asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" );
   asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
   __syncthreads();
   asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
   const uint32_t tmem_base = *tmem_base_p;
-  const uint32_t lane_off = static_cast<uint32_t>( warp * 32 ) << 16; // this warp's quarter of the TMEM lanes
-  const uint32_t tmem_s = tmem_base + lane_off;                       // + 64 for the second buffer
-  const uint32_t tmem_o = tmem_base + lane_off + 128;
-
-  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-  // instruction descriptors: fp32 accumulate, A/B format, M = 128; S has N = 64 keys, O has N = 128 dims with V as
-  // the MN-major B operand
-  const uint32_t idesc_s = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( ( (uint32_t)kKeys >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
-  const uint32_t idesc_pv = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( 1u << 16 ) | ( ( 128u >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
-
-  const long long row_bytes = (long long)sh.row_elems * (long long)sizeof( T );
-  const int arena_row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / row_bytes );
-  const int xk = kvh * kHS, xv = (int)sh.kv_dim + kvh * kHS;
-
-  // TMA loads of key tile t (thread 0 only).  Only boxes holding at least one live key are fetched: rows beyond may
-  // lie in pages that are not mapped.
-  auto load_tile = [&]( int t, uint8_t* dst, int x, uint64_t* bar ) {
-    const int live = min( kKeys, n_keys - t * kKeys );
-    const int boxes = ( live + kBoxRows - 1 ) / kBoxRows;
-    asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar ) ),
-                  "r"( (uint32_t)boxes * kBoxRows * 128 * 2 )
-                  : "memory" );
-    for ( int j = 0; j < boxes; j++ ) {
-      const int y = arena_row0 + t * kKeys + j * kBoxRows;
-      tma_load_2d( dst + j * kBoxRows * 128, &kv_map, x, y, bar );
-      tma_load_2d( dst + kKRegion + j * kBoxRows * 128, &kv_map, x + 64, y, bar );
-    }
-  };
-  auto load_k = [&]( int t ) { load_tile( t, sK + ( t & 1 ) * kKTile, xk, &bar_k[t & 1] ); };
-  auto load_v = [&]( int t ) { load_tile( t, sV + ( t & 1 ) * kKTile, xv, &bar_v[t & 1] ); };
-  // S(t) = Q K_tile^T into S buffer t & 1: 8 MMAs of 16 dims each (thread 0 only)
-  auto issue_s = [&]( int t ) {
-    const int b = t & 1;
-#pragma unroll
-    for ( int k = 0; k < 8; k++ ) {
-      const uint64_t da = desc_kmajor( smem_u32( sQ + ( k >> 2 ) * kQRegion + ( k & 3 ) * 32 ) );
-      const uint64_t db = desc_kmajor( smem_u32( sK + b * kKTile + ( k >> 2 ) * kKRegion + ( k & 3 ) * 32 ) );
-      umma_f16( tmem_base + b * kKeys, da, db, idesc_s, k > 0 ? 1u : 0u );
-    }
-    umma_commit( &bar_s[b] );
-  };
+  // the append kernel (the kernel before this one in the stream) rotated q and wrote the chunk's K/V rows
+  asm volatile( "griddepcontrol.wait;" ::: "memory" );
 
   constexpr unsigned kFull = 0xffffffffu;
-  const bool t0 = r == 0;
-  bool ok = true;
-  if ( t0 ) {
-    load_k( 0 );
-    if ( n_tiles > 1 )
-      load_k( 1 );
-    load_v( 0 );
-    if ( mbar_wait( &bar_k[0], 0 ) )
-      issue_s( 0 );
-    else
-      ok = false;
-  }
 
-  float m = -INFINITY; // the maximum the row's exponentials are taken against (log2 units); may lag the true one
-  float l = 0.f;       // row sum of P
+  if ( warp == 4 ) {
+    // =========================== TMA lane: K/V tiles into the two stages ===========================
+    if ( r == 4 * 32 ) {
+      // The query block: box = [64 dims][group heads][128 / group tokens] of q viewed as
+      // [contexts][chunk tokens][heads][128], twice (dims 0..63, 64..127).  Its rows land in (token, head) order
+      // with the 128-byte swizzle the MMA descriptors expect; tokens past the chunk's end arrive as zeros.
+      asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar_q ) ), "r"( 2 * kQRegion )
+                    : "memory" );
+      tma_load_4d( sQ, &q_map, 0, kvh * group, tok0, it.ctx, bar_q );
+      tma_load_4d( sQ + kQRegion, &q_map, 64, kvh * group, tok0, it.ctx, bar_q );
+      const CtxMeta c = a.ctx[it.ctx];
+      const long long row_bytes = (long long)sh.row_elems * (long long)sizeof( T );
+      const int arena_row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / row_bytes );
+      const int xk = kvh * kHS, xv = (int)sh.kv_dim + kvh * kHS;
+      // Only boxes holding at least one live key are fetched: rows beyond may lie in pages that are not mapped.
+      auto load_tile = [&]( int t, uint8_t* dst, int x, uint64_t* bar ) {
+        const int live = min( kKeys, n_keys - t * kKeys );
+        const int boxes = ( live + kBoxRows - 1 ) / kBoxRows;
+        asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar ) ),
+                      "r"( (uint32_t)boxes * kBoxRows * 128 * 2 )
+                      : "memory" );
+        for ( int j = 0; j < boxes; j++ ) {
+          const int y = arena_row0 + t * kKeys + j * kBoxRows;
+          tma_load_2d( dst + j * kBoxRows * 128, &kv_map, x, y, bar );
+          tma_load_2d( dst + kKRegion + j * kBoxRows * 128, &kv_map, x + 64, y, bar );
+        }
+      };
+      auto load_k = [&]( int t ) { load_tile( t, sK + ( t & 1 ) * kKTile, xk, &bar_k[t & 1] ); };
+      auto load_v = [&]( int t ) { load_tile( t, sV + ( t & 1 ) * kKTile, xv, &bar_v[t & 1] ); };
+      GH_TRACE_DECL;
+      GH_TRACE( 1, 1 );
+      load_k( 0 );
+      if ( n_tiles > 1 )
+        load_k( 1 );
+      load_v( 0 );
+      GH_TRACE( 1, 2 );
+      // in the order the MMA lane needs them: K(t+2) once S(t) has completed, V(t+1) once P.V(t-1) has
+      bool ok = true;
+      for ( int t = 0; t < n_tiles && ok; t++ ) {
+        if ( t + 2 < n_tiles ) {
+          ok = mbar_wait( &bar_kfree[t & 1], ( t >> 1 ) & 1, fail );
+          GH_TRACE( 1, 3 );
+          if ( ok )
+            load_k( t + 2 );
+        }
+        if ( ok && t + 1 < n_tiles ) {
+          if ( t >= 1 )
+            ok = mbar_wait( &bar_vfree[( t + 1 ) & 1], ( ( t - 1 ) >> 1 ) & 1, fail );
+          GH_TRACE( 1, 4 );
+          if ( ok )
+            load_v( t + 1 );
+        }
+      }
+      if ( !ok )
+        *fail = 1;
+    }
+  } else if ( warp == 5 ) {
+    // =========================== MMA lane ===========================
+    if ( r == 5 * 32 ) {
+      constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      // instruction descriptors: fp32 accumulate, A/B format, M = 128; S has N = 64 keys, O has N = 128 dims with V
+      // as the MN-major B operand
+      const uint32_t idesc_s = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( ( (uint32_t)kKeys >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
+      const uint32_t idesc_pv = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( 1u << 16 ) | ( ( 128u >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
+      // S(t) = Q K_tile^T into S buffer t & 1: 8 MMAs of 16 dims each
+      auto issue_s = [&]( int t ) {
+        const int b = t & 1;
+#pragma unroll
+        for ( int k = 0; k < 8; k++ ) {
+          const uint64_t da = desc_kmajor( smem_u32( sQ + ( k >> 2 ) * kQRegion + ( k & 3 ) * 32 ) );
+          const uint64_t db = desc_kmajor( smem_u32( sK + b * kKTile + ( k >> 2 ) * kKRegion + ( k & 3 ) * 32 ) );
+          umma_f16( tmem_base + b * kKeys, da, db, idesc_s, k > 0 ? 1u : 0u );
+        }
+        umma_commit( &bar_s[b] );
+        umma_commit( &bar_kfree[b] );
+      };
+      GH_TRACE_DECL;
+      GH_TRACE( 2, 1 );
+      bool ok = mbar_wait( bar_q, 0, fail );
+      GH_TRACE( 2, 2 );
+      ok = ok && mbar_wait( &bar_k[0], 0, fail );
+      GH_TRACE( 2, 3 );
+      if ( ok ) {
+        asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+        issue_s( 0 );
+      }
+      for ( int t = 0; t < n_tiles && ok; t++ ) {
+        const int b = t & 1;
+        // S of the next tile first, so that the row owners find it ready; its TMEM buffer was read during tile
+        // t-1, which bar_p of that tile (waited for below, one iteration ago) covers
+        if ( t + 1 < n_tiles ) {
+          ok = mbar_wait( &bar_k[b ^ 1], ( ( t + 1 ) >> 1 ) & 1, fail );
+          if ( !ok )
+            break;
+          GH_TRACE( 2, 4 );
+          issue_s( t + 1 );
+          GH_TRACE( 2, 5 );
+        }
+        ok = mbar_wait( bar_p, t & 1, fail );
+        GH_TRACE( 2, 6 );
+        ok = ok && mbar_wait( &bar_v[b], ( t >> 1 ) & 1, fail );
+        GH_TRACE( 2, 7 );
+        if ( !ok )
+          break;
+        asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+#pragma unroll
+        for ( int k = 0; k < kKeys / 16; k++ ) { // 16 keys per MMA
+          const uint64_t da = desc_kmajor( smem_u32( sP + k * 32 ) );
+          const uint64_t db = desc_mnmajor( smem_u32( sV + b * kKTile + k * 16 * 128 ) );
+          umma_f16( tmem_base + 128, da, db, idesc_pv, ( t > 0 || k > 0 ) ? 1u : 0u );
+        }
+        umma_commit( bar_pv );
+        umma_commit( &bar_vfree[b] );
+        GH_TRACE( 2, 8 );
+      }
+      if ( !ok )
+        *fail = 1;
+    }
+  } else {
+    // =========================== row owners (warps 0..3) ===========================
+    const int row_tok = r / group;
+    const bool row_live = row_tok < n_tok;
+    const int row_limit = row_live ? n_keys - ( n_tok - 1 - row_tok ) : 0; // keys seen by this row's token
+    const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+    GH_TRACE_DECL;
+#define GH_TRACE0( tag )                                                                                               \
+  if ( r == 0 )                                                                                                        \
+  GH_TRACE( 0, tag )
+    GH_TRACE0( 1 );
+
+    const uint32_t lane_off = static_cast<uint32_t>( warp * 32 ) << 16; // this warp's quarter of the TMEM lanes
+    const uint32_t tmem_s = tmem_base + lane_off;                       // + 64 for the second buffer
+    const uint32_t tmem_o = tmem_base + lane_off + 128;
+
+    float m = -INFINITY; // the maximum the row's exponentials are taken against (log2 units); may lag the true one
+    float l = 0.f;       // row sum of P
+    bool ok = true;
 #pragma unroll 1
-  for ( int t = 0; t < n_tiles; t++ ) {
-    const int b = t & 1;
-    const uint32_t ph = ( t >> 1 ) & 1;
-
-    // ---- tensor work for the next tile first: its S buffer was last read during tile t-1
-    if ( t0 && t + 1 < n_tiles ) {
-      if ( mbar_wait( &bar_k[b ^ 1], ( ( t + 1 ) >> 1 ) & 1 ) )
-        issue_s( t + 1 );
-      else
-        ok = false;
-    }
-    ok = mbar_wait( &bar_s[b], ph ) && ok;
-    asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-    if ( t0 && t + 2 < n_tiles )
-      load_k( t + 2 ); // S(t) is complete: its K stage is free
-    __syncwarp();
-
-    // ---- scores of this thread's row; tcgen05.ld is warp-wide, so whether to load a column block is decided per warp
-    const int lim = row_limit - t * kKeys; // keys of this tile the row sees
-    const int warp_lim = __reduce_max_sync( kFull, lim );
-    const bool full_tile = __all_sync( kFull, lim >= kKeys );
-    float s0[32], s1[32];
-    if ( warp_lim > 0 ) {
-      tmem_ld32( tmem_s + b * kKeys, s0 );
-    } else {
-#pragma unroll
-      for ( int j = 0; j < 32; j++ )
-        s0[j] = 0.f;
-    }
-    if ( warp_lim > 32 ) {
-      tmem_ld32( tmem_s + b * kKeys + 32, s1 );
-    } else {
-#pragma unroll
-      for ( int j = 0; j < 32; j++ )
-        s1[j] = 0.f;
-    }
-    float tmax = -INFINITY;
-    if ( full_tile ) {
-#pragma unroll
-      for ( int j = 0; j < 32; j++ )
-        tmax = fmaxf( tmax, fmaxf( s0[j], s1[j] ) );
-    } else {
-#pragma unroll
-      for ( int j = 0; j < 32; j++ ) {
-        tmax = fmaxf( tmax, j < lim ? s0[j] : -INFINITY );
-        tmax = fmaxf( tmax, 32 + j < lim ? s1[j] : -INFINITY );
-      }
-    }
-    // raise m only when some row of the warp has outgrown it by more than 2^kGrowLog2: then every row of the warp
-    // adopts its true maximum and O is rescaled below
-    const float m_new = fmaxf( m, tmax * scale_log2 );
-    const bool warp_grow = __any_sync( kFull, m_new > m + kGrowLog2 );
-    float f = 1.f;
-    if ( warp_grow ) {
-      if ( m_new > m )
-        f = fast_exp2( m - m_new ); // 0 for a row that had seen nothing
-      m = m_new;
-      l *= f;
-    }
-    const float neg_m = ( m == -INFINITY ) ? 0.f : -m; // a row that sees nothing carries zeros, not NaNs
-    uint32_t pk[32];
-    if ( full_tile ) {
-#pragma unroll
-      for ( int j = 0; j < 32; j += 2 ) {
-        const float a0 = fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ), a1 = fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) );
-        const float b0 = fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ), b1 = fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) );
-        l += ( a0 + a1 ) + ( b0 + b1 );
-        pk[j >> 1] = pack2<T>( a0, a1 );
-        pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
-      }
-    } else {
-#pragma unroll
-      for ( int j = 0; j < 32; j += 2 ) {
-        const float a0 = j < lim ? fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ) : 0.f;
-        const float a1 = j + 1 < lim ? fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) ) : 0.f;
-        const float b0 = 32 + j < lim ? fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ) : 0.f;
-        const float b1 = 33 + j < lim ? fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) ) : 0.f;
-        l += ( a0 + a1 ) + ( b0 + b1 );
-        pk[j >> 1] = pack2<T>( a0, a1 );
-        pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
-      }
-    }
-
-    // ---- P, the other V stage and O are free once the previous tile's P.V has finished
-    if ( t > 0 ) {
-      ok = mbar_wait( bar_pv, ( t - 1 ) & 1 ) && ok;
+    for ( int t = 0; t < n_tiles; t++ ) {
+      const int b = t & 1;
+      const uint32_t ph = ( t >> 1 ) & 1;
+      ok = __all_sync( kFull, mbar_wait( &bar_s[b], ph, fail ) );
+      if ( !ok )
+        break;
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-    }
-    if ( t0 && t + 1 < n_tiles )
-      load_v( t + 1 );
-    __syncwarp();
-    if ( t > 0 && warp_grow ) { // tile 0 has nothing to rescale: its first MMA overwrites O
-#pragma unroll 1
-      for ( int cb = 0; cb < 4; cb++ ) {
-        float o[32];
-        tmem_ld32( tmem_o + cb * 32, o );
+      GH_TRACE0( 3 );
+
+      // ---- scores of this thread's row; tcgen05.ld is warp-wide, so whether to load a column block is decided per
+      //      warp
+      const int lim = row_limit - t * kKeys; // keys of this tile the row sees
+      const int warp_lim = __reduce_max_sync( kFull, lim );
+      const bool full_tile = __all_sync( kFull, lim >= kKeys );
+      float s0[32], s1[32];
+      if ( warp_lim > 0 ) {
+        tmem_ld32( tmem_s + b * kKeys, s0 );
+      } else {
 #pragma unroll
         for ( int j = 0; j < 32; j++ )
-          o[j] *= f;
-        tmem_st32( tmem_o + cb * 32, o );
+          s0[j] = 0.f;
       }
-    }
-    // 64 keys = 8 chunks of 8 keys (16 B) of row r in P's K-major swizzled layout
+      if ( warp_lim > 32 ) {
+        tmem_ld32( tmem_s + b * kKeys + 32, s1 );
+      } else {
 #pragma unroll
-    for ( int ch = 0; ch < 8; ch++ )
-      *reinterpret_cast<uint4*>( sP + r * 128 + ( ( ch ^ ( r & 7 ) ) << 4 ) )
-        = make_uint4( pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3] );
-    // V rows past the last key hold stale or foreign data: clear them so that 0 * garbage cannot make a NaN
-    ok = mbar_wait( &bar_v[b], ph ) && ok;
-    const int live = min( kKeys, n_keys - t * kKeys ); // keys of this tile that exist at all
-    if ( r >= live && r < kKeys ) {
-      uint8_t* v0 = sV + b * kKTile + r * 128;
-#pragma unroll
-      for ( int ch = 0; ch < 8; ch++ ) {
-        *reinterpret_cast<uint4*>( v0 + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
-        *reinterpret_cast<uint4*>( v0 + kKRegion + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
+        for ( int j = 0; j < 32; j++ )
+          s1[j] = 0.f;
       }
+      GH_TRACE0( 4 );
+      float tmax = -INFINITY;
+      if ( full_tile ) {
+#pragma unroll
+        for ( int j = 0; j < 32; j++ )
+          tmax = fmaxf( tmax, fmaxf( s0[j], s1[j] ) );
+      } else {
+#pragma unroll
+        for ( int j = 0; j < 32; j++ ) {
+          tmax = fmaxf( tmax, j < lim ? s0[j] : -INFINITY );
+          tmax = fmaxf( tmax, 32 + j < lim ? s1[j] : -INFINITY );
+        }
+      }
+      // raise m only when some row of the warp has outgrown it by more than 2^kGrowLog2: then every row of the warp
+      // adopts its true maximum and O is rescaled below
+      const float m_new = fmaxf( m, tmax * scale_log2 );
+      const bool warp_grow = __any_sync( kFull, m_new > m + kGrowLog2 );
+      float f = 1.f;
+      if ( warp_grow ) {
+        if ( m_new > m )
+          f = fast_exp2( m - m_new ); // 0 for a row that had seen nothing
+        m = m_new;
+        l *= f;
+      }
+      const float neg_m = ( m == -INFINITY ) ? 0.f : -m; // a row that sees nothing carries zeros, not NaNs
+      uint32_t pk[32];
+      if ( full_tile ) {
+#pragma unroll
+        for ( int j = 0; j < 32; j += 2 ) {
+          const float a0 = fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ), a1 = fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) );
+          const float b0 = fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ), b1 = fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) );
+          l += ( a0 + a1 ) + ( b0 + b1 );
+          pk[j >> 1] = pack2<T>( a0, a1 );
+          pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
+        }
+      } else {
+#pragma unroll
+        for ( int j = 0; j < 32; j += 2 ) {
+          const float a0 = j < lim ? fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ) : 0.f;
+          const float a1 = j + 1 < lim ? fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) ) : 0.f;
+          const float b0 = 32 + j < lim ? fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ) : 0.f;
+          const float b1 = 33 + j < lim ? fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) ) : 0.f;
+          l += ( a0 + a1 ) + ( b0 + b1 );
+          pk[j >> 1] = pack2<T>( a0, a1 );
+          pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
+        }
+      }
+
+      GH_TRACE0( 5 );
+      // ---- P and O are free once the previous tile's P.V has completed
+      if ( t > 0 ) {
+        ok = __all_sync( kFull, mbar_wait( bar_pv, ( t - 1 ) & 1, fail ) );
+        if ( !ok )
+          break;
+        asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+        if ( warp_grow ) { // (tile 0 has nothing to rescale: its first MMA overwrites O)
+#pragma unroll 1
+          for ( int cb = 0; cb < 4; cb++ ) {
+            float o[32];
+            tmem_ld32( tmem_o + cb * 32, o );
+#pragma unroll
+            for ( int j = 0; j < 32; j++ )
+              o[j] *= f;
+            tmem_st32( tmem_o + cb * 32, o );
+          }
+        }
+      }
+      GH_TRACE0( 6 );
+      // 64 keys = 8 chunks of 8 keys (16 B) of row r in P's K-major swizzled layout
+#pragma unroll
+      for ( int ch = 0; ch < 8; ch++ )
+        *reinterpret_cast<uint4*>( sP + r * 128 + ( ( ch ^ ( r & 7 ) ) << 4 ) )
+          = make_uint4( pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3] );
+      // V rows past the last key hold stale or foreign data: clear them so that 0 * garbage cannot make a NaN
+      const int live = min( kKeys, n_keys - t * kKeys ); // keys of this tile that exist at all
+      if ( live < kKeys ) {
+        ok = __all_sync( kFull, mbar_wait( &bar_v[b], ph, fail ) );
+        if ( !ok )
+          break;
+        if ( r >= live && r < kKeys ) {
+          uint8_t* v0 = sV + b * kKTile + r * 128;
+#pragma unroll
+          for ( int ch = 0; ch < 8; ch++ ) {
+            *reinterpret_cast<uint4*>( v0 + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
+            *reinterpret_cast<uint4*>( v0 + kKRegion + ch * 16 ) = make_uint4( 0, 0, 0, 0 );
+          }
+        }
+      }
+      asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" ); // P and the cleared V rows -> tensor-core proxy
+      asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
+      asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( bar_p ) ) : "memory" );
+      GH_TRACE0( 7 );
     }
-    asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" ); // P and the cleared V rows -> tensor-core proxy
-    asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
-    ok = __syncthreads_and( ok ) != 0;
-    if ( !ok )
-      break;
-    if ( t0 ) {
+
+    // ---- epilogue: O / l -> xb
+    if ( ok )
+      ok = __all_sync( kFull, mbar_wait( bar_pv, ( n_tiles - 1 ) & 1, fail ) );
+    GH_TRACE0( 8 );
+    if ( ok ) {
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+      // O / l goes through the Q block's shared memory (free since the last S completed), in the same row-major
+      // swizzled layout, and leaves by TMA: rows of tokens past the chunk's end are clipped by the tensor map
+      const float inv = row_live ? 1.0f / l : 0.f;
+#pragma unroll 1
+      for ( int cb = 0; cb < 4; cb++ ) {
+        float v[32];
+        tmem_ld32( tmem_o + cb * 32, v );
 #pragma unroll
-      for ( int k = 0; k < kKeys / 16; k++ ) { // 16 keys per MMA
-        const uint64_t da = desc_kmajor( smem_u32( sP + k * 32 ) );
-        const uint64_t db = desc_mnmajor( smem_u32( sV + b * kKTile + k * 16 * 128 ) );
-        umma_f16( tmem_base + 128, da, db, idesc_pv, ( t > 0 || k > 0 ) ? 1u : 0u );
+        for ( int q4 = 0; q4 < 4; q4++ ) {
+          uint32_t w[4];
+#pragma unroll
+          for ( int j = 0; j < 4; j++ )
+            w[j] = pack2<T>( v[q4 * 8 + 2 * j] * inv, v[q4 * 8 + 2 * j + 1] * inv );
+          const int ch = cb * 4 + q4; // 16-byte chunk 0..15 of the row
+          *reinterpret_cast<uint4*>( sQ + ( ch >> 3 ) * kQRegion + r * 128 + ( ( ( ch & 7 ) ^ ( r & 7 ) ) << 4 ) )
+            = make_uint4( w[0], w[1], w[2], w[3] );
+        }
       }
-      umma_commit( bar_pv );
+      asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" );
+      asm volatile( "bar.sync 1, %0;" ::"n"( kRows ) : "memory" ); // the four row-owner warps only
+      if ( r == 0 ) {
+        tma_store_4d( &xb_map, 0, kvh * group, tok0, it.ctx, sQ );
+        tma_store_4d( &xb_map, 64, kvh * group, tok0, it.ctx, sQ + kQRegion );
+        asm volatile( "cp.async.bulk.commit_group;" ::: "memory" );
+        asm volatile( "cp.async.bulk.wait_group.read 0;" ::: "memory" ); // shared memory is read out before the block ends
+      }
+    } else {
+      *fail = 1;
     }
+    GH_TRACE0( 9 );
   }
 
-  // ================= epilogue: O / l -> xb =================
-  if ( ok ) {
-    ok = mbar_wait( bar_pv, ( n_tiles - 1 ) & 1 );
-    asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-  }
-  ok = __all_sync( kFull, ok );
-  if ( ok ) { // warp-uniform: the TMEM loads below are warp-wide; only the stores depend on the row
-    T* out = static_cast<T*>( a.xb )
-             + ( ( (size_t)it.ctx * a.chunk_tokens + tok0 + row_tok ) * sh.n_heads + (size_t)kvh * group + row_head ) * kHS;
-    const float inv = 1.0f / l;
-#pragma unroll 1
-    for ( int cb = 0; cb < 4; cb++ ) {
-      float v[32];
-      tmem_ld32( tmem_o + cb * 32, v );
-#pragma unroll
-      for ( int q4 = 0; q4 < 4; q4++ ) {
-        uint32_t w[4];
-#pragma unroll
-        for ( int j = 0; j < 4; j++ )
-          w[j] = pack2<T>( v[q4 * 8 + 2 * j] * inv, v[q4 * 8 + 2 * j + 1] * inv );
-        if ( row_live )
-          *reinterpret_cast<uint4*>( out + cb * 32 + q4 * 8 ) = make_uint4( w[0], w[1], w[2], w[3] );
-      }
-    }
-  }
-  if ( !ok && r == 0 )
-    atomicOr( a.dev_error, 4u );
   asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
   __syncthreads();
-  if ( warp == 0 ) {
+  if ( r == 0 && *fail != 0 )
+    atomicOr( a.dev_error, 4u );
+  if ( warp == 4 ) {
     __syncwarp();
     asm volatile( "tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"( tmem_base ), "r"( kTmemCols ) );
   }
@@ -509,13 +614,14 @@ cudaError_t prefill_umma_prepare()
   return e;
 }
 
-cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map, cudaStream_t st, uint64_t* launches )
+cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map, const CUtensorMap* q_map,
+                                 const CUtensorMap* xb_map, cudaStream_t st, uint64_t* launches )
 {
   if ( a.n_items == 0 )
     return cudaSuccess;
   cudaLaunchConfig_t cfg {};
   cfg.gridDim = dim3( a.n_items * a.sh.n_kv_heads );
-  cfg.blockDim = dim3( kRows );
+  cfg.blockDim = dim3( kThreads );
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = st;
   cudaLaunchAttribute attr {};
@@ -525,9 +631,9 @@ cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map,
   cfg.numAttrs = 1;
   cudaError_t e;
   if ( a.dtype == DT_F16 )
-    e = cudaLaunchKernelEx( &cfg, prefill_umma_kernel<__half>, a, *kv_map );
+    e = cudaLaunchKernelEx( &cfg, prefill_umma_kernel<__half>, a, *kv_map, *q_map, *xb_map );
   else if ( a.dtype == DT_BF16 )
-    e = cudaLaunchKernelEx( &cfg, prefill_umma_kernel<__nv_bfloat16>, a, *kv_map );
+    e = cudaLaunchKernelEx( &cfg, prefill_umma_kernel<__nv_bfloat16>, a, *kv_map, *q_map, *xb_map );
   else
     return cudaErrorInvalidValue;
   ( *launches )++;
@@ -535,3 +641,16 @@ cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map,
 }
 
 } // namespace gh
+
+#ifdef GH_PREFILL_TRACE
+// out: 3 x 1024 words of (clock << 8 | tag), zero-terminated per role; block = the block to trace next
+extern "C" int gh_debug_prefill_trace( unsigned long long* out, int block )
+{
+  cudaError_t e = cudaDeviceSynchronize();
+  if ( e == cudaSuccess )
+    e = cudaMemcpyFromSymbol( out, gh::g_trace, sizeof( gh::g_trace ) );
+  if ( e == cudaSuccess )
+    e = cudaMemcpyToSymbol( gh::g_trace_block, &block, sizeof( int ) );
+  return static_cast<int>( e );
+}
+#endif
