@@ -95,6 +95,81 @@ __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
   }
 }
 
+// Prompt chunks: the same arithmetic, but one thread carries its 16-byte unit through TB consecutive tokens of a
+// context with all of their loads in flight together.  A chunk moves hundreds of MB, so it is bandwidth-bound
+// work, and one unit per thread (as above) would leave each block with too little to hide its start-up behind.
+template<typename T, int TB>
+__global__ void __launch_bounds__( 256 ) append_chunk_kernel( const AppendArgs a )
+{
+  constexpr int N = Vec16<T>::N;
+  const Shape& sh = a.sh;
+  const int blocks_per_ctx = ( a.tokens_per_ctx + TB - 1 ) / TB;
+  const int i = blockIdx.x / blocks_per_ctx;                 // context
+  const int tk0 = ( blockIdx.x - i * blocks_per_ctx ) * TB;  // first token of the chunk this block handles
+  asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
+  const CtxMeta c = a.ctx[i];
+  if ( c.kv_off == kInactive )
+    return;
+  const int n_tok = min( TB, (int)a.tokens_per_ctx - tk0 );
+
+  // units of a token, each a 16-byte chunk, in address order so that a warp touches consecutive bytes:
+  // K chunks | q chunks (every head) | V chunks
+  const int k_chunks = sh.kv_dim / N;
+  const int q_chunks = a.q != nullptr ? (int)( sh.n_heads * sh.head_size ) / N : 0;
+  const int u = blockIdx.y * blockDim.x + threadIdx.x;
+  if ( u >= 2 * k_chunks + q_chunks )
+    return;
+
+  const size_t in_row0 = (size_t)i * a.tokens_per_ctx + tk0; // row of q and kv_new: [context][token]
+  const uint32_t pos0 = c.pos + tk0;
+  T* row0 = reinterpret_cast<T*>( a.arena + c.kv_off + a.layer_off ) + (size_t)pos0 * sh.row_elems;
+  const T* src0 = static_cast<const T*>( a.kv_new ) + in_row0 * sh.row_elems;
+
+  if ( u >= k_chunks + q_chunks ) { // V: plain copy
+    const int e = sh.kv_dim + ( u - k_chunks - q_chunks ) * N;
+    Vec16<T> x[TB];
+#pragma unroll
+    for ( int t = 0; t < TB; t++ )
+      if ( t < n_tok )
+        x[t] = ld16( src0 + (size_t)t * sh.row_elems + e );
+#pragma unroll
+    for ( int t = 0; t < TB; t++ )
+      if ( t < n_tok )
+        st16( row0 + (size_t)t * sh.row_elems + e, x[t] );
+    return;
+  }
+  const size_t q_row = (size_t)sh.n_heads * sh.head_size;
+  const T* from;  // token t's chunk is at from + t * from_stride, and goes to to + t * to_stride
+  T* to;
+  size_t from_stride, to_stride;
+  int e; // element offset inside the K half of the row, or inside the token's q
+  if ( u < k_chunks ) {
+    e = u * N;
+    from = src0 + e, from_stride = sh.row_elems;
+    to = row0 + e, to_stride = sh.row_elems;
+  } else {
+    e = ( u - k_chunks ) * N;
+    to = static_cast<T*>( a.q ) + in_row0 * q_row + e;
+    from = to, from_stride = to_stride = q_row;
+  }
+  const int d = e % (int)sh.head_size; // first dimension of the chunk within its head, even
+  const T* cs0 = static_cast<const T*>( a.rope_cos ) + (size_t)pos0 * ( sh.head_size / 2 ) + d / 2;
+  const T* sn0 = static_cast<const T*>( a.rope_sin ) + (size_t)pos0 * ( sh.head_size / 2 ) + d / 2;
+  Vec16<T> x[TB], cs[TB], sn[TB];
+#pragma unroll
+  for ( int t = 0; t < TB; t++ )
+    if ( t < n_tok ) {
+      x[t] = ld16( from + (size_t)t * from_stride );
+      // the chunk's N / 2 rotation pairs: 8 bytes of each table
+      *reinterpret_cast<uint2*>( &cs[t] ) = *reinterpret_cast<const uint2*>( cs0 + (size_t)t * ( sh.head_size / 2 ) );
+      *reinterpret_cast<uint2*>( &sn[t] ) = *reinterpret_cast<const uint2*>( sn0 + (size_t)t * ( sh.head_size / 2 ) );
+    }
+#pragma unroll
+  for ( int t = 0; t < TB; t++ )
+    if ( t < n_tok )
+      st16( to + (size_t)t * to_stride, rotate_chunk( x[t], cs[t].v, sn[t].v ) );
+}
+
 } // namespace
 
 cudaError_t launch_append( const AppendArgs& args, cudaStream_t st, uint64_t* launches )
@@ -108,6 +183,20 @@ cudaError_t launch_append( const AppendArgs& args, cudaStream_t st, uint64_t* la
   const unsigned n16 = a.dtype == DT_F32 ? 4 : 8;
   const unsigned units = ( a.sh.kv_dim / n16 ) * ( 2 + a.sh.group );
   const unsigned tokens = a.tokens_per_ctx > 0 ? a.tokens_per_ctx : 1;
+  // prompt chunks with rotation, new rows and the arena's own slots (what the chunk entry point passes)
+  constexpr int TB = 8;
+  if ( tokens >= TB && a.token_rows == nullptr && a.kv_new != nullptr && a.rope_cos != nullptr ) {
+    const unsigned cunits = 2 * ( a.sh.kv_dim / n16 ) + ( a.q != nullptr ? a.sh.n_heads * a.sh.head_size / n16 : 0 );
+    const dim3 cgrid( a.batch * ( ( tokens + TB - 1 ) / TB ), ( cunits + 255 ) / 256 );
+    switch ( a.dtype ) {
+      case DT_F32: append_chunk_kernel<float, TB><<<cgrid, 256, 0, st>>>( a ); break;
+      case DT_F16: append_chunk_kernel<__half, TB><<<cgrid, 256, 0, st>>>( a ); break;
+      case DT_BF16: append_chunk_kernel<__nv_bfloat16, TB><<<cgrid, 256, 0, st>>>( a ); break;
+      default: return cudaErrorInvalidValue;
+    }
+    ( *launches )++;
+    return cudaGetLastError();
+  }
   const dim3 grid( a.batch * tokens, ( units + 255 ) / 256 );
   switch ( a.dtype ) {
     case DT_F32: append_kernel<float><<<grid, 256, 0, st>>>( a ); break;

@@ -10,19 +10,23 @@
 // tiles of 64 tokens, staged by TMA (same arena descriptor and 128-byte swizzle as the decode kernel):
 //
 //   S[128 x 64]   = Q[128 x 128 dims] . K_tile^T      tcgen05.mma, both operands K-major in shared memory -> TMEM
-//   P             = 2^(S * scale - m), causal mask    one thread per row (tcgen05.ld), no shuffles; written to shared
-//                                                     memory as the next MMA's A operand
-//   O[128 x 128] += P[128 x 64 keys] . V_tile         tcgen05.mma, V is the MN-major B operand straight from the tile
+//   P             = 2^(S * scale - m), causal mask    one thread per row (tcgen05.ld), no shuffles; stored back over
+//                                                     S in TMEM (tcgen05.st), 16 bits per key
+//   O[128 x 128] += P[128 x 64 keys] . V_tile         tcgen05.mma with A = P from TMEM, V the MN-major B operand
+//                                                     straight from the tile
+//
+// Three roles: warps 0..3 own one score row per thread; one lane of warp 4 feeds the K/V stages (and the Q block)
+// by TMA; one lane of warp 5 issues the MMAs.  They meet only on mbarriers.
 //
 // One pass over the keys with a running row maximum m.  O lives in TMEM, so raising m means rescaling O there
 // (tcgen05.ld, multiply, tcgen05.st); that is done lazily, only when some row of a warp has outgrown its m by more
 // than 2^8, so P stays below 256 (exact enough in fp16 and bf16, harmless in the fp32 accumulator) and on typical data
-// only the first tiles rescale.  The pipeline per block:
-//   * K and V tiles are double-buffered; S has two TMEM buffers: S of tile t+1 is issued before the threads start
-//     the softmax of tile t, and the P.V MMAs of tile t run while they work on tile t+1;
-//   * P is single-buffered: its store waits for the P.V of the previous tile, after the exponentials are done.
-// fp32 accumulation throughout; P is rounded to the storage type (as in the decode kernel).
-// 112 KiB of shared memory and 256 TMEM columns per block: two blocks per SM overlap each other's phases.
+// only the first tiles rescale.  K and V tiles are double-buffered and S has two TMEM buffers: S of tile t+1 is
+// issued before the row owners start on tile t, and the P.V MMAs of tile t run while they work on tile t+1.  Keeping
+// P out of shared memory matters: the MMAs' operand reads, not their arithmetic, are what fills the SM here.
+// fp32 accumulation throughout; P is rounded to the storage type (as in the decode kernel).  The finished O block
+// leaves through the Q block's shared memory and a TMA store.
+// 96 KiB of shared memory and 256 TMEM columns per block: two blocks per SM overlap each other's phases.
 //
 // Every wait is bounded; on expiry the kernel raises the sticky error word, frees its TMEM and leaves.
 #include <type_traits>
@@ -38,14 +42,13 @@ constexpr int kRows = 128;                 // rows of a query block = TMEM lanes
 constexpr int kThreads = kRows + 64;       // + the TMA warp and the MMA warp
 constexpr int kKeys = 64;                  // keys per tile
 constexpr int kBoxRows = 32;               // token rows per TMA box of the arena descriptor
-constexpr int kQRegion = kRows * 128;      // [128 rows x 128 B] swizzled region (Q: two of them, P: one) = 16 KiB
+constexpr int kQRegion = kRows * 128;      // [128 rows x 128 B] swizzled region (Q: two of them) = 16 KiB
 constexpr int kKRegion = kKeys * 128;      // [64 keys x 128 B] swizzled region (K and V tiles: two each) = 8 KiB
 constexpr int kKTile = 2 * kKRegion;       // 16 KiB
-constexpr int kOffP = 2 * kQRegion;        // shared-memory map: Q | P | K stages 0, 1 | V stages 0, 1 | barriers
-constexpr int kOffK = kOffP + kQRegion;
+constexpr int kOffK = 2 * kQRegion;        // shared-memory map: Q | K stages 0, 1 | V stages 0, 1 | barriers
 constexpr int kOffV = kOffK + 2 * kKTile;
 constexpr int kOffBar = kOffV + 2 * kKTile;
-constexpr int kSmemBytes = kOffBar + 128;  // 112 KiB + barriers; no static shared memory, so two blocks fit an SM
+constexpr int kSmemBytes = kOffBar + 128;  // 96 KiB + barriers; two blocks per SM
 constexpr int kTmemCols = 256;             // S buffers: columns 0..63 and 64..127, O: columns 128..255
 constexpr float kGrowLog2 = 8.f;           // a row's maximum may lag its true maximum by this much (log2 units)
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -128,6 +131,14 @@ __device__ __forceinline__ void umma_f16( uint32_t tmem_d, uint64_t da, uint64_t
                 : "memory" );
 }
 
+// The same with the A operand in tensor memory: row i of A in lane i, two 16-bit elements per 32-bit column.
+__device__ __forceinline__ void umma_f16_ts( uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate )
+{
+  asm volatile( "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                ::"r"( tmem_d ), "r"( tmem_a ), "l"( db ), "r"( idesc ), "r"( accumulate )
+                : "memory" );
+}
+
 __device__ __forceinline__ void umma_commit( uint64_t* bar )
 {
   asm volatile( "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"( smem_u32( bar ) )
@@ -151,6 +162,20 @@ __device__ __forceinline__ void tmem_ld32( uint32_t taddr, float ( &v )[32] )
     v[i] = __uint_as_float( r[i] );
 }
 
+// 64 consecutive fp32 columns of this thread's TMEM lane, one load and one wait.
+__device__ __forceinline__ void tmem_ld64( uint32_t taddr, float ( &v )[64] )
+{
+  uint32_t r[64];
+  asm volatile( "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+                "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+                : "=r"( r[0] ), "=r"( r[1] ), "=r"( r[2] ), "=r"( r[3] ), "=r"( r[4] ), "=r"( r[5] ), "=r"( r[6] ), "=r"( r[7] ), "=r"( r[8] ), "=r"( r[9] ), "=r"( r[10] ), "=r"( r[11] ), "=r"( r[12] ), "=r"( r[13] ), "=r"( r[14] ), "=r"( r[15] ), "=r"( r[16] ), "=r"( r[17] ), "=r"( r[18] ), "=r"( r[19] ), "=r"( r[20] ), "=r"( r[21] ), "=r"( r[22] ), "=r"( r[23] ), "=r"( r[24] ), "=r"( r[25] ), "=r"( r[26] ), "=r"( r[27] ), "=r"( r[28] ), "=r"( r[29] ), "=r"( r[30] ), "=r"( r[31] ), "=r"( r[32] ), "=r"( r[33] ), "=r"( r[34] ), "=r"( r[35] ), "=r"( r[36] ), "=r"( r[37] ), "=r"( r[38] ), "=r"( r[39] ), "=r"( r[40] ), "=r"( r[41] ), "=r"( r[42] ), "=r"( r[43] ), "=r"( r[44] ), "=r"( r[45] ), "=r"( r[46] ), "=r"( r[47] ), "=r"( r[48] ), "=r"( r[49] ), "=r"( r[50] ), "=r"( r[51] ), "=r"( r[52] ), "=r"( r[53] ), "=r"( r[54] ), "=r"( r[55] ), "=r"( r[56] ), "=r"( r[57] ), "=r"( r[58] ), "=r"( r[59] ), "=r"( r[60] ), "=r"( r[61] ), "=r"( r[62] ), "=r"( r[63] )
+                : "r"( taddr ) );
+  asm volatile( "tcgen05.wait::ld.sync.aligned;" ::: "memory" );
+#pragma unroll
+  for ( int i = 0; i < 64; i++ )
+    v[i] = __uint_as_float( r[i] );
+}
+
 // Write 32 consecutive fp32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_st32( uint32_t taddr, const float ( &v )[32] )
 {
@@ -158,6 +183,19 @@ __device__ __forceinline__ void tmem_st32( uint32_t taddr, const float ( &v )[32
 #pragma unroll
   for ( int i = 0; i < 32; i++ )
     r[i] = __float_as_uint( v[i] );
+  asm volatile( "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                ::"r"( taddr ),
+                "r"( r[0] ), "r"( r[1] ), "r"( r[2] ), "r"( r[3] ), "r"( r[4] ), "r"( r[5] ), "r"( r[6] ), "r"( r[7] ), "r"( r[8] ),
+                "r"( r[9] ), "r"( r[10] ), "r"( r[11] ), "r"( r[12] ), "r"( r[13] ), "r"( r[14] ), "r"( r[15] ), "r"( r[16] ),
+                "r"( r[17] ), "r"( r[18] ), "r"( r[19] ), "r"( r[20] ), "r"( r[21] ), "r"( r[22] ), "r"( r[23] ), "r"( r[24] ),
+                "r"( r[25] ), "r"( r[26] ), "r"( r[27] ), "r"( r[28] ), "r"( r[29] ), "r"( r[30] ), "r"( r[31] )
+                : "memory" );
+  asm volatile( "tcgen05.wait::st.sync.aligned;" ::: "memory" );
+}
+
+__device__ __forceinline__ void tmem_st32_bits( uint32_t taddr, const uint32_t ( &r )[32] )
+{
   asm volatile( "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
                 ::"r"( taddr ),
@@ -220,7 +258,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
 {
   extern __shared__ __align__( 1024 ) uint8_t smem[];
   uint8_t* sQ = smem;
-  uint8_t* sP = smem + kOffP;
   uint8_t* sK = smem + kOffK; // two stages
   uint8_t* sV = smem + kOffV; // two stages
   uint64_t* bars = reinterpret_cast<uint64_t*>( smem + kOffBar );
@@ -229,8 +266,8 @@ __global__ void __launch_bounds__( kThreads, 2 )
   uint64_t* bar_s = bars + 4;      // [2] S = Q K^T complete in TMEM buffer b           (MMA -> row owners)
   uint64_t* bar_kfree = bars + 6;  // [2] the MMAs reading K stage s have completed     (MMA -> TMA lane)
   uint64_t* bar_vfree = bars + 8;  // [2] the MMAs reading V stage s have completed     (MMA -> TMA lane)
-  uint64_t* bar_pv = bars + 10;    // O += P V of a tile has completed: P and O are free (MMA -> row owners)
-  uint64_t* bar_p = bars + 11;     // all 128 row owners have written P (and read S)    (row owners -> MMA lane)
+  uint64_t* bar_pv = bars + 10;    // O += P V of a tile has completed: O may be rescaled (MMA -> row owners)
+  uint64_t* bar_p = bars + 11;     // all 128 row owners have put P in place of S       (row owners -> MMA lane)
   uint64_t* bar_q = bars + 12;     // Q block has landed                                (TMA -> MMA lane)
   uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>( bars + 13 );
   volatile int* fail = reinterpret_cast<volatile int*>( bars + 14 );
@@ -256,14 +293,48 @@ __global__ void __launch_bounds__( kThreads, 2 )
   const int n_keys = it.t_end;                                        // keys seen by the block's last token
   const int n_tiles = ( n_keys + kKeys - 1 ) / kKeys;
 
-  if ( r == 0 ) {
+  // The TMA lane sets the barriers up and has the Q block and the first tiles on their way before the rest of the
+  // block has finished its own set-up; warp 5 gets the tensor memory.
+  const CtxMeta c = a.ctx[it.ctx];
+  const long long row_bytes = (long long)sh.row_elems * (long long)sizeof( T );
+  const int arena_row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / row_bytes );
+  const int xk = kvh * kHS, xv = (int)sh.kv_dim + kvh * kHS;
+  // Only boxes holding at least one live key are fetched: rows beyond may lie in pages that are not mapped.
+  auto load_tile = [&]( int t, uint8_t* dst, int x, uint64_t* bar ) {
+    const int live = min( kKeys, n_keys - t * kKeys );
+    const int boxes = ( live + kBoxRows - 1 ) / kBoxRows;
+    asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar ) ),
+                  "r"( (uint32_t)boxes * kBoxRows * 128 * 2 )
+                  : "memory" );
+    for ( int j = 0; j < boxes; j++ ) {
+      const int y = arena_row0 + t * kKeys + j * kBoxRows;
+      tma_load_2d( dst + j * kBoxRows * 128, &kv_map, x, y, bar );
+      tma_load_2d( dst + kKRegion + j * kBoxRows * 128, &kv_map, x + 64, y, bar );
+    }
+  };
+  auto load_k = [&]( int t ) { load_tile( t, sK + ( t & 1 ) * kKTile, xk, &bar_k[t & 1] ); };
+  auto load_v = [&]( int t ) { load_tile( t, sV + ( t & 1 ) * kKTile, xv, &bar_v[t & 1] ); };
+  if ( r == 4 * 32 ) {
     *fail = 0;
 #pragma unroll
     for ( int i = 0; i < 13; i++ )
       asm volatile( "mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"( smem_u32( &bars[i] ) ), "r"( i == 11 ? kRows : 1 ) );
     asm volatile( "fence.mbarrier_init.release.cluster;" ::: "memory" );
+    // the append kernel (the kernel before this one in the stream) rotated q and wrote the chunk's K/V rows
+    asm volatile( "griddepcontrol.wait;" ::: "memory" );
+    // The query block: box = [64 dims][group heads][128 / group tokens] of q viewed as
+    // [contexts][chunk tokens][heads][128], twice (dims 0..63, 64..127).  Its rows land in (token, head) order
+    // with the 128-byte swizzle the MMA descriptors expect; tokens past the chunk's end arrive as zeros.
+    asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar_q ) ), "r"( 2 * kQRegion )
+                  : "memory" );
+    tma_load_4d( sQ, &q_map, 0, kvh * group, tok0, it.ctx, bar_q );
+    tma_load_4d( sQ + kQRegion, &q_map, 64, kvh * group, tok0, it.ctx, bar_q );
+    load_k( 0 );
+    if ( n_tiles > 1 )
+      load_k( 1 );
+    load_v( 0 );
   }
-  if ( warp == 4 ) {
+  if ( warp == 5 ) {
     asm volatile( "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"( smem_u32( tmem_base_p ) ),
                   "r"( kTmemCols ) );
     asm volatile( "tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" );
@@ -272,46 +343,14 @@ __global__ void __launch_bounds__( kThreads, 2 )
   __syncthreads();
   asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
   const uint32_t tmem_base = *tmem_base_p;
-  // the append kernel (the kernel before this one in the stream) rotated q and wrote the chunk's K/V rows
   asm volatile( "griddepcontrol.wait;" ::: "memory" );
 
   constexpr unsigned kFull = 0xffffffffu;
 
   if ( warp == 4 ) {
-    // =========================== TMA lane: K/V tiles into the two stages ===========================
+    // =========================== TMA lane: the remaining K/V tiles, as their stages fall free ===========================
     if ( r == 4 * 32 ) {
-      // The query block: box = [64 dims][group heads][128 / group tokens] of q viewed as
-      // [contexts][chunk tokens][heads][128], twice (dims 0..63, 64..127).  Its rows land in (token, head) order
-      // with the 128-byte swizzle the MMA descriptors expect; tokens past the chunk's end arrive as zeros.
-      asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar_q ) ), "r"( 2 * kQRegion )
-                    : "memory" );
-      tma_load_4d( sQ, &q_map, 0, kvh * group, tok0, it.ctx, bar_q );
-      tma_load_4d( sQ + kQRegion, &q_map, 64, kvh * group, tok0, it.ctx, bar_q );
-      const CtxMeta c = a.ctx[it.ctx];
-      const long long row_bytes = (long long)sh.row_elems * (long long)sizeof( T );
-      const int arena_row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / row_bytes );
-      const int xk = kvh * kHS, xv = (int)sh.kv_dim + kvh * kHS;
-      // Only boxes holding at least one live key are fetched: rows beyond may lie in pages that are not mapped.
-      auto load_tile = [&]( int t, uint8_t* dst, int x, uint64_t* bar ) {
-        const int live = min( kKeys, n_keys - t * kKeys );
-        const int boxes = ( live + kBoxRows - 1 ) / kBoxRows;
-        asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( bar ) ),
-                      "r"( (uint32_t)boxes * kBoxRows * 128 * 2 )
-                      : "memory" );
-        for ( int j = 0; j < boxes; j++ ) {
-          const int y = arena_row0 + t * kKeys + j * kBoxRows;
-          tma_load_2d( dst + j * kBoxRows * 128, &kv_map, x, y, bar );
-          tma_load_2d( dst + kKRegion + j * kBoxRows * 128, &kv_map, x + 64, y, bar );
-        }
-      };
-      auto load_k = [&]( int t ) { load_tile( t, sK + ( t & 1 ) * kKTile, xk, &bar_k[t & 1] ); };
-      auto load_v = [&]( int t ) { load_tile( t, sV + ( t & 1 ) * kKTile, xv, &bar_v[t & 1] ); };
       GH_TRACE_DECL;
-      GH_TRACE( 1, 1 );
-      load_k( 0 );
-      if ( n_tiles > 1 )
-        load_k( 1 );
-      load_v( 0 );
       GH_TRACE( 1, 2 );
       // in the order the MMA lane needs them: K(t+2) once S(t) has completed, V(t+1) once P.V(t-1) has
       bool ok = true;
@@ -384,9 +423,8 @@ __global__ void __launch_bounds__( kThreads, 2 )
         asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
 #pragma unroll
         for ( int k = 0; k < kKeys / 16; k++ ) { // 16 keys per MMA
-          const uint64_t da = desc_kmajor( smem_u32( sP + k * 32 ) );
           const uint64_t db = desc_mnmajor( smem_u32( sV + b * kKTile + k * 16 * 128 ) );
-          umma_f16( tmem_base + 128, da, db, idesc_pv, ( t > 0 || k > 0 ) ? 1u : 0u );
+          umma_f16_ts( tmem_base + 128, tmem_base + b * kKeys + k * 8, db, idesc_pv, ( t > 0 || k > 0 ) ? 1u : 0u );
         }
         umma_commit( bar_pv );
         umma_commit( &bar_vfree[b] );
@@ -429,32 +467,25 @@ __global__ void __launch_bounds__( kThreads, 2 )
       const int lim = row_limit - t * kKeys; // keys of this tile the row sees
       const int warp_lim = __reduce_max_sync( kFull, lim );
       const bool full_tile = __all_sync( kFull, lim >= kKeys );
-      float s0[32], s1[32];
+      float sc[64];
       if ( warp_lim > 0 ) {
-        tmem_ld32( tmem_s + b * kKeys, s0 );
+        tmem_ld64( tmem_s + b * kKeys, sc );
       } else {
 #pragma unroll
-        for ( int j = 0; j < 32; j++ )
-          s0[j] = 0.f;
-      }
-      if ( warp_lim > 32 ) {
-        tmem_ld32( tmem_s + b * kKeys + 32, s1 );
-      } else {
-#pragma unroll
-        for ( int j = 0; j < 32; j++ )
-          s1[j] = 0.f;
+        for ( int j = 0; j < 64; j++ )
+          sc[j] = 0.f;
       }
       GH_TRACE0( 4 );
       float tmax = -INFINITY;
       if ( full_tile ) {
 #pragma unroll
         for ( int j = 0; j < 32; j++ )
-          tmax = fmaxf( tmax, fmaxf( s0[j], s1[j] ) );
+          tmax = fmaxf( tmax, fmaxf( sc[j], sc[32 + j] ) );
       } else {
 #pragma unroll
         for ( int j = 0; j < 32; j++ ) {
-          tmax = fmaxf( tmax, j < lim ? s0[j] : -INFINITY );
-          tmax = fmaxf( tmax, 32 + j < lim ? s1[j] : -INFINITY );
+          tmax = fmaxf( tmax, j < lim ? sc[j] : -INFINITY );
+          tmax = fmaxf( tmax, 32 + j < lim ? sc[32 + j] : -INFINITY );
         }
       }
       // raise m only when some row of the warp has outgrown it by more than 2^kGrowLog2: then every row of the warp
@@ -473,8 +504,8 @@ __global__ void __launch_bounds__( kThreads, 2 )
       if ( full_tile ) {
 #pragma unroll
         for ( int j = 0; j < 32; j += 2 ) {
-          const float a0 = fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ), a1 = fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) );
-          const float b0 = fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ), b1 = fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) );
+          const float a0 = fast_exp2( fmaf( sc[j], scale_log2, neg_m ) ), a1 = fast_exp2( fmaf( sc[j + 1], scale_log2, neg_m ) );
+          const float b0 = fast_exp2( fmaf( sc[32 + j], scale_log2, neg_m ) ), b1 = fast_exp2( fmaf( sc[33 + j], scale_log2, neg_m ) );
           l += ( a0 + a1 ) + ( b0 + b1 );
           pk[j >> 1] = pack2<T>( a0, a1 );
           pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
@@ -482,10 +513,10 @@ __global__ void __launch_bounds__( kThreads, 2 )
       } else {
 #pragma unroll
         for ( int j = 0; j < 32; j += 2 ) {
-          const float a0 = j < lim ? fast_exp2( fmaf( s0[j], scale_log2, neg_m ) ) : 0.f;
-          const float a1 = j + 1 < lim ? fast_exp2( fmaf( s0[j + 1], scale_log2, neg_m ) ) : 0.f;
-          const float b0 = 32 + j < lim ? fast_exp2( fmaf( s1[j], scale_log2, neg_m ) ) : 0.f;
-          const float b1 = 33 + j < lim ? fast_exp2( fmaf( s1[j + 1], scale_log2, neg_m ) ) : 0.f;
+          const float a0 = j < lim ? fast_exp2( fmaf( sc[j], scale_log2, neg_m ) ) : 0.f;
+          const float a1 = j + 1 < lim ? fast_exp2( fmaf( sc[j + 1], scale_log2, neg_m ) ) : 0.f;
+          const float b0 = 32 + j < lim ? fast_exp2( fmaf( sc[32 + j], scale_log2, neg_m ) ) : 0.f;
+          const float b1 = 33 + j < lim ? fast_exp2( fmaf( sc[33 + j], scale_log2, neg_m ) ) : 0.f;
           l += ( a0 + a1 ) + ( b0 + b1 );
           pk[j >> 1] = pack2<T>( a0, a1 );
           pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
@@ -493,30 +524,27 @@ __global__ void __launch_bounds__( kThreads, 2 )
       }
 
       GH_TRACE0( 5 );
-      // ---- P and O are free once the previous tile's P.V has completed
-      if ( t > 0 ) {
+      // ---- O may be rescaled once the previous tile's P.V has completed
+      if ( t > 0 && warp_grow ) {
         ok = __all_sync( kFull, mbar_wait( bar_pv, ( t - 1 ) & 1, fail ) );
         if ( !ok )
           break;
         asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-        if ( warp_grow ) { // (tile 0 has nothing to rescale: its first MMA overwrites O)
 #pragma unroll 1
-          for ( int cb = 0; cb < 4; cb++ ) {
-            float o[32];
-            tmem_ld32( tmem_o + cb * 32, o );
+        for ( int cb = 0; cb < 4; cb++ ) {
+          float o[32];
+          tmem_ld32( tmem_o + cb * 32, o );
 #pragma unroll
-            for ( int j = 0; j < 32; j++ )
-              o[j] *= f;
-            tmem_st32( tmem_o + cb * 32, o );
-          }
+          for ( int j = 0; j < 32; j++ )
+            o[j] *= f;
+          tmem_st32( tmem_o + cb * 32, o );
         }
       }
       GH_TRACE0( 6 );
-      // 64 keys = 8 chunks of 8 keys (16 B) of row r in P's K-major swizzled layout
-#pragma unroll
-      for ( int ch = 0; ch < 8; ch++ )
-        *reinterpret_cast<uint4*>( sP + r * 128 + ( ( ch ^ ( r & 7 ) ) << 4 ) )
-          = make_uint4( pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3] );
+      // ---- P replaces S in tensor memory: 64 keys of 16 bits = the first 32 columns of this tile's S buffer, from
+      //      where the P.V MMAs take it as their A operand.  (Tile 0 has nothing to rescale: its first MMA
+      //      overwrites O.)
+      tmem_st32_bits( tmem_s + b * kKeys, pk );
       // V rows past the last key hold stale or foreign data: clear them so that 0 * garbage cannot make a NaN
       const int live = min( kKeys, n_keys - t * kKeys ); // keys of this tile that exist at all
       if ( live < kKeys ) {
@@ -532,7 +560,7 @@ __global__ void __launch_bounds__( kThreads, 2 )
           }
         }
       }
-      asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" ); // P and the cleared V rows -> tensor-core proxy
+      asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" ); // the cleared V rows -> tensor-core proxy
       asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
       asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( bar_p ) ) : "memory" );
       GH_TRACE0( 7 );
@@ -548,17 +576,16 @@ __global__ void __launch_bounds__( kThreads, 2 )
       // swizzled layout, and leaves by TMA: rows of tokens past the chunk's end are clipped by the tensor map
       const float inv = row_live ? 1.0f / l : 0.f;
 #pragma unroll 1
-      for ( int cb = 0; cb < 4; cb++ ) {
-        float v[32];
-        tmem_ld32( tmem_o + cb * 32, v );
+      for ( int half = 0; half < 2; half++ ) { // 64 dims = one swizzled region of the staging buffer
+        float v[64];
+        tmem_ld64( tmem_o + half * 64, v );
 #pragma unroll
-        for ( int q4 = 0; q4 < 4; q4++ ) {
+        for ( int ch = 0; ch < 8; ch++ ) { // 16-byte chunks of the row
           uint32_t w[4];
 #pragma unroll
           for ( int j = 0; j < 4; j++ )
-            w[j] = pack2<T>( v[q4 * 8 + 2 * j] * inv, v[q4 * 8 + 2 * j + 1] * inv );
-          const int ch = cb * 4 + q4; // 16-byte chunk 0..15 of the row
-          *reinterpret_cast<uint4*>( sQ + ( ch >> 3 ) * kQRegion + r * 128 + ( ( ( ch & 7 ) ^ ( r & 7 ) ) << 4 ) )
+            w[j] = pack2<T>( v[ch * 8 + 2 * j] * inv, v[ch * 8 + 2 * j + 1] * inv );
+          *reinterpret_cast<uint4*>( sQ + half * kQRegion + r * 128 + ( ( ch ^ ( r & 7 ) ) << 4 ) )
             = make_uint4( w[0], w[1], w[2], w[3] );
         }
       }
@@ -580,7 +607,7 @@ __global__ void __launch_bounds__( kThreads, 2 )
   __syncthreads();
   if ( r == 0 && *fail != 0 )
     atomicOr( a.dev_error, 4u );
-  if ( warp == 4 ) {
+  if ( warp == 5 ) {
     __syncwarp();
     asm volatile( "tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"( tmem_base ), "r"( kTmemCols ) );
   }
