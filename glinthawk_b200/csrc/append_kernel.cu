@@ -95,11 +95,11 @@ __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
   }
 }
 
-// Prompt chunks: the same arithmetic, but one thread carries its 16-byte unit through TB consecutive tokens of a
-// context with all of their loads in flight together.  A chunk moves hundreds of MB, so it is bandwidth-bound
-// work, and one unit per thread (as above) would leave each block with too little to hide its start-up behind.
+// Prompt chunks: the same arithmetic over hundreds of MB, so bandwidth-bound work.  The units of a token are taken
+// in address order (a warp reads and writes 512 consecutive bytes) and one thread carries its unit through TB
+// consecutive tokens of a context with their loads in flight together.
 template<typename T, int TB>
-__global__ void __launch_bounds__( 256 ) append_chunk_kernel( const AppendArgs a )
+__global__ void __launch_bounds__( 256, 6 ) append_chunk_kernel( const AppendArgs a )
 {
   constexpr int N = Vec16<T>::N;
   const Shape& sh = a.sh;
@@ -155,19 +155,20 @@ __global__ void __launch_bounds__( 256 ) append_chunk_kernel( const AppendArgs a
   const int d = e % (int)sh.head_size; // first dimension of the chunk within its head, even
   const T* cs0 = static_cast<const T*>( a.rope_cos ) + (size_t)pos0 * ( sh.head_size / 2 ) + d / 2;
   const T* sn0 = static_cast<const T*>( a.rope_sin ) + (size_t)pos0 * ( sh.head_size / 2 ) + d / 2;
-  Vec16<T> x[TB], cs[TB], sn[TB];
+  Vec16<T> x[TB];
+  uint2 cs[TB], sn[TB]; // the chunk's N / 2 rotation pairs: 8 bytes of each table
 #pragma unroll
   for ( int t = 0; t < TB; t++ )
     if ( t < n_tok ) {
       x[t] = ld16( from + (size_t)t * from_stride );
-      // the chunk's N / 2 rotation pairs: 8 bytes of each table
-      *reinterpret_cast<uint2*>( &cs[t] ) = *reinterpret_cast<const uint2*>( cs0 + (size_t)t * ( sh.head_size / 2 ) );
-      *reinterpret_cast<uint2*>( &sn[t] ) = *reinterpret_cast<const uint2*>( sn0 + (size_t)t * ( sh.head_size / 2 ) );
+      cs[t] = *reinterpret_cast<const uint2*>( cs0 + (size_t)t * ( sh.head_size / 2 ) );
+      sn[t] = *reinterpret_cast<const uint2*>( sn0 + (size_t)t * ( sh.head_size / 2 ) );
     }
 #pragma unroll
   for ( int t = 0; t < TB; t++ )
     if ( t < n_tok )
-      st16( to + (size_t)t * to_stride, rotate_chunk( x[t], cs[t].v, sn[t].v ) );
+      st16( to + (size_t)t * to_stride,
+            rotate_chunk( x[t], reinterpret_cast<const T*>( &cs[t] ), reinterpret_cast<const T*>( &sn[t] ) ) );
 }
 
 } // namespace
@@ -184,7 +185,10 @@ cudaError_t launch_append( const AppendArgs& args, cudaStream_t st, uint64_t* la
   const unsigned units = ( a.sh.kv_dim / n16 ) * ( 2 + a.sh.group );
   const unsigned tokens = a.tokens_per_ctx > 0 ? a.tokens_per_ctx : 1;
   // prompt chunks with rotation, new rows and the arena's own slots (what the chunk entry point passes)
-  constexpr int TB = 8;
+  // prompt chunks with rotation, new rows and the arena's own slots (what the chunk entry point passes).  Two
+  // tokens per thread measured best on B200 (1, 2, 3, 4, 8, 16 tried): more tokens per thread cost more in
+  // occupancy than they gain in loads in flight.
+  constexpr int TB = 2;
   if ( tokens >= TB && a.token_rows == nullptr && a.kv_new != nullptr && a.rope_cos != nullptr ) {
     const unsigned cunits = 2 * ( a.sh.kv_dim / n16 ) + ( a.q != nullptr ? a.sh.n_heads * a.sh.head_size / n16 : 0 );
     const dim3 cgrid( a.batch * ( ( tokens + TB - 1 ) / TB ), ( cunits + 255 ) / 256 );

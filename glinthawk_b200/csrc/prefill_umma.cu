@@ -51,7 +51,8 @@ constexpr int kOffBar = kOffV + 2 * kKTile;
 constexpr int kSmemBytes = kOffBar + 128;  // 96 KiB + barriers; two blocks per SM
 constexpr int kTmemCols = 256;             // S buffers: columns 0..63 and 64..127, O: columns 128..255
 constexpr float kGrowLog2 = 8.f;           // a row's maximum may lag its true maximum by this much (log2 units)
-constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t kWaitLimit = 1u << 16;     // attempts per wait ...
+constexpr uint32_t kWaitHintNs = 20000;     // ... of up to 20 us each: a wait gives up after about a second
 
 __device__ __forceinline__ uint32_t smem_u32( const void* p )
 {
@@ -65,13 +66,15 @@ __device__ __forceinline__ bool mbar_wait( uint64_t* bar, uint32_t parity, volat
   const uint32_t addr = smem_u32( bar );
   for ( uint32_t it = 0; it < kWaitLimit; it++ ) {
     uint32_t done;
-    asm volatile( "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+    // the hint lets a waiting thread sleep up to that many nanoseconds per attempt instead of taking issue slots
+    // from the warps that have work; it wakes as soon as the phase completes
+    asm volatile( "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
                   : "=r"( done )
-                  : "r"( addr ), "r"( parity )
+                  : "r"( addr ), "r"( parity ), "r"( kWaitHintNs )
                   : "memory" );
     if ( done )
       return true;
-    if ( ( it & 255u ) == 255u && *fail != 0 )
+    if ( ( it & 15u ) == 15u && *fail != 0 )
       return false;
   }
   return false;
