@@ -179,7 +179,9 @@ int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new
  * [n_ctx][n_tokens][n_heads*head_size], kv_new is [n_ctx][n_tokens][2*kv_dim] (device pointers); slots and pos0 are
  * host arrays.  The result equals n_tokens consecutive gh_attn_step calls.  The reference has no multi-token
  * operation: it feeds prompts one token per forward pass (src/worker/worker.hh:789-796,
- * src/frontend/infer.cc:124-126).  Does not disturb the batch set up by gh_attn_batch_begin. */
+ * src/frontend/infer.cc:124-126).  Does not disturb the batch set up by gh_attn_batch_begin.
+ * fp16/bf16 with head size 128 runs on the tcgen05 tensor-core kernel when q_inout and xb are 16-byte aligned
+ * (gh_attn_stats.last_kernel == 2); every other case takes a slower kernel with the same result. */
 int gh_attn_prefill_chunk( gh_attn_t h,
                            uint32_t layer,
                            uint64_t n_ctx,
