@@ -227,107 +227,19 @@ def test_layers_in_flight_on_several_streams(oracle):
     st.close()
 
 
-def _exact_causal_attention(sh, dtype, pos0, q_rot, cache):
-    """Softmax attention in float64 over the given rotated queries [B][T][dim] and cache rows, every token seeing the
-    keys up to its own position."""
-    B, T = q_rot.shape[:2]
-    out = np.zeros(q_rot.shape, dtype=np.float64)
-    group, hs = sh.n_heads // sh.n_kv_heads, sh.head_size
-    for i, p in enumerate(pos0):
-        rows = cases.as_f32(cache[i][:p + T], dtype).astype(np.float64)
-        k = rows[:, :sh.kv_dim].reshape(-1, sh.n_kv_heads, hs)
-        v = rows[:, sh.kv_dim:].reshape(-1, sh.n_kv_heads, hs)
-        qi = cases.as_f32(q_rot[i], dtype).astype(np.float64).reshape(T, sh.n_heads, hs)
-        visible = np.arange(p + T)[None, :] <= (p + np.arange(T))[:, None]
-        for h in range(sh.n_heads):
-            s = qi[:, h] @ k[:, h // group].T / np.sqrt(hs)
-            s = np.where(visible, s, -np.inf)
-            w = np.exp(s - s.max(axis=1, keepdims=True))
-            out[i, :, h * hs:(h + 1) * hs] = (w / w.sum(axis=1, keepdims=True)) @ v[:, h // group]
-    return out
-
-
-def _check_prefill(oracle, shape_name, dtype, pos0, chunk_lens, k_ramp=0.0, seed=321, exact_attention=False):
-    """Feeds `chunk_lens` consecutive prompt chunks to contexts whose slots already hold `pos0[i]` tokens, and
-    compares everything the calls leave behind with token-by-token reference layer-steps on a growing cache.
-    `k_ramp` > 0 scales the new K rows by (1 + k_ramp * position): the scores then grow along the keys by far more
-    than the kernel lets a row's running maximum lag, so the accumulator is rescaled again and again.
-    `exact_attention` replaces the reference's attention output by the exact softmax over the reference's own
-    rotated queries and cache rows (the appended rows and q are still held to the reference's)."""
-    sh = cases.SHAPES[shape_name]
-    T = int(sum(chunk_lens))
-    rng = np.random.default_rng(seed)
-    B = len(pos0)
-    base = cases.make_case("pf", shape_name, dtype, [p + T - 1 for p in pos0], seed=9)
-    q = cases.store(rng.standard_normal((B, T, sh.dim), dtype=np.float32), dtype)
-    kv32 = rng.standard_normal((B, T, 2 * sh.kv_dim), dtype=np.float32)
-    if k_ramp:
-        for i, p in enumerate(pos0):
-            kv32[i, :, :sh.kv_dim] *= (1.0 + k_ramp * (p + np.arange(T, dtype=np.float32)))[:, None]
-    kv = cases.store(kv32, dtype)
-
-    # oracle: token by token
-    cache = [c.copy() for c in base.cache]
-    want_xb = np.zeros_like(q)
-    want_q = np.zeros_like(q)
-    for t in range(T):
-        step = cases.Case("pf", sh, dtype, np.array([p + t for p in pos0], dtype=np.uint32), base.active,
-                          [c[: p + t + 1] for c, p in zip(cache, pos0)], np.ascontiguousarray(q[:, t]),
-                          np.ascontiguousarray(kv[:, t]), base.fcr, base.fci)
-        res = oracle.layer_step(step)
-        for i, p in enumerate(pos0):
-            cache[i][p + t] = res.rows[i]
-        want_xb[:, t], want_q[:, t] = res.xb, res.q
-
-    want_xb = cases.as_f32(want_xb, dtype)
-    if exact_attention:
-        want_xb = _exact_causal_attention(sh, dtype, pos0, want_q, cache)
-
-    st = gpu_util.make_stage(base, layers=2, paged=True)
-    slots = st.get_contexts(np.arange(1, B + 1, dtype=np.uint32))
-    for i, p in enumerate(pos0):
-        st.prepare(int(slots[i]), 1, max(p, 1) - 1, False)
-        if p > 0:
-            st.layer_view(int(slots[i]), 1, p).copy_(gpu_util.to_dev(base.cache[i][:p], dtype))
-    got_xb, got_q = np.zeros_like(q), np.zeros_like(q)
-    t0 = 0
-    for n in chunk_lens:
-        q_d = gpu_util.to_dev(np.ascontiguousarray(q[:, t0:t0 + n]), dtype)
-        kv_d = gpu_util.to_dev(np.ascontiguousarray(kv[:, t0:t0 + n]), dtype)
-        xb_d = torch.zeros_like(q_d)
-        st.prefill_chunk(1, slots, [p + t0 for p in pos0], n, q_d, kv_d, xb_d)
-        torch.cuda.synchronize()
-        got_xb[:, t0:t0 + n], got_q[:, t0:t0 + n] = gpu_util.to_host(xb_d, dtype), gpu_util.to_host(q_d, dtype)
-        t0 += n
-    assert st.stats().device_error == 0
-    tol = cases.TOL_XB[dtype]
-    k_atol = 1e-3 if dtype != cases.BF16 else 8e-3
-    np.testing.assert_allclose(cases.as_f32(got_xb, dtype), want_xb, rtol=0, atol=tol)
-    np.testing.assert_allclose(cases.as_f32(got_q, dtype), cases.as_f32(want_q, dtype), rtol=cases.TOL_K_REL, atol=k_atol)
-    for i, p in enumerate(pos0):
-        got = gpu_util.to_host(st.layer_view(int(slots[i]), 1, p + T), dtype)
-        kvd = sh.kv_dim
-        assert np.array_equal(got[p:, kvd:].view(np.uint8), cache[i][p:p + T, kvd:].view(np.uint8)), "V rows bit-exact"
-        np.testing.assert_allclose(cases.as_f32(got[p:, :kvd], dtype), cases.as_f32(cache[i][p:p + T, :kvd], dtype),
-                                   rtol=cases.TOL_K_REL, atol=k_atol * (1.0 + k_ramp * (p + T)))
-    kernel = st.stats().last_kernel
-    st.close()
-    return kernel
-
-
 @pytest.mark.parametrize("shape_name,dtype", [("mini_g4", cases.BF16), ("mini_g8", cases.F16), ("tiny15m", cases.F32),
                                               ("mini_mha", cases.F16), ("mini_g16", cases.F16), ("mini_g4", cases.F16)])
 def test_prefill_chunk_equals_token_by_token_reference_steps(oracle, shape_name, dtype):
     """A multi-token prompt chunk in one call.  The reference has no such operation — it feeds prompts one token
     per forward pass — so the oracle is n_tokens consecutive reference layer-steps on a growing cache.  Fresh slot,
     short prefix, longer prefix; 37 tokens leave the last query block ragged."""
-    _check_prefill(oracle, shape_name, dtype, pos0=[0, 5, 100], chunk_lens=[37])
+    gpu_util.check_prefill(oracle, shape_name, dtype, pos0=[0, 5, 100], chunk_lens=[37])
 
 
 @pytest.mark.parametrize("dtype", [cases.F16, cases.BF16])
 def test_prefill_in_several_chunks_continues_where_the_last_one_ended(oracle, dtype):
     """A prompt fed as three chunks of different sizes: the later chunks attend to rows the earlier calls wrote."""
-    kernel = _check_prefill(oracle, "mini_g4", dtype, pos0=[0, 17], chunk_lens=[64, 40, 9])
+    kernel = gpu_util.check_prefill(oracle, "mini_g4", dtype, pos0=[0, 17], chunk_lens=[64, 40, 9])
     assert kernel == 2, "head size 128 in a 16-bit type runs the tcgen05 kernel"
 
 
@@ -340,7 +252,7 @@ def test_prefill_with_scores_that_keep_growing_along_the_keys(oracle, shape_name
     The yardstick for the attention output here is the exact softmax: the reference stores its scores in the 16-bit
     type between its three operations (src/arch/amd64/llama2/ops.hh:170-298), and at scores of this size that rounding
     alone moves the reference's own output by up to 0.5."""
-    _check_prefill(oracle, shape_name, dtype, pos0=[0, 150], chunk_lens=[200], k_ramp=0.125, seed=5, exact_attention=True)
+    gpu_util.check_prefill(oracle, shape_name, dtype, pos0=[0, 150], chunk_lens=[200], k_ramp=0.125, seed=5, exact_attention=True)
 
 
 @pytest.mark.parametrize("force_generic", [False, True])
