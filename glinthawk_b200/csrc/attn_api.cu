@@ -681,10 +681,30 @@ int gh_attn_batch_begin( gh_attn_t h, uint64_t batch, const int32_t* slots, cons
   return GH_OK;
 }
 
+// The kernels move q, new K/V rows, cache rows and outputs in 16-byte pieces.  cudaMalloc'ed buffers and rows of the
+// model's sizes always satisfy this; anything else is turned away here instead of faulting on the device.
+static bool aligned16( const void* p )
+{
+  return ( reinterpret_cast<uintptr_t>( p ) & 15 ) == 0;
+}
+static int misaligned( gh_attn* h )
+{
+  return fail( h, GH_ERR_INVALID, "device buffers must be 16-byte aligned" );
+}
+static bool rows_aligned16( void* const* rows, uint64_t batch )
+{
+  for ( uint64_t i = 0; rows != nullptr && i < batch; i++ )
+    if ( !aligned16( rows[i] ) )
+      return false;
+  return true;
+}
+
 int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new, void* stream )
 {
   if ( h == nullptr || kv_new == nullptr )
     return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( q_inout ) || !aligned16( kv_new ) )
+    return misaligned( h );
   if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
     return rc;
   if ( h->rope_cos == nullptr )
@@ -713,6 +733,8 @@ int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* 
 {
   if ( h == nullptr || q == nullptr || xb == nullptr )
     return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( q ) || !aligned16( xb ) )
+    return misaligned( h );
   if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
     return rc;
   DeviceGuard guard( h->device );
@@ -746,6 +768,8 @@ int gh_attn_prefill_chunk( gh_attn_t h,
   if ( h == nullptr || slots == nullptr || pos0 == nullptr || q_inout == nullptr || kv_new == nullptr || xb == nullptr
        || n_ctx == 0 || n_ctx > h->cfg.max_batch || n_tokens == 0 )
     return fail( h, GH_ERR_INVALID, "bad prefill arguments" );
+  if ( !aligned16( q_inout ) || !aligned16( kv_new ) || !aligned16( xb ) )
+    return misaligned( h );
   if ( layer >= h->sh.n_layers )
     return fail( h, GH_ERR_INVALID, "layer is not hosted" );
   if ( h->rope_cos == nullptr )
@@ -805,9 +829,7 @@ int gh_attn_prefill_chunk( gh_attn_t h,
     const char* e = std::getenv( "GLINTHAWK_PREFILL" );
     return e != nullptr && std::string( e ) == "mma";
   }();
-  // the tcgen05 kernel moves q and xb by TMA, which needs 16-byte aligned buffers
-  const bool umma = h->use_mma && prefill_umma_supported( h->sh, h->cfg.dtype ) && !prefer_warp_mma
-                    && ( ( reinterpret_cast<uintptr_t>( q_inout ) | reinterpret_cast<uintptr_t>( xb ) ) & 15 ) == 0;
+  const bool umma = h->use_mma && prefill_umma_supported( h->sh, h->cfg.dtype ) && !prefer_warp_mma;
   CUtensorMap q_map {}, xb_map {};
   if ( umma ) {
     const DriverApi* api = driver_api( h->err );
@@ -1011,6 +1033,8 @@ int gh_op_copy_kv_cache( gh_attn_t h, void* const* token_rows, const void* state
 {
   if ( h == nullptr || state_kv == nullptr )
     return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( state_kv ) || ( batch <= h->cfg.max_batch && !rows_aligned16( token_rows, batch ) ) )
+    return misaligned( h );
   DeviceGuard guard( h->device );
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
   int entry;
@@ -1038,6 +1062,9 @@ int gh_op_apply_rope( gh_attn_t h,
 {
   if ( h == nullptr || pos == nullptr || freq_cis_real == nullptr || freq_cis_imag == nullptr || state_q == nullptr )
     return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( state_q ) || !aligned16( freq_cis_real ) || !aligned16( freq_cis_imag )
+       || ( batch <= h->cfg.max_batch && !rows_aligned16( token_rows, batch ) ) )
+    return misaligned( h );
   for ( uint64_t i = 0; i < batch && i < h->cfg.max_batch; i++ )
     if ( token_rows != nullptr && token_rows[i] != nullptr && pos[i] >= h->sh.seq_len )
       return fail( h, GH_ERR_CAPACITY, "token position beyond the RoPE tables" );
@@ -1149,6 +1176,8 @@ int gh_op_attention_fused( gh_attn_t h,
     return fail( h, GH_ERR_INVALID, "null argument" );
   if ( const int rc = check_positions( h, batch, layer_bases, pos ); rc != GH_OK )
     return rc;
+  if ( !aligned16( query ) || !aligned16( xb ) || !rows_aligned16( const_cast<void* const*>( layer_bases ), batch ) )
+    return misaligned( h );
   DeviceGuard guard( h->device );
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
   const char* arena = h->pool.arena();

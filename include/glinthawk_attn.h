@@ -152,6 +152,10 @@ size_t gh_slot_bytes( gh_attn_t h );
 
 /* ---- fused hot path -------------------------------------------------------------------------------- */
 
+/* Alignment: q, the new K/V rows, xb and every cache row handed to the entry points of this and the next section
+ * must be 16-byte aligned device pointers; a call with a misaligned one returns GH_ERR_INVALID and launches nothing.
+ * Buffers from cudaMalloc and the rows of any model shape (row sizes are multiples of 16 bytes) always are. */
+
 /* Per-batch set-up, the attention-relevant part of Llama2::forward_prelude / forward_attention
  * (src/models/llama2/model.hh:446-477, 611-628): records slot and token position of every prompt of the
  * batch (host arrays, as the reference's ScratchPad keeps them, src/models/llama2/base.hh:197-202), plans
@@ -180,8 +184,8 @@ int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new
  * host arrays.  The result equals n_tokens consecutive gh_attn_step calls.  The reference has no multi-token
  * operation: it feeds prompts one token per forward pass (src/worker/worker.hh:789-796,
  * src/frontend/infer.cc:124-126).  Does not disturb the batch set up by gh_attn_batch_begin.
- * fp16/bf16 with head size 128 runs on the tcgen05 tensor-core kernel when q_inout and xb are 16-byte aligned
- * (gh_attn_stats.last_kernel == 2); every other case takes a slower kernel with the same result. */
+ * fp16/bf16 with head size 128 runs on the tcgen05 tensor-core kernel (gh_attn_stats.last_kernel == 2); every other
+ * case takes a slower kernel with the same result. */
 int gh_attn_prefill_chunk( gh_attn_t h,
                            uint32_t layer,
                            uint64_t n_ctx,

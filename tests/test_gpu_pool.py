@@ -122,6 +122,33 @@ def test_error_conventions():
     st.close()
 
 
+def test_misaligned_device_buffers_are_refused_before_any_launch():
+    """The kernels move q, K/V rows and outputs in 16-byte pieces.  A pointer that is not 16-byte aligned comes back
+    as GH_ERR_INVALID with nothing launched, and the handle keeps working."""
+    sh = SHAPES["mini_g4"]
+    st = AttentionStage(sh, torch.float16, n_layers_hosted=1, max_batch=2, max_contexts=2)
+    cos = torch.ones(sh.seq_len, sh.head_size // 2, device="cuda", dtype=torch.float16)
+    st.set_rope_tables(cos, torch.zeros_like(cos))
+    s = st.get_context(1)
+    st.batch_begin([s, -1], [0, 0])
+    big = torch.zeros(2 * sh.dim + 8, device="cuda", dtype=torch.float16)
+    q_odd = big[4:4 + 2 * sh.dim].view(2, sh.dim)  # 8 bytes off
+    q = torch.zeros(2, sh.dim, device="cuda", dtype=torch.float16)
+    kv = torch.zeros(2, 2 * sh.kv_dim, device="cuda", dtype=torch.float16)
+    launches = st.stats().kernel_launches
+    for call in (lambda: st.append(0, q_odd, kv), lambda: st.decode(0, q_odd, q.clone()), lambda: st.decode(0, q, q_odd),
+                 lambda: st.step(0, q_odd, kv, q.clone()),
+                 lambda: st.prefill_chunk(0, [s], [0], 2, q_odd.view(1, 2, sh.dim), kv.view(1, 2, -1), q.clone().view(1, 2, -1))):
+        with pytest.raises(GlinthawkAttnError) as e:
+            call()
+        assert e.value.status == _lib.GH_ERR_INVALID and "aligned" in str(e.value)
+    assert st.stats().kernel_launches == launches
+    st.step(0, q, kv, q.clone())
+    torch.cuda.synchronize()
+    assert st.stats().device_error == 0 and st.stats().kernel_launches > launches
+    st.close()
+
+
 def test_fill_normal_statistics():
     sh = SHAPES["tiny15m"]
     st = AttentionStage(sh, torch.float32, n_layers_hosted=1, max_batch=1, max_contexts=1)
