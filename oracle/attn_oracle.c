@@ -2,7 +2,7 @@
  * TEST INFRASTRUCTURE ONLY — never linked into, imported by, or called from the product path.
  *
  * Plain-C restatement of the attention-stage operations of Glinthawk's amd64 backend
- * (src/arch/amd64/llama2/ops.hh) over Glinthawk's KV layout (src/models/llama2/context.hh:79-89,
+ * (src/arch/amd64/llama2/ops.hh; rmsnorm and matmul of src/arch/amd64/common/ops.hh for the stage's producer) over Glinthawk's KV layout (src/models/llama2/context.hh:79-89,
  * 115-127: per layer, token t lives at base + t * 2 * kv_dim elements, K heads first, then V heads).
  * It is the checker the CUDA path is compared with; it is itself pinned against the reference's own
  * amd64 code compiled from the reference tree (oracle/ref_harness.cc) through the fixtures in
@@ -167,6 +167,44 @@ int gho_attention_2_gemm( int dtype,
     attention_2_gemm_f32( (const float*)att, layer_bases, (float*)xb, B, pos, n_kv_heads, gqa, hs, seq_len ),
     attention_2_gemm_f16( (const gho_f16*)att, layer_bases, (gho_f16*)xb, B, pos, n_kv_heads, gqa, hs, seq_len ),
     attention_2_gemm_bf16( (const gho_bf16*)att, layer_bases, (gho_bf16*)xb, B, pos, n_kv_heads, gqa, hs, seq_len ) )
+}
+
+int gho_rmsnorm( int dtype, void* out, const void* x, const void* weight, uint64_t B, uint64_t size )
+{
+  DISPATCH( dtype,
+            rmsnorm_f32( (float*)out, (const float*)x, (const float*)weight, B, size ),
+            rmsnorm_f16( (gho_f16*)out, (const gho_f16*)x, (const gho_f16*)weight, B, size ),
+            rmsnorm_bf16( (gho_bf16*)out, (const gho_bf16*)x, (const gho_bf16*)weight, B, size ) )
+}
+
+int gho_matmul( int dtype, void* xout, const void* x, const void* w, uint64_t B, uint64_t s, uint64_t r )
+{
+  DISPATCH( dtype,
+            matmul_f32( (float*)xout, (const float*)x, (const float*)w, B, s, r ),
+            matmul_f16( (gho_f16*)xout, (const gho_f16*)x, (const gho_f16*)w, B, s, r ),
+            matmul_bf16( (gho_bf16*)xout, (const gho_bf16*)x, (const gho_bf16*)w, B, s, r ) )
+}
+
+/* The producer of the attention stage's inputs, src/models/llama2/model.hh:326-351 (pre_attention_ops without the
+ * cache update): xb = rmsnorm(x, rms_att_weight); q = xb . wq^T; kv = xb . wkv^T.  wq is [dim][dim], wkv
+ * [2*kv_dim][dim], both row-major. */
+int gho_pre_attention( int dtype,
+                       uint64_t B,
+                       const void* x,
+                       const void* rms_w,
+                       const void* wq,
+                       const void* wkv,
+                       void* xb,
+                       void* q,
+                       void* kv,
+                       uint64_t dim,
+                       uint64_t kv_dim )
+{
+  if ( gho_rmsnorm( dtype, xb, x, rms_w, B, dim ) != 0 )
+    return -1;
+  gho_matmul( dtype, q, xb, wq, B, dim, dim );
+  gho_matmul( dtype, kv, xb, wkv, B, dim, 2 * kv_dim );
+  return 0;
 }
 
 static size_t elem_size( int dtype )

@@ -13,6 +13,7 @@
  *   ghref_shape_count / ghref_shape_name / ghref_shape_dims   the shape table
  *   ghref_op          one reference operation on caller buffers
  *   ghref_layer_step  the five operations in model order (src/models/llama2/model.hh:345-387)
+ *   ghref_pre_attention  rmsnorm + the q and kv projections that feed the stage (model.hh:326-343)
  *   ghref_threads     omp_get_max_threads()
  */
 #include <cstdint>
@@ -154,6 +155,34 @@ int run_dtype( int dtype,
   }
 }
 
+// pre_attention_ops without the cache update (src/models/llama2/model.hh:326-343): the reference's own rmsnorm and
+// matmul templates (src/arch/amd64/common/ops.hh:141-170, 212-229).
+template<typename Config, typename DType>
+int run_pre_attention( uint64_t B, const void* x, const void* rms_w, const void* wq, const void* wkv, void* xb, void* q, void* kv )
+{
+  using Ops = ref::amd64::LlamaOperations<Config, DType>;
+  alignas( ref::ConfigRuntime<Config> ) static unsigned char settings_storage[sizeof( ref::ConfigRuntime<Config> )] {};
+  Ops ops { *reinterpret_cast<const ref::ConfigRuntime<Config>*>( settings_storage ) };
+  ops.template rmsnorm<Config::dim>(
+    static_cast<DType*>( xb ), static_cast<const DType*>( x ), nullptr, static_cast<const DType*>( rms_w ), B );
+  ops.template matmul<Config::dim, Config::dim>(
+    static_cast<DType*>( q ), static_cast<const DType*>( xb ), static_cast<const DType*>( wq ), B );
+  ops.template matmul<Config::dim, Config::kv_dim * 2>(
+    static_cast<DType*>( kv ), static_cast<const DType*>( xb ), static_cast<const DType*>( wkv ), B );
+  return 0;
+}
+
+template<typename Config>
+int run_pre_attention_dtype( int dtype, uint64_t B, const void* x, const void* rms_w, const void* wq, const void* wkv, void* xb,
+                             void* q, void* kv )
+{
+  switch ( dtype ) {
+    case 0: return run_pre_attention<Config, glinthawk::float16_t>( B, x, rms_w, wq, wkv, xb, q, kv );
+    case 1: return run_pre_attention<Config, glinthawk::float32_t>( B, x, rms_w, wq, wkv, xb, q, kv );
+    default: return -2;
+  }
+}
+
 } // namespace
 
 extern "C" {
@@ -203,6 +232,26 @@ int ghref_op( int idx,
 #define X_RUN( n, d, hq, hkv, s, l )                                                                                   \
   if ( idx == i++ )                                                                                                    \
     return run_dtype<Shape<d, hq, hkv, s, l>>( dtype, op, B, pos, layer_bases, fcr, fci, q, kv_new, att, xb );
+  GHREF_SHAPES( X_RUN )
+#undef X_RUN
+  return -1;
+}
+
+int ghref_pre_attention( int idx,
+                         int dtype,
+                         uint64_t B,
+                         const void* x,
+                         const void* rms_w,
+                         const void* wq,
+                         const void* wkv,
+                         void* xb,
+                         void* q,
+                         void* kv )
+{
+  int i = 0;
+#define X_RUN( n, d, hq, hkv, s, l )                                                                                   \
+  if ( idx == i++ )                                                                                                    \
+    return run_pre_attention_dtype<Shape<d, hq, hkv, s, l>>( dtype, B, x, rms_w, wq, wkv, xb, q, kv );
   GHREF_SHAPES( X_RUN )
 #undef X_RUN
   return -1;

@@ -103,6 +103,50 @@ def _vp(a):
     return C.c_void_p(a.ctypes.data) if a is not None else C.c_void_p(0)
 
 
+@dataclass
+class ProjCase:
+    """Inputs of the stage's producer (src/models/llama2/model.hh:326-343): the residual stream, the rmsnorm weight
+    and the two projection matrices, plus the batch's token positions for the rotation and the append."""
+    name: str
+    shape: AttnShape
+    dtype: int
+    pos: np.ndarray       # uint32 [B]
+    x: np.ndarray         # [B, dim]
+    rms_w: np.ndarray     # [dim]
+    wq: np.ndarray        # [dim, dim]          (row r = output feature r)
+    wkv: np.ndarray       # [2*kv_dim, dim]
+    fcr: np.ndarray
+    fci: np.ndarray
+
+    @property
+    def B(self) -> int:
+        return len(self.pos)
+
+
+def make_proj_case(name: str, shape_name: str, dtype: int, pos, seed: int) -> ProjCase:
+    """x ~ N(0,1), rmsnorm weights around 1, projection weights ~ N(0, 1/dim) so that q, k, v come out ~ N(0,1)."""
+    sh = SHAPES[shape_name]
+    rng = np.random.default_rng(seed)
+    pos = np.asarray(pos, dtype=np.uint32)
+    B = len(pos)
+    x = store(rng.standard_normal((B, sh.dim), dtype=np.float32), dtype)
+    rms_w = store(1.0 + 0.1 * rng.standard_normal(sh.dim, dtype=np.float32), dtype)
+    scale = np.float32(1.0 / np.sqrt(sh.dim))
+    wq = store(rng.standard_normal((sh.dim, sh.dim), dtype=np.float32) * scale, dtype)
+    wkv = store(rng.standard_normal((2 * sh.kv_dim, sh.dim), dtype=np.float32) * scale, dtype)
+    cos, sin = rope_tables(sh.head_size, sh.seq_len, sh.rope_theta)
+    return ProjCase(name, sh, dtype, pos, x, rms_w, wq, wkv, store(cos, dtype), store(sin, dtype))
+
+
+@dataclass
+class ProjResult:
+    xb: np.ndarray           # rmsnorm output [B, dim]
+    q: np.ndarray            # projected q [B, dim], before rotation
+    kv: np.ndarray           # projected [K|V] rows [B, 2*kv_dim], before rotation
+    q_rot: np.ndarray        # q after apply_rope
+    rows: np.ndarray         # the rows as copy_kv_cache + apply_rope leave them in the slots [B, 2*kv_dim]
+
+
 class Oracle:
     def __init__(self):
         self.lib = oracle_build.load_oracle()
@@ -119,6 +163,29 @@ class Oracle:
         assert rc == 0
         rows = [c[int(p)].copy() if a else None for c, p, a in zip(cache, case.pos, case.active)]
         return StepResult(rows, q, xb, att if keep_att else None)
+
+    def _rotate_and_append(self, case: "ProjCase", q: np.ndarray, kv: np.ndarray):
+        """copy_kv_cache + apply_rope on one-row slots: what the reference does with the projections next
+        (src/models/llama2/model.hh:345-360)."""
+        sh, B = case.shape, case.B
+        rows = np.zeros_like(kv)
+        q_rot = q.copy()
+        ptrs = (C.c_void_p * B)(*[rows[i].ctypes.data for i in range(B)])
+        assert self.lib.gho_copy_kv_cache(case.dtype, ptrs, _vp(kv), C.c_uint64(B), C.c_uint64(sh.kv_dim)) == 0
+        assert self.lib.gho_apply_rope(case.dtype, C.c_uint64(B), _vp(case.pos), _vp(case.fcr), _vp(case.fci), _vp(q_rot),
+                                       ptrs, C.c_uint64(sh.n_kv_heads), C.c_uint64(sh.gqa_size),
+                                       C.c_uint64(sh.head_size)) == 0
+        return q_rot, rows
+
+    def pre_attention(self, case: "ProjCase") -> "ProjResult":
+        sh, B = case.shape, case.B
+        xb, q = np.zeros_like(case.x), np.zeros_like(case.x)
+        kv = np.zeros((B, 2 * sh.kv_dim), dtype=case.x.dtype)
+        rc = self.lib.gho_pre_attention(case.dtype, C.c_uint64(B), _vp(case.x), _vp(case.rms_w), _vp(case.wq), _vp(case.wkv),
+                                        _vp(xb), _vp(q), _vp(kv), C.c_uint64(sh.dim), C.c_uint64(sh.kv_dim))
+        assert rc == 0
+        q_rot, rows = self._rotate_and_append(case, q, kv)
+        return ProjResult(xb, q, kv, q_rot, rows)
 
     def op(self, name: str, *args):
         fn = getattr(self.lib, "gho_" + name)
@@ -155,6 +222,33 @@ class Reference:
         assert rc == 0
         rows = [c[int(p)].copy() if a else None for c, p, a in zip(cache, case.pos, case.active)]
         return StepResult(rows, q, xb, att if keep_att else None)
+
+
+    def pre_attention(self, case: "ProjCase", oracle: "Oracle") -> "ProjResult":
+        """The reference's own rmsnorm and matmul; rotation and append as in layer_step (through the oracle's
+        restatement of the two operations, which the layer-step fixtures pin)."""
+        assert case.dtype in (F16, F32), "the reference's amd64 backend has no bf16"
+        sh, B = case.shape, case.B
+        idx = self.names.index(sh.name)
+        xb, q = np.zeros_like(case.x), np.zeros_like(case.x)
+        kv = np.zeros((B, 2 * sh.kv_dim), dtype=case.x.dtype)
+        rc = self.lib.ghref_pre_attention(idx, case.dtype, C.c_uint64(B), _vp(case.x), _vp(case.rms_w), _vp(case.wq),
+                                          _vp(case.wkv), _vp(xb), _vp(q), _vp(kv))
+        assert rc == 0
+        q_rot, rows = oracle._rotate_and_append(case, q, kv)
+        return ProjResult(xb, q, kv, q_rot, rows)
+
+
+# The producer's golden cases: one per storage type the reference has, small matrices.
+GOLDEN_PROJ_SPECS = [
+    dict(name="proj_mini_mha_f16", shape_name="mini_mha", dtype=F16, pos=[0, 5, 64, 300, 511], seed=201),
+    dict(name="proj_mini_g4_f16", shape_name="mini_g4", dtype=F16, pos=[1, 2, 3, 100, 101, 102, 400], seed=202),
+    dict(name="proj_tiny15m_f32", shape_name="tiny15m", dtype=F32, pos=[0, 17, 255], seed=203),
+]
+
+
+def golden_proj_case(spec: dict) -> ProjCase:
+    return make_proj_case(spec["name"], spec["shape_name"], spec["dtype"], spec["pos"], spec["seed"])
 
 
 # The golden cases: small enough for the checkers to finish in well under a second each, covering every head

@@ -3,8 +3,9 @@ reference tree into ``oracle/_ref`` by ``oracle/build.py``) on the seeded cases 
 
     python tests/golden/make_golden.py
 
-Each fixture stores the outputs of one layer-step (appended row after RoPE, rotated q, attention output) plus a
-checksum of the seeded inputs, so that a drift in the input generator is caught instead of silently
+Each fixture stores the outputs of one layer-step (appended row after RoPE, rotated q, attention output) — the
+``proj_*`` fixtures those of the stage's producer (rmsnorm output, projected q and K/V rows, before and after the
+rotation) — plus a checksum of the seeded inputs, so that a drift in the input generator is caught instead of silently
 invalidating the fixture.  Inputs are regenerated from the seed at test time; they are not stored.
 """
 from __future__ import annotations
@@ -42,6 +43,16 @@ def main() -> None:
         np.savez_compressed(out_dir / f"{case.name}.npz", rows=rows, q=res.q, xb=res.xb,
                             input_crc=np.uint32(input_checksum(case)), threads=np.int32(ref.threads()))
         print(f"{case.name}: xb absmax {np.abs(res.xb.astype(np.float32)).max():.4f}")
+    oracle = cases.Oracle()
+    for spec in cases.GOLDEN_PROJ_SPECS:
+        case = cases.golden_proj_case(spec)
+        res = ref.pre_attention(case, oracle)
+        crc = 0
+        for a in [case.x, case.rms_w, case.wq, case.wkv, case.fcr, case.fci, case.pos]:
+            crc = zlib.crc32(np.ascontiguousarray(a).tobytes(), crc)
+        np.savez_compressed(out_dir / f"{case.name}.npz", xb=res.xb, q=res.q, kv=res.kv, q_rot=res.q_rot, rows=res.rows,
+                            input_crc=np.uint32(crc), threads=np.int32(ref.threads()))
+        print(f"{case.name}: q absmax {np.abs(res.q.astype(np.float32)).max():.4f}")
 
 
 if __name__ == "__main__":

@@ -94,3 +94,40 @@ def test_oracle_convert_and_copy(oracle):
     oracle.op("convert_and_copy", cases.F32, C.c_void_p(back.ctypes.data), cases.F16, C.c_void_p(h.ctypes.data),
               C.c_uint64(1000))
     assert np.array_equal(back, h.astype(np.float32))
+
+
+# ---- the stage's producer: rmsnorm + q / kv projections (+ rotation and append) -------------------------------
+
+# fp32: sums of `dim` products, reassociated by -ffast-math in the reference build.  fp16: one rounding of a sum of
+# magnitude ~1, so a last-place flip (2^-10 relative) is the most that survives.
+PROJ_ABS = {cases.F32: 2e-5, cases.F16: 4e-3}
+
+
+def _proj_crc(case):
+    crc = 0
+    for a in [case.x, case.rms_w, case.wq, case.wkv, case.fcr, case.fci, case.pos]:
+        crc = zlib.crc32(np.ascontiguousarray(a).tobytes(), crc)
+    return crc
+
+
+def check_proj(res, gold, case):
+    atol = PROJ_ABS[case.dtype]
+    for name in ("xb", "q", "kv", "q_rot", "rows"):
+        np.testing.assert_allclose(_f32(getattr(res, name), case.dtype), _f32(gold[name], case.dtype), rtol=cases.TOL_K_REL,
+                                   atol=atol, err_msg=name)
+
+
+@pytest.mark.parametrize("spec", cases.GOLDEN_PROJ_SPECS, ids=lambda s: s["name"])
+def test_oracle_producer_matches_reference_fixture(oracle, spec):
+    case = cases.golden_proj_case(spec)
+    gold = np.load(GOLDEN / f"{case.name}.npz")
+    assert int(gold["input_crc"]) == _proj_crc(case), "seeded inputs drifted: regenerate tests/golden"
+    check_proj(oracle.pre_attention(case), gold, case)
+
+
+@pytest.mark.parametrize("spec", cases.GOLDEN_PROJ_SPECS, ids=lambda s: s["name"])
+def test_producer_fixture_reproduced_by_reference_library(oracle, reference, spec):
+    case = cases.golden_proj_case(spec)
+    gold = np.load(GOLDEN / f"{case.name}.npz")
+    check_proj(reference.pre_attention(case, oracle), gold, case)
+
