@@ -112,6 +112,12 @@ struct gh_attn
 
   HostStage stage[kHostStages];
   uint32_t stage_next = 0;
+
+  // q / kv projection (allocated by the first gh_attn_project_append call)
+  void* proj_xb = nullptr;        // rmsnorm output, [max_batch][dim]
+  float* proj_ws = nullptr;       // partial sums of the tiles that were cut
+  uint32_t* proj_count = nullptr; // [tiles] pieces arrived, zero between launches
+  bool proj_ready = false;
 };
 
 namespace {
@@ -521,6 +527,9 @@ int gh_attn_destroy( gh_attn_t h )
       cudaEventDestroy( set.done );
   }
   cudaFree( h->dev_error );
+  cudaFree( h->proj_xb );
+  cudaFree( h->proj_ws );
+  cudaFree( h->proj_count );
   h->pool.destroy();
   (void)cudaGetLastError();
   delete h;
@@ -726,6 +735,98 @@ int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_n
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
   if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
     return cuda_fail( h, "append kernel launch", e );
+  return ring_touch( h, h->cur, st );
+}
+
+int gh_attn_project_append( gh_attn_t h,
+                            uint32_t layer,
+                            const void* x,
+                            const void* rms_weight,
+                            const void* wq,
+                            const void* wkv,
+                            void* q_out,
+                            void* stream )
+{
+  if ( h == nullptr || x == nullptr || rms_weight == nullptr || wq == nullptr || wkv == nullptr || q_out == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( x ) || !aligned16( rms_weight ) || !aligned16( wq ) || !aligned16( wkv ) || !aligned16( q_out ) )
+    return misaligned( h );
+  if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
+    return rc;
+  if ( h->rope_cos == nullptr )
+    return fail( h, GH_ERR_STATE, "RoPE tables not set" );
+  if ( !h->use_mma || !project_supported( h->sh, h->cfg.dtype ) )
+    return fail( h, GH_ERR_UNSUPPORTED,
+                 "the fused projection needs fp16 or bf16 storage and dim, kv_dim that are multiples of 128" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  const DriverApi* api = driver_api( h->err );
+  if ( api == nullptr )
+    return GH_ERR_CUDA;
+  if ( const int rc = prepare_layer( h, layer ); rc != GH_OK )
+    return rc;
+
+  const uint32_t dim = h->sh.n_heads * h->sh.head_size;
+  ProjectArgs a {};
+  uint32_t grid = 0;
+  project_plan( h->sh, h->sm_count, &a, &grid );
+  if ( !h->proj_ready ) { // first call: scratch for the normalised activations and the stream-K pieces
+    GH_CUDA( h, project_prepare() );
+    GH_CUDA( h, cudaMalloc( &h->proj_xb, static_cast<size_t>( h->cfg.max_batch ) * dim * h->elem ) );
+    GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &h->proj_ws ), project_workspace_bytes( a ) ) );
+    GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &h->proj_count ), a.n_tiles * sizeof( uint32_t ) ) );
+    GH_CUDA( h, cudaMemset( h->proj_count, 0, a.n_tiles * sizeof( uint32_t ) ) );
+    h->stats.scratch_bytes += static_cast<size_t>( h->cfg.max_batch ) * dim * h->elem + project_workspace_bytes( a );
+    h->proj_ready = true;
+  }
+
+  // rmsnorm for the whole batch (src/models/llama2/model.hh:331-335)
+  if ( const cudaError_t e = launch_rmsnorm( h->proj_xb, x, rms_weight, h->cur_batch, dim, h->cfg.dtype, st, &h->stats.kernel_launches );
+       e != cudaSuccess )
+    return cuda_fail( h, "rmsnorm launch", e );
+
+  const CUtensorMapDataType dt = h->cfg.dtype == GH_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  auto encode = [&]( CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows ) -> int {
+    const cuuint64_t dims[2] = { dim, rows };
+    const cuuint64_t strides[1] = { static_cast<cuuint64_t>( dim ) * h->elem };
+    const cuuint32_t box[2] = { 64, box_rows };
+    const cuuint32_t estr[2] = { 1, 1 };
+    const CUresult r = api->TensorMapEncodeTiled( map, dt, 2, const_cast<void*>( base ), dims, strides, box, estr,
+                                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE );
+    if ( r != CUDA_SUCCESS )
+      return fail( h, GH_ERR_CUDA, "cuTensorMapEncodeTiled (projection): " + driver_error( api, r ) );
+    return GH_OK;
+  };
+  CUtensorMap wq_map {}, wkv_map {}, xb_map {};
+  if ( const int rc = encode( &wq_map, wq, dim, 128 ); rc != GH_OK )
+    return rc;
+  if ( const int rc = encode( &wkv_map, wkv, 2ull * h->sh.kv_dim, 128 ); rc != GH_OK )
+    return rc;
+
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.ctx = entry_ctx( h, h->ring[h->cur].dev );
+  a.arena = h->pool.arena();
+  a.layer_off = h->pool.layer_offset( layer );
+  a.q_out = q_out;
+  a.rope_cos = h->rope_cos;
+  a.rope_sin = h->rope_sin;
+  a.ws = h->proj_ws;
+  a.seg_count = h->proj_count;
+  a.dev_error = h->dev_error;
+  // the MMA's N takes at most project_max_rows() batch rows: larger batches go in slices (the weights are then
+  // streamed once per slice)
+  for ( uint32_t b0 = 0; b0 < h->cur_batch; b0 += project_max_rows() ) {
+    a.batch0 = b0;
+    a.batch = std::min( project_max_rows(), h->cur_batch - b0 );
+    a.nb = ( a.batch + 15 ) / 16 * 16;
+    if ( const int rc = encode( &xb_map, h->proj_xb, h->cur_batch, a.nb ); rc != GH_OK )
+      return rc;
+    if ( const cudaError_t e = launch_project( a, grid, &wq_map, &wkv_map, &xb_map, st, &h->stats.kernel_launches );
+         e != cudaSuccess )
+      return cuda_fail( h, "projection launch", e );
+  }
   return ring_touch( h, h->cur, st );
 }
 

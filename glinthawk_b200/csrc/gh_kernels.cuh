@@ -77,6 +77,37 @@ cudaError_t prefill_umma_prepare();
 cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map, const CUtensorMap* q_map,
                                  const CUtensorMap* xb_map, cudaStream_t st, uint64_t* launches );
 
+// The stage's producer (rmsnorm + q / kv projection) with the RoPE + append epilogue, on tcgen05.
+struct ProjectArgs
+{
+  Shape sh;
+  uint32_t dtype;
+  uint32_t batch;  // batch rows covered by this launch (at most project_max_rows())
+  uint32_t batch0; // index of the first of them in the whole batch
+  uint32_t nb;     // batch rounded up to a multiple of 16: the MMA's N
+  uint32_t dim, n_tiles, q_tiles, kblocks, units_per_cta, max_segs; // set by project_plan()
+  const CtxMeta* ctx; // device, whole batch
+  char* arena;
+  long long layer_off;
+  void* q_out;          // [whole batch][dim]
+  const void* rope_cos; // [seq_len][head_size / 2]
+  const void* rope_sin;
+  float* ws;           // project_workspace_bytes()
+  uint32_t* seg_count; // [n_tiles], zero between launches
+  uint32_t* dev_error;
+};
+bool project_supported( const Shape& sh, uint32_t dtype );
+uint32_t project_max_rows();
+cudaError_t project_prepare();
+void project_plan( const Shape& sh, uint32_t sm_count, ProjectArgs* a, uint32_t* grid );
+size_t project_workspace_bytes( const ProjectArgs& a );
+cudaError_t launch_rmsnorm( void* out, const void* x, const void* weight, uint32_t rows, uint32_t dim, uint32_t dtype,
+                            cudaStream_t st, uint64_t* launches );
+// wq_map / wkv_map: the weight matrices as [rows][dim] with box [128][64]; xb_map: the normalised activations as
+// [batch][dim] with box [nb][64]; all with the 128-byte swizzle.
+cudaError_t launch_project( const ProjectArgs& a, uint32_t grid, const CUtensorMap* wq_map, const CUtensorMap* wkv_map,
+                            const CUtensorMap* xb_map, cudaStream_t st, uint64_t* launches );
+
 cudaError_t launch_scores( const ScoreArgs& a, cudaStream_t st, uint64_t* launches );  // attention_0_gemm
 cudaError_t launch_softmax( const ScoreArgs& a, cudaStream_t st, uint64_t* launches ); // attention_softmax
 cudaError_t launch_values( const ScoreArgs& a, cudaStream_t st, uint64_t* launches );  // attention_2_gemm

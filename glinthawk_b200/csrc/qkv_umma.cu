@@ -1,0 +1,437 @@
+// The producer of the attention stage fused to it: rmsnorm, the q and kv projections on the 5th-generation tensor
+// cores (tcgen05 + TMEM), and RoPE + K/V append straight from the accumulators.
+//
+// Replaces, per layer-step, the reference's
+//   rmsnorm( xb, x, rms_att_weight ); matmul( q, xb, wq ); matmul( kv, xb, wkv );   src/models/llama2/model.hh:326-343
+//   copy_kv_cache( token_contexts, kv ); apply_rope( pos, fcr, fci, q, token_contexts )            model.hh:345-360
+// (operations: src/arch/amd64/common/ops.hh:141-170, 212-229; src/arch/amd64/llama2/ops.hh:138-164, 300-352).  The kv
+// scratch buffer disappears: K and V go from TMEM into the slot rows.  Rounding points are the reference's: xb, q and
+// kv are rounded to the storage type, the rotation is done in fp32 on those rounded values with separately rounded
+// products and rounded once more.
+//
+// The GEMM is skinny (a decode batch of at most a few hundred rows against [dim + 2 kv_dim] x [dim] weights), so the
+// weight stream is what has to be kept flowing and the weights take the MMA's M side:
+//   D[128 features x Nb batch rows] += W[128 x 64] . XB[Nb x 64]^T          tcgen05.mma M = 128, N = Nb <= 256, fp32 in TMEM
+// Work unit = (tile of 128 output features, block of 64 k).  The units are dealt to the CTAs (one per SM) as equal
+// contiguous runs, so a CTA works through the tail of one tile, some whole tiles and the head of another
+// ("stream-K"): all SMs stream weights for the same time whatever the number of tiles.  A tile that was cut leaves
+// its partial sums in a workspace, one slot per piece; the CTA whose piece completes the tile (an atomic counter tells
+// it, nobody waits for anybody) adds the pieces in a fixed order and runs the epilogue.
+//
+// Roles per CTA: warps 0..3 = epilogue (thread r owns feature r of the tile = TMEM lane r), one lane of warp 4 = TMA
+// producer (4-stage ring of W and XB tiles, 128-byte swizzle), one lane of warp 5 = MMA issuer.  Two TMEM accumulators
+// so that the next piece is multiplied while the previous one is written out.  Every wait is bounded.
+#include <algorithm>
+#include <type_traits>
+
+#include "gh_kernels.cuh"
+#include "gh_umma.cuh"
+
+namespace gh {
+
+namespace {
+
+using namespace umma;
+
+constexpr int kTileF = 128;                   // output features per tile = MMA M = TMEM lanes
+constexpr int kBK = 64;                       // k elements per stage: one 128-byte swizzled row
+constexpr int kStages = 4;
+constexpr int kMaxNb = 256;                   // batch rows per launch = MMA N
+constexpr int kATile = kTileF * 128;          // 16 KiB of weights per stage
+constexpr int kBTile = kMaxNb * 128;          // up to 32 KiB of activations per stage
+constexpr int kStageBytes = kATile + kBTile;
+constexpr int kOffBar = kStages * kStageBytes; // 192 KiB, then: barriers | pos[256] | slot-row offsets[256]
+constexpr int kOffPos = kOffBar + 256;
+constexpr int kOffRow = kOffPos + kMaxNb * 4;
+constexpr int kSmemBytes = kOffRow + kMaxNb * 8;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;                // two accumulators of up to 256 columns
+
+template<typename T>
+__global__ void __launch_bounds__( 256 ) rmsnorm_kernel( T* __restrict__ out, const T* __restrict__ x,
+                                                          const T* __restrict__ weight, uint32_t dim )
+{
+  asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
+  const T* X = x + (size_t)blockIdx.x * dim;
+  T* O = out + (size_t)blockIdx.x * dim;
+  float ss = 0.f;
+  for ( uint32_t j = threadIdx.x; j < dim; j += blockDim.x ) {
+    const float v = Conv<T>::to_f32( X[j] );
+    ss += v * v;
+  }
+  __shared__ float part[8];
+  ss = warp_sum( ss );
+  if ( ( threadIdx.x & 31 ) == 0 )
+    part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for ( int w = 0; w < 8; w++ )
+    tot += part[w];
+  // src/arch/amd64/common/ops.hh:158-161
+  tot /= dim;
+  tot += 1e-5f;
+  tot = 1.0f / sqrtf( tot );
+  for ( uint32_t j = threadIdx.x; j < dim; j += blockDim.x )
+    O[j] = Conv<T>::from_f32( __fmul_rn( Conv<T>::to_f32( weight[j] ), __fmul_rn( tot, Conv<T>::to_f32( X[j] ) ) ) );
+}
+
+// The run of work units CTA `c` owns, and the pieces (tile, k-block range) it falls into.
+struct Piece
+{
+  int tile, k0, k1; // k-blocks [k0, k1) of the tile
+  int seg, nsegs;   // index of this piece among the tile's pieces, and how many there are
+};
+
+__device__ __forceinline__ Piece piece_at( int u, int u_end, int kblocks, int upc )
+{
+  Piece p;
+  p.tile = u / kblocks;
+  p.k0 = u - p.tile * kblocks;
+  p.k1 = min( kblocks, p.k0 + ( u_end - u ) );
+  const int first = p.tile * kblocks, last = first + kblocks - 1; // the tile's units; cuts fall on multiples of upc
+  p.seg = u / upc - first / upc;
+  p.nsegs = last / upc - first / upc + 1;
+  return p;
+}
+
+template<typename T>
+__global__ void __launch_bounds__( kThreads, 1 )
+  project_kernel( const ProjectArgs a, const __grid_constant__ CUtensorMap wq_map,
+                  const __grid_constant__ CUtensorMap wkv_map, const __grid_constant__ CUtensorMap xb_map )
+{
+  extern __shared__ __align__( 1024 ) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>( smem + kOffBar );
+  uint64_t* bar_full = bars;           // [kStages] tiles of a stage have landed          (TMA -> MMA lane)
+  uint64_t* bar_empty = bars + 4;      // [kStages] the MMAs reading a stage have completed (MMA -> TMA lane)
+  uint64_t* bar_acc_full = bars + 8;   // [2] a piece's accumulator is complete            (MMA -> epilogue)
+  uint64_t* bar_acc_free = bars + 10;  // [2] the accumulator has been read out            (epilogue -> MMA lane)
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>( bars + 12 );
+  volatile int* fail = reinterpret_cast<volatile int*>( bars + 13 );
+  volatile int* last_flag = reinterpret_cast<volatile int*>( bars + 14 );
+  uint32_t* pos_s = reinterpret_cast<uint32_t*>( smem + kOffPos );
+  long long* row_s = reinterpret_cast<long long*>( smem + kOffRow );
+
+  const int r = threadIdx.x;
+  const int warp = r >> 5;
+  if ( ( smem_u32( smem ) & 1023u ) != 0 ) { // the swizzled tiles need a 1024-byte aligned base
+    if ( r == 0 )
+      atomicOr( a.dev_error, 8u );
+    return;
+  }
+  asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
+
+  const int kblocks = a.kblocks, upc = a.units_per_cta;
+  const int u_begin = blockIdx.x * upc;
+  const int u_end = min( (int)( a.n_tiles * a.kblocks ), u_begin + upc );
+  const int nb = a.nb;
+
+  if ( r == 0 ) {
+    *fail = 0;
+    for ( int i = 0; i < 10; i++ )
+      asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bars[i] ) ) );
+    asm volatile( "mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"( smem_u32( &bar_acc_free[0] ) ), "r"( kTileF ) );
+    asm volatile( "mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"( smem_u32( &bar_acc_free[1] ) ), "r"( kTileF ) );
+    asm volatile( "fence.mbarrier_init.release.cluster;" ::: "memory" );
+  }
+  if ( warp == 5 ) {
+    asm volatile( "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"( smem_u32( tmem_base_p ) ),
+                  "r"( kTmemCols ) );
+    asm volatile( "tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" );
+  }
+  // positions and slot-row byte offsets of the batch rows this launch covers
+  for ( int i = r; i < nb; i += kThreads ) {
+    uint32_t p = 0;
+    long long off = -1;
+    if ( i < (int)a.batch ) {
+      const CtxMeta c = a.ctx[a.batch0 + i];
+      p = c.pos;
+      if ( c.kv_off != kInactive )
+        off = c.kv_off + a.layer_off + (long long)c.pos * a.sh.row_elems * (long long)sizeof( T );
+    }
+    pos_s[i] = p;
+    row_s[i] = off;
+  }
+  asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
+  __syncthreads();
+  asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+  const uint32_t tmem_base = *tmem_base_p;
+  // xb was written by the rmsnorm kernel, the kernel before this one in the stream
+  asm volatile( "griddepcontrol.wait;" ::: "memory" );
+
+  constexpr unsigned kFull = 0xffffffffu;
+
+  if ( warp == 4 ) {
+    // =========================== TMA lane ===========================
+    if ( r == 4 * 32 ) {
+      bool ok = true;
+      uint32_t n = 0; // stages filled so far
+      for ( int u = u_begin; u < u_end && ok; ) {
+        const Piece p = piece_at( u, u_end, kblocks, upc );
+        const bool is_q = p.tile < (int)a.q_tiles;
+        const CUtensorMap* wmap = is_q ? &wq_map : &wkv_map;
+        const int wrow = ( is_q ? p.tile : p.tile - (int)a.q_tiles ) * kTileF;
+        for ( int kb = p.k0; kb < p.k1 && ok; kb++, n++ ) {
+          const int s = n % kStages;
+          if ( n >= (uint32_t)kStages )
+            ok = mbar_wait( &bar_empty[s], ( n / kStages - 1 ) & 1, fail );
+          if ( !ok )
+            break;
+          uint8_t* sA = smem + s * kStageBytes;
+          asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( &bar_full[s] ) ),
+                        "r"( (uint32_t)( kATile + nb * 128 ) )
+                        : "memory" );
+          tma_load_2d( sA, wmap, kb * kBK, wrow, &bar_full[s] );
+          tma_load_2d( sA + kATile, &xb_map, kb * kBK, (int)a.batch0, &bar_full[s] ); // rows past the batch arrive as zeros
+        }
+        u += p.k1 - p.k0;
+      }
+      if ( !ok )
+        *fail = 1;
+    }
+  } else if ( warp == 5 ) {
+    // =========================== MMA lane ===========================
+    if ( r == 5 * 32 ) {
+      constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      // fp32 accumulate, A/B format, both operands K-major, N = nb, M = 128
+      const uint32_t idesc = ( 1u << 4 ) | ( fmt << 7 ) | ( fmt << 10 ) | ( ( (uint32_t)nb >> 3 ) << 17 ) | ( ( 128u >> 4 ) << 24 );
+      bool ok = true;
+      uint32_t n = 0, piece_i = 0;
+      for ( int u = u_begin; u < u_end && ok; piece_i++ ) {
+        const Piece p = piece_at( u, u_end, kblocks, upc );
+        const int ab = piece_i & 1;
+        if ( piece_i >= 2 ) { // the accumulator was used two pieces ago: wait until it has been read out
+          ok = mbar_wait( &bar_acc_free[ab], ( piece_i / 2 - 1 ) & 1, fail );
+          asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+        }
+        for ( int kb = p.k0; kb < p.k1 && ok; kb++, n++ ) {
+          const int s = n % kStages;
+          ok = mbar_wait( &bar_full[s], ( n / kStages ) & 1, fail );
+          if ( !ok )
+            break;
+          asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+          const uint32_t sA = smem_u32( smem + s * kStageBytes );
+#pragma unroll
+          for ( int k = 0; k < kBK / 16; k++ )
+            umma_f16( tmem_base + ab * kMaxNb, desc_kmajor( sA + k * 32 ), desc_kmajor( sA + kATile + k * 32 ), idesc,
+                      ( kb > p.k0 || k > 0 ) ? 1u : 0u );
+          umma_commit( &bar_empty[s] );
+        }
+        if ( ok )
+          umma_commit( &bar_acc_full[ab] );
+        u += p.k1 - p.k0;
+      }
+      if ( !ok )
+        *fail = 1;
+    }
+  } else {
+    // =========================== epilogue (warps 0..3): thread r owns feature r of the tile ===========================
+    const uint32_t lane_off = static_cast<uint32_t>( warp * 32 ) << 16; // this warp's quarter of the TMEM lanes
+    const int hs = a.sh.head_size;
+    const int dim = a.dim, kv_dim = a.sh.kv_dim, batch = a.batch;
+    const T* cos_t = static_cast<const T*>( a.rope_cos );
+    const T* sin_t = static_cast<const T*>( a.rope_sin );
+    const bool odd = ( r & 1 ) != 0;
+
+    // 32 batch rows of one feature: round to the storage type (the reference stores q and kv there), rotate the
+    // (even, odd) feature pair held by neighbouring lanes, and put the value where it belongs: q, or the slot row.
+    auto store_chunk = [&]( int tile, int cb, const float ( &v )[32] ) {
+      const int f = tile * kTileF + r;
+      const bool rotate = f < dim + kv_dim; // q and K; a tile never straddles two of q, K, V
+      const int d2 = ( f % hs ) >> 1;
+#pragma unroll 4
+      for ( int j = 0; j < 32; j++ ) {
+        const int i = cb * 32 + j;
+        if ( i >= batch )
+          break;
+        float x = Conv<T>::to_f32( Conv<T>::from_f32( v[j] ) );
+        if ( rotate ) {
+          const float other = __shfl_xor_sync( kFull, x, 1 );
+          const size_t ti = (size_t)pos_s[i] * ( hs / 2 ) + d2;
+          const float c = Conv<T>::to_f32( cos_t[ti] ), s = Conv<T>::to_f32( sin_t[ti] );
+          const float x0 = odd ? other : x, x1 = odd ? x : other;
+          // src/arch/amd64/llama2/ops.hh:150-162: separately rounded products
+          x = odd ? __fadd_rn( __fmul_rn( x0, s ), __fmul_rn( x1, c ) ) : __fsub_rn( __fmul_rn( x0, c ), __fmul_rn( x1, s ) );
+        }
+        const T o = Conv<T>::from_f32( x );
+        if ( f < dim ) {
+          static_cast<T*>( a.q_out )[(size_t)( a.batch0 + i ) * dim + f] = o;
+        } else if ( row_s[i] >= 0 ) {
+          *reinterpret_cast<T*>( a.arena + row_s[i] + (size_t)( f - dim ) * sizeof( T ) ) = o;
+        }
+      }
+    };
+
+    bool ok = true;
+    uint32_t piece_i = 0;
+    const int n_chunks = ( batch + 31 ) / 32;
+    for ( int u = u_begin; u < u_end; piece_i++ ) {
+      const Piece p = piece_at( u, u_end, kblocks, upc );
+      const int ab = piece_i & 1;
+      ok = __all_sync( kFull, mbar_wait( &bar_acc_full[ab], ( piece_i / 2 ) & 1, fail ) );
+      if ( !ok )
+        break;
+      asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
+      const uint32_t tacc = tmem_base + ab * kMaxNb + lane_off;
+      if ( p.nsegs == 1 ) {
+        // ---- the whole tile was accumulated here
+        for ( int cb = 0; cb < n_chunks; cb++ ) {
+          float v[32];
+          tmem_ld32( tacc + cb * 32, v );
+          store_chunk( p.tile, cb, v );
+        }
+        asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
+        asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_acc_free[ab] ) ) : "memory" );
+      } else {
+        // ---- a piece of a tile: leave the partial sums in this piece's workspace slot, [batch row][feature]
+        float* slot = a.ws + ( (size_t)p.tile * a.max_segs + p.seg ) * ( (size_t)nb * kTileF );
+        for ( int cb = 0; cb < n_chunks; cb++ ) {
+          float v[32];
+          tmem_ld32( tacc + cb * 32, v );
+#pragma unroll
+          for ( int j = 0; j < 32; j++ )
+            if ( cb * 32 + j < batch )
+              slot[(size_t)( cb * 32 + j ) * kTileF + r] = v[j];
+        }
+        asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
+        asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_acc_free[ab] ) ) : "memory" );
+        __threadfence();
+        asm volatile( "bar.sync 1, %0;" ::"n"( kTileF ) : "memory" );
+        if ( r == 0 ) {
+          const uint32_t arrived = atomicAdd( &a.seg_count[p.tile], 1u );
+          const bool last = arrived == (uint32_t)p.nsegs - 1;
+          if ( last )
+            a.seg_count[p.tile] = 0; // every piece has arrived: ready for the next launch
+          *last_flag = last ? 1 : 0;
+        }
+        asm volatile( "bar.sync 1, %0;" ::"n"( kTileF ) : "memory" );
+        if ( *last_flag != 0 ) {
+          // ---- this piece completed the tile: add the pieces in their fixed order and finish the tile
+          __threadfence();
+          const float* tile_ws = a.ws + (size_t)p.tile * a.max_segs * ( (size_t)nb * kTileF );
+          for ( int cb = 0; cb < n_chunks; cb++ ) {
+            float v[32];
+#pragma unroll
+            for ( int j = 0; j < 32; j++ )
+              v[j] = 0.f;
+            for ( int sgm = 0; sgm < p.nsegs; sgm++ ) {
+              const float* src = tile_ws + (size_t)sgm * ( (size_t)nb * kTileF );
+#pragma unroll
+              for ( int j = 0; j < 32; j++ )
+                if ( cb * 32 + j < batch )
+                  v[j] += __ldcg( src + (size_t)( cb * 32 + j ) * kTileF + r );
+            }
+            store_chunk( p.tile, cb, v );
+          }
+        }
+      }
+      u += p.k1 - p.k0;
+    }
+    if ( !ok )
+      *fail = 1;
+  }
+
+  asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
+  __syncthreads();
+  if ( r == 0 && *fail != 0 )
+    atomicOr( a.dev_error, 16u );
+  if ( warp == 5 ) {
+    __syncwarp();
+    asm volatile( "tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"( tmem_base ), "r"( kTmemCols ) );
+  }
+}
+
+} // namespace
+
+bool project_supported( const Shape& sh, uint32_t dtype )
+{
+  const uint32_t dim = sh.n_heads * sh.head_size;
+  return ( dtype == DT_F16 || dtype == DT_BF16 ) && dim % kTileF == 0 && sh.kv_dim % kTileF == 0 && sh.head_size % 2 == 0
+         && kTileF % sh.head_size == 0;
+}
+
+uint32_t project_max_rows()
+{
+  return kMaxNb;
+}
+
+cudaError_t project_prepare()
+{
+  cudaError_t e = cudaFuncSetAttribute( project_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
+  if ( e == cudaSuccess )
+    e = cudaFuncSetAttribute( project_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes );
+  return e;
+}
+
+void project_plan( const Shape& sh, uint32_t sm_count, ProjectArgs* a, uint32_t* grid )
+{
+  const uint32_t dim = sh.n_heads * sh.head_size;
+  a->dim = dim;
+  a->q_tiles = dim / kTileF;
+  a->n_tiles = ( dim + 2 * sh.kv_dim ) / kTileF;
+  a->kblocks = dim / kBK;
+  const uint32_t units = a->n_tiles * a->kblocks;
+  // one CTA per SM, but no piece shorter than four k-blocks unless the whole problem is that small
+  const uint32_t ctas = std::max( 1u, std::min( sm_count, units / 4 ) );
+  a->units_per_cta = ( units + ctas - 1 ) / ctas;
+  *grid = ( units + a->units_per_cta - 1 ) / a->units_per_cta;
+  a->max_segs = ( a->kblocks + a->units_per_cta - 1 ) / a->units_per_cta + 1;
+}
+
+size_t project_workspace_bytes( const ProjectArgs& a )
+{
+  return (size_t)a.n_tiles * a.max_segs * kMaxNb * kTileF * sizeof( float );
+}
+
+cudaError_t launch_rmsnorm( void* out, const void* x, const void* weight, uint32_t rows, uint32_t dim, uint32_t dtype,
+                            cudaStream_t st, uint64_t* launches )
+{
+  if ( rows == 0 )
+    return cudaSuccess;
+  switch ( dtype ) {
+    case DT_F32:
+      rmsnorm_kernel<float><<<rows, 256, 0, st>>>( static_cast<float*>( out ), static_cast<const float*>( x ),
+                                                   static_cast<const float*>( weight ), dim );
+      break;
+    case DT_F16:
+      rmsnorm_kernel<__half><<<rows, 256, 0, st>>>( static_cast<__half*>( out ), static_cast<const __half*>( x ),
+                                                    static_cast<const __half*>( weight ), dim );
+      break;
+    case DT_BF16:
+      rmsnorm_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>( static_cast<__nv_bfloat16*>( out ),
+                                                           static_cast<const __nv_bfloat16*>( x ),
+                                                           static_cast<const __nv_bfloat16*>( weight ), dim );
+      break;
+    default: return cudaErrorInvalidValue;
+  }
+  ( *launches )++;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_project( const ProjectArgs& a, uint32_t grid, const CUtensorMap* wq_map, const CUtensorMap* wkv_map,
+                            const CUtensorMap* xb_map, cudaStream_t st, uint64_t* launches )
+{
+  if ( a.batch == 0 )
+    return cudaSuccess;
+  cudaLaunchConfig_t cfg {};
+  cfg.gridDim = dim3( grid );
+  cfg.blockDim = dim3( kThreads );
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  if ( a.dtype == DT_F16 )
+    e = cudaLaunchKernelEx( &cfg, project_kernel<__half>, a, *wq_map, *wkv_map, *xb_map );
+  else if ( a.dtype == DT_BF16 )
+    e = cudaLaunchKernelEx( &cfg, project_kernel<__nv_bfloat16>, a, *wq_map, *wkv_map, *xb_map );
+  else
+    return cudaErrorInvalidValue;
+  ( *launches )++;
+  return e;
+}
+
+} // namespace gh

@@ -183,6 +183,12 @@ class AttentionStage:
         self._ck(lib.gh_attn_prefill_chunk(self._h, layer, len(slots), _ptr(slots), _ptr(pos0), n_tokens,
                                            _ptr(q_inout), _ptr(kv_new), _ptr(xb), _stream(stream)))
 
+    def project_append(self, layer: int, x, rms_weight, wq, wkv, q_out, stream=None) -> None:
+        """rmsnorm + q / kv projections + RoPE + K/V append for the current batch (the reference's pre_attention_ops
+        followed by copy_kv_cache and apply_rope); q_out receives the rotated queries."""
+        self._ck(lib.gh_attn_project_append(self._h, layer, _ptr(x), _ptr(rms_weight), _ptr(wq), _ptr(wkv), _ptr(q_out),
+                                            _stream(stream)))
+
     def forward_attention_host(self, layer: int, io_dtype, q_host, kv_host, xb_host, stream=None) -> None:
         self._ck(lib.gh_attn_forward_attention_host(self._h, layer, dtype_code(io_dtype), _ptr(q_host), _ptr(kv_host),
                                                     _ptr(xb_host), _stream(stream)))

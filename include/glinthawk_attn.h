@@ -178,6 +178,27 @@ int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* 
  * (src/models/llama2/model.hh:345-387). */
 int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new, void* xb, void* stream );
 
+/* The producer of the stage's inputs fused to the append, for the batch set up by gh_attn_batch_begin:
+ *   xb = rmsnorm( x, rms_weight );  q = xb . wq^T;  kv = xb . wkv^T        Llama2::pre_attention_ops,
+ *                                                                           src/models/llama2/model.hh:326-343
+ *   copy_kv_cache( kv ) and apply_rope( q, K )                              model.hh:345-360
+ * x is [batch][dim], rms_weight [dim], wq [dim][dim], wkv [2*kv_dim][dim] (row r = output feature r, as the
+ * reference stores them: src/models/llama2/base.hh:477-499), q_out [batch][dim]: device pointers of the handle's
+ * dtype.  On return (stream order) q_out holds the rotated queries and every active prompt's slot row at its
+ * position holds the rotated K and the V; follow with gh_attn_decode.  The intermediate kv buffer of the reference does
+ * not exist: K and V go from the tensor cores' accumulators into the slots.  Values are rounded to the storage type
+ * where the reference rounds them (xb, q, kv before the rotation, and after it).
+ * fp16 / bf16 with dim and kv_dim multiples of 128 only (GH_ERR_UNSUPPORTED otherwise).  The first call allocates
+ * scratch (batch x dim activations and a few tens of MB of partial sums). */
+int gh_attn_project_append( gh_attn_t h,
+                            uint32_t layer,
+                            const void* x,
+                            const void* rms_weight,
+                            const void* wq,
+                            const void* wkv,
+                            void* q_out,
+                            void* stream );
+
 /* A chunk of n_tokens consecutive prompt tokens per context in one call: token t of context i is appended at
  * position pos0[i] + t and attends causally over positions 0 .. pos0[i] + t.  q_inout and xb are
  * [n_ctx][n_tokens][n_heads*head_size], kv_new is [n_ctx][n_tokens][2*kv_dim] (device pointers); slots and pos0 are

@@ -1,0 +1,152 @@
+"""The stage's producer fused to the append (gh_attn_project_append) against the CPU restatement of the reference's
+rmsnorm, matmul, copy_kv_cache and apply_rope, on a GPU."""
+import numpy as np
+import pytest
+import torch
+
+from glinthawk_b200 import _lib
+from glinthawk_b200.shapes import SHAPES
+from glinthawk_b200.stage import AttentionStage, GlinthawkAttnError
+from tests import cases, gpu_util
+
+pytestmark = pytest.mark.gpu
+
+# One rounding of a sum of magnitude ~1 to the storage type may flip in the last place (the GPU adds the products in
+# another order than the reference's serial loop): 2^-10 relative for fp16, 2^-7 for bf16; the rotation then mixes
+# two such values.
+RTOL = {cases.F16: 1e-3, cases.BF16: 8e-3}
+ATOL = {cases.F16: 4e-3, cases.BF16: 3e-2}
+
+
+def _run(case: cases.ProjCase, inactive=()):
+    """project_append on fresh slots; returns q_out, the appended rows (None where inactive) and the stage."""
+    sh, B, dt = case.shape, case.B, case.dtype
+    tdt = gpu_util.TORCH_DT[dt]
+    st = AttentionStage(sh, tdt, n_layers_hosted=2, max_batch=B, max_contexts=B, paged=True)
+    st.set_rope_tables(gpu_util.to_dev(case.fcr, dt), gpu_util.to_dev(case.fci, dt))
+    slots = st.get_contexts(np.arange(1, B + 1, dtype=np.uint32)).astype(np.int32)
+    slots[list(inactive)] = -1
+    st.batch_begin(slots, case.pos)
+    q_out = torch.full((B, sh.dim), float("nan"), device="cuda", dtype=tdt)
+    st.project_append(1, gpu_util.to_dev(case.x, dt), gpu_util.to_dev(case.rms_w, dt), gpu_util.to_dev(case.wq, dt),
+                      gpu_util.to_dev(case.wkv, dt), q_out)
+    torch.cuda.synchronize()
+    assert st.stats().device_error == 0
+    rows = []
+    for i in range(B):
+        if slots[i] < 0:
+            rows.append(None)
+            continue
+        p = int(case.pos[i])
+        rows.append(gpu_util.to_host(st.layer_view(int(slots[i]), 1, p + 1), dt)[p])
+    return gpu_util.to_host(q_out, dt), rows, st, slots
+
+
+def _check(case, want, q_out, rows):
+    dt = case.dtype
+    np.testing.assert_allclose(cases.as_f32(q_out, dt), cases.as_f32(want.q_rot, dt), rtol=RTOL[dt], atol=ATOL[dt])
+    for i, row in enumerate(rows):
+        if row is not None:
+            np.testing.assert_allclose(cases.as_f32(row, dt), cases.as_f32(want.rows[i], dt), rtol=RTOL[dt], atol=ATOL[dt],
+                                       err_msg=f"slot row of prompt {i}")
+
+
+@pytest.mark.parametrize("shape_name,dtype,n", [("mini_mha", cases.F16, 5), ("mini_g4", cases.F16, 7), ("mini_g4", cases.BF16, 33),
+                                                ("mini_g8", cases.F16, 16), ("mini_g16", cases.BF16, 3)])
+def test_projection_rope_and_append_match_the_reference_operations(oracle, shape_name, dtype, n):
+    sh = SHAPES[shape_name]
+    pos = np.random.default_rng(n).integers(0, sh.seq_len, n)
+    pos[0], pos[-1] = 0, sh.seq_len - 1
+    case = cases.make_proj_case("proj", shape_name, dtype, pos, seed=40 + n)
+    want = oracle.pre_attention(case)
+    q_out, rows, st, _ = _run(case)
+    _check(case, want, q_out, rows)
+    st.close()
+
+
+def test_projection_fixture_from_the_reference(oracle):
+    """The same call against the committed outputs of the reference's own rmsnorm and matmul."""
+    from pathlib import Path
+    for spec in cases.GOLDEN_PROJ_SPECS[:2]:
+        case = cases.golden_proj_case(spec)
+        gold = np.load(Path(__file__).resolve().parent / "golden" / f"{case.name}.npz")
+        q_out, rows, st, _ = _run(case)
+        np.testing.assert_allclose(cases.as_f32(q_out, case.dtype), cases.as_f32(gold["q_rot"], case.dtype),
+                                   rtol=RTOL[case.dtype], atol=ATOL[case.dtype])
+        np.testing.assert_allclose(cases.as_f32(np.stack(rows), case.dtype), cases.as_f32(gold["rows"], case.dtype),
+                                   rtol=RTOL[case.dtype], atol=ATOL[case.dtype])
+        st.close()
+
+
+def test_inactive_prompts_get_no_row_and_large_batches_go_in_slices(oracle):
+    """300 prompts (two slices of the tensor-core tile's 256 columns), every seventh inactive: their slots stay
+    untouched, everybody else's row and q match."""
+    sh = SHAPES["mini_g4"]
+    n = 300
+    pos = np.random.default_rng(3).integers(0, sh.seq_len, n)
+    case = cases.make_proj_case("proj300", "mini_g4", cases.F16, pos, seed=77)
+    want = oracle.pre_attention(case)
+    inactive = list(range(3, n, 7))
+    q_out, rows, st, slots = _run(case, inactive=inactive)
+    _check(case, want, q_out, rows)
+    assert all(rows[i] is None for i in inactive)
+    st.close()
+
+
+def test_full_size_weights_cut_across_all_sms(oracle):
+    """Llama2-70B's matrices (8192 x 8192 and 2048 x 8192): 80 tiles of 128 k-blocks dealt to one CTA per SM, so
+    most tiles are finished from two CTAs' partial sums."""
+    sh = SHAPES["l70b_4k"]
+    pos = np.array([0, 1, 100, 1000, 4095, 17, 33, 2048], dtype=np.uint32)
+    case = cases.make_proj_case("proj70b", "l70b_4k", cases.F16, pos, seed=5)
+    want = oracle.pre_attention(case)
+    q_out, rows, st, _ = _run(case)
+    _check(case, want, q_out, rows)
+    # the same call again gives the same bits: the pieces are added in a fixed order
+    q2, rows2, st2, _ = _run(case)
+    assert np.array_equal(q_out.view(np.uint16), q2.view(np.uint16))
+    assert all(np.array_equal(a.view(np.uint16), b.view(np.uint16)) for a, b in zip(rows, rows2))
+    st.close()
+    st2.close()
+
+
+def test_projection_then_decode_equals_the_reference_layer_step(oracle):
+    """project_append followed by decode against: reference projections, then the reference's layer-step on a cache
+    that already holds a prefix."""
+    shape_name, dt = "mini_g4", cases.F16
+    sh = SHAPES[shape_name]
+    pos = [0, 9, 64, 200, 511]
+    base = cases.make_case("pd", shape_name, dt, pos, seed=12)
+    proj = cases.make_proj_case("pd", shape_name, dt, pos, seed=13)
+    pre = oracle.pre_attention(proj)
+    step = cases.Case("pd", sh, dt, base.pos, base.active, base.cache, pre.q, pre.kv, base.fcr, base.fci)
+    want = oracle.layer_step(step)
+
+    st = gpu_util.make_stage(step, layers=2, paged=True)
+    slots = gpu_util.load_case(st, step, layer=1)
+    st.batch_begin(slots, step.pos)
+    q_out = torch.zeros((len(pos), sh.dim), device="cuda", dtype=torch.float16)
+    xb = torch.zeros_like(q_out)
+    st.project_append(1, gpu_util.to_dev(proj.x, dt), gpu_util.to_dev(proj.rms_w, dt), gpu_util.to_dev(proj.wq, dt),
+                      gpu_util.to_dev(proj.wkv, dt), q_out)
+    st.decode(1, q_out, xb)
+    torch.cuda.synchronize()
+    assert st.stats().device_error == 0
+    np.testing.assert_allclose(gpu_util.to_host(xb, dt).astype(np.float32), want.xb.astype(np.float32), rtol=0,
+                               atol=cases.TOL_XB[dt])
+    st.close()
+
+
+def test_unsupported_shapes_are_refused():
+    sh = SHAPES["tiny15m"]  # fp32, dim 288
+    st = AttentionStage(sh, torch.float32, n_layers_hosted=1, max_batch=2, max_contexts=2)
+    cos = torch.ones(sh.seq_len, sh.head_size // 2, device="cuda")
+    st.set_rope_tables(cos, torch.zeros_like(cos))
+    s = st.get_context(1)
+    st.batch_begin([s], [0])
+    x = torch.zeros(1, sh.dim, device="cuda")
+    w = torch.zeros(sh.dim, sh.dim, device="cuda")
+    with pytest.raises(GlinthawkAttnError) as e:
+        st.project_append(0, x, x[0], w, torch.zeros(2 * sh.kv_dim, sh.dim, device="cuda"), torch.zeros_like(x))
+    assert e.value.status == _lib.GH_ERR_UNSUPPORTED
+    st.close()
