@@ -115,8 +115,7 @@ struct gh_attn
 
   // q / kv projection (allocated by the first gh_attn_project_append call)
   void* proj_xb = nullptr;        // rmsnorm output, [max_batch][dim]
-  float* proj_ws = nullptr;       // partial sums of the tiles that were cut
-  uint32_t* proj_count = nullptr; // [tiles] pieces arrived, zero between launches
+  float* proj_ws = nullptr;       // fp32 sums of every piece of every tile
   bool proj_ready = false;
 };
 
@@ -529,7 +528,6 @@ int gh_attn_destroy( gh_attn_t h )
   cudaFree( h->dev_error );
   cudaFree( h->proj_xb );
   cudaFree( h->proj_ws );
-  cudaFree( h->proj_count );
   h->pool.destroy();
   (void)cudaGetLastError();
   delete h;
@@ -774,8 +772,6 @@ int gh_attn_project_append( gh_attn_t h,
     GH_CUDA( h, project_prepare() );
     GH_CUDA( h, cudaMalloc( &h->proj_xb, static_cast<size_t>( h->cfg.max_batch ) * dim * h->elem ) );
     GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &h->proj_ws ), project_workspace_bytes( a ) ) );
-    GH_CUDA( h, cudaMalloc( reinterpret_cast<void**>( &h->proj_count ), a.n_tiles * sizeof( uint32_t ) ) );
-    GH_CUDA( h, cudaMemset( h->proj_count, 0, a.n_tiles * sizeof( uint32_t ) ) );
     h->stats.scratch_bytes += static_cast<size_t>( h->cfg.max_batch ) * dim * h->elem + project_workspace_bytes( a );
     h->proj_ready = true;
   }
@@ -813,7 +809,6 @@ int gh_attn_project_append( gh_attn_t h,
   a.rope_cos = h->rope_cos;
   a.rope_sin = h->rope_sin;
   a.ws = h->proj_ws;
-  a.seg_count = h->proj_count;
   a.dev_error = h->dev_error;
   // the MMA's N takes at most project_max_rows() batch rows: larger batches go in slices (the weights are then
   // streamed once per slice)

@@ -93,7 +93,6 @@ struct ProjectArgs
   const void* rope_cos; // [seq_len][head_size / 2]
   const void* rope_sin;
   float* ws;           // project_workspace_bytes()
-  uint32_t* seg_count; // [n_tiles], zero between launches
   uint32_t* dev_error;
 };
 bool project_supported( const Shape& sh, uint32_t dtype );

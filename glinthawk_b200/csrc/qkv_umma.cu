@@ -5,7 +5,7 @@
 //   rmsnorm( xb, x, rms_att_weight ); matmul( q, xb, wq ); matmul( kv, xb, wkv );   src/models/llama2/model.hh:326-343
 //   copy_kv_cache( token_contexts, kv ); apply_rope( pos, fcr, fci, q, token_contexts )            model.hh:345-360
 // (operations: src/arch/amd64/common/ops.hh:141-170, 212-229; src/arch/amd64/llama2/ops.hh:138-164, 300-352).  The kv
-// scratch buffer disappears: K and V go from TMEM into the slot rows.  Rounding points are the reference's: xb, q and
+// scratch buffer in the storage type disappears: K and V go from the fp32 sums into the slot rows.  Rounding points are the reference's: xb, q and
 // kv are rounded to the storage type, the rotation is done in fp32 on those rounded values with separately rounded
 // products and rounded once more.
 //
@@ -14,12 +14,14 @@
 //   D[128 features x Nb batch rows] += W[128 x 64] . XB[Nb x 64]^T          tcgen05.mma M = 128, N = Nb <= 256, fp32 in TMEM
 // Work unit = (tile of 128 output features, block of 64 k).  The units are dealt to the CTAs (one per SM) as equal
 // contiguous runs, so a CTA works through the tail of one tile, some whole tiles and the head of another
-// ("stream-K"): all SMs stream weights for the same time whatever the number of tiles.  A tile that was cut leaves
-// its partial sums in a workspace, one slot per piece; the CTA whose piece completes the tile (an atomic counter tells
-// it, nobody waits for anybody) adds the pieces in a fixed order and runs the epilogue.
+// ("stream-K"): all SMs stream weights for the same time whatever the number of tiles.  Every piece leaves its fp32
+// sums in a workspace slot of its own, and a second, wide kernel adds the pieces of each tile in a fixed order, rounds,
+// rotates and stores: no counters, no waiting, the same bits on every run.  (Finishing tiles inside the GEMM kernel,
+// by whichever CTA delivered the last piece, was measured first: with only the four read-out warps per SM doing the
+// rotation it cost 70 us of tail at 256 rows; the wide kernel costs a few.)
 //
-// Roles per CTA: warps 0..3 = epilogue (thread r owns feature r of the tile = TMEM lane r), one lane of warp 4 = TMA
-// producer (4-stage ring of W and XB tiles, 128-byte swizzle), one lane of warp 5 = MMA issuer.  Two TMEM accumulators
+// Roles per CTA: warps 0..3 = read-out (thread r owns feature r of the tile = TMEM lane r), one lane of warp 4 = TMA
+// producer (ring of W and XB tiles, 4 to 10 stages deep, 128-byte swizzle), one lane of warp 5 = MMA issuer.  Two TMEM accumulators
 // so that the next piece is multiplied while the previous one is written out.  Every wait is bounded.
 #include <algorithm>
 #include <type_traits>
@@ -35,29 +37,41 @@ using namespace umma;
 
 constexpr int kTileF = 128;                   // output features per tile = MMA M = TMEM lanes
 constexpr int kBK = 64;                       // k elements per stage: one 128-byte swizzled row
-constexpr int kStages = 4;
 constexpr int kMaxNb = 256;                   // batch rows per launch = MMA N
 constexpr int kATile = kTileF * 128;          // 16 KiB of weights per stage
-constexpr int kBTile = kMaxNb * 128;          // up to 32 KiB of activations per stage
-constexpr int kStageBytes = kATile + kBTile;
-constexpr int kOffBar = kStages * kStageBytes; // 192 KiB, then: barriers | pos[256] | slot-row offsets[256]
-constexpr int kOffPos = kOffBar + 256;
-constexpr int kOffRow = kOffPos + kMaxNb * 4;
-constexpr int kSmemBytes = kOffRow + kMaxNb * 8;
+constexpr int kRing = 4 * ( kATile + kMaxNb * 128 ); // 192 KiB of stages: 4 at 256 batch rows, more when the
+constexpr int kMaxStages = 10;                //   activation tile is smaller (a stage is 16 KiB + nb * 128 B)
+constexpr int kOffBar = kRing;                // then the barriers: ( 2 * kMaxStages + 6 ) words of 8 bytes
+constexpr int kSmemBytes = kOffBar + 256;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;                // two accumulators of up to 256 columns
+
+// One block per row; the row is read once, in 16-byte pieces, and kept in registers between the two passes
+// (up to kNormPieces pieces per thread: dim <= 256 * kNormPieces * elements per piece).
+constexpr int kNormPieces = 8;
 
 template<typename T>
 __global__ void __launch_bounds__( 256 ) rmsnorm_kernel( T* __restrict__ out, const T* __restrict__ x,
                                                           const T* __restrict__ weight, uint32_t dim )
 {
+  constexpr int N = Vec16<T>::N;
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
   const T* X = x + (size_t)blockIdx.x * dim;
   T* O = out + (size_t)blockIdx.x * dim;
+  const uint32_t pieces = dim / N; // dim is a multiple of 128
+  Vec16<T> row[kNormPieces];
   float ss = 0.f;
-  for ( uint32_t j = threadIdx.x; j < dim; j += blockDim.x ) {
-    const float v = Conv<T>::to_f32( X[j] );
-    ss += v * v;
+#pragma unroll
+  for ( int k = 0; k < kNormPieces; k++ ) {
+    const uint32_t p = threadIdx.x + k * 256;
+    if ( p < pieces ) {
+      row[k] = ld16( X + (size_t)p * N );
+#pragma unroll
+      for ( int e = 0; e < N; e++ ) {
+        const float v = Conv<T>::to_f32( row[k].v[e] );
+        ss += v * v;
+      }
+    }
   }
   __shared__ float part[8];
   ss = warp_sum( ss );
@@ -72,8 +86,18 @@ __global__ void __launch_bounds__( 256 ) rmsnorm_kernel( T* __restrict__ out, co
   tot /= dim;
   tot += 1e-5f;
   tot = 1.0f / sqrtf( tot );
-  for ( uint32_t j = threadIdx.x; j < dim; j += blockDim.x )
-    O[j] = Conv<T>::from_f32( __fmul_rn( Conv<T>::to_f32( weight[j] ), __fmul_rn( tot, Conv<T>::to_f32( X[j] ) ) ) );
+#pragma unroll
+  for ( int k = 0; k < kNormPieces; k++ ) {
+    const uint32_t p = threadIdx.x + k * 256;
+    if ( p < pieces ) {
+      const Vec16<T> w = ld16( weight + (size_t)p * N );
+      Vec16<T> o;
+#pragma unroll
+      for ( int e = 0; e < N; e++ )
+        o.v[e] = Conv<T>::from_f32( __fmul_rn( Conv<T>::to_f32( w.v[e] ), __fmul_rn( tot, Conv<T>::to_f32( row[k].v[e] ) ) ) );
+      st16( O + (size_t)p * N, o );
+    }
+  }
 }
 
 // The run of work units CTA `c` owns, and the pieces (tile, k-block range) it falls into.
@@ -102,15 +126,12 @@ __global__ void __launch_bounds__( kThreads, 1 )
 {
   extern __shared__ __align__( 1024 ) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>( smem + kOffBar );
-  uint64_t* bar_full = bars;           // [kStages] tiles of a stage have landed          (TMA -> MMA lane)
-  uint64_t* bar_empty = bars + 4;      // [kStages] the MMAs reading a stage have completed (MMA -> TMA lane)
-  uint64_t* bar_acc_full = bars + 8;   // [2] a piece's accumulator is complete            (MMA -> epilogue)
-  uint64_t* bar_acc_free = bars + 10;  // [2] the accumulator has been read out            (epilogue -> MMA lane)
-  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>( bars + 12 );
-  volatile int* fail = reinterpret_cast<volatile int*>( bars + 13 );
-  volatile int* last_flag = reinterpret_cast<volatile int*>( bars + 14 );
-  uint32_t* pos_s = reinterpret_cast<uint32_t*>( smem + kOffPos );
-  long long* row_s = reinterpret_cast<long long*>( smem + kOffRow );
+  uint64_t* bar_full = bars;                    // [stages] tiles of a stage have landed          (TMA -> MMA lane)
+  uint64_t* bar_empty = bars + kMaxStages;      // [stages] the MMAs reading a stage have completed (MMA -> TMA lane)
+  uint64_t* bar_acc_full = bars + 2 * kMaxStages;     // [2] a piece's accumulator is complete     (MMA -> epilogue)
+  uint64_t* bar_acc_free = bars + 2 * kMaxStages + 2; // [2] the accumulator has been read out     (epilogue -> MMA lane)
+  uint32_t* tmem_base_p = reinterpret_cast<uint32_t*>( bars + 2 * kMaxStages + 4 );
+  volatile int* fail = reinterpret_cast<volatile int*>( bars + 2 * kMaxStages + 5 );
 
   const int r = threadIdx.x;
   const int warp = r >> 5;
@@ -125,10 +146,12 @@ __global__ void __launch_bounds__( kThreads, 1 )
   const int u_begin = blockIdx.x * upc;
   const int u_end = min( (int)( a.n_tiles * a.kblocks ), u_begin + upc );
   const int nb = a.nb;
+  const int stage_bytes = kATile + ( ( nb * 128 + 1023 ) & ~1023 ); // both tiles 1024-byte aligned
+  const int n_stages = min( kMaxStages, kRing / stage_bytes );
 
   if ( r == 0 ) {
     *fail = 0;
-    for ( int i = 0; i < 10; i++ )
+    for ( int i = 0; i < 2 * kMaxStages + 2; i++ )
       asm volatile( "mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"( smem_u32( &bars[i] ) ) );
     asm volatile( "mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"( smem_u32( &bar_acc_free[0] ) ), "r"( kTileF ) );
     asm volatile( "mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"( smem_u32( &bar_acc_free[1] ) ), "r"( kTileF ) );
@@ -138,19 +161,6 @@ __global__ void __launch_bounds__( kThreads, 1 )
     asm volatile( "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"( smem_u32( tmem_base_p ) ),
                   "r"( kTmemCols ) );
     asm volatile( "tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" );
-  }
-  // positions and slot-row byte offsets of the batch rows this launch covers
-  for ( int i = r; i < nb; i += kThreads ) {
-    uint32_t p = 0;
-    long long off = -1;
-    if ( i < (int)a.batch ) {
-      const CtxMeta c = a.ctx[a.batch0 + i];
-      p = c.pos;
-      if ( c.kv_off != kInactive )
-        off = c.kv_off + a.layer_off + (long long)c.pos * a.sh.row_elems * (long long)sizeof( T );
-    }
-    pos_s[i] = p;
-    row_s[i] = off;
   }
   asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
   __syncthreads();
@@ -172,12 +182,12 @@ __global__ void __launch_bounds__( kThreads, 1 )
         const CUtensorMap* wmap = is_q ? &wq_map : &wkv_map;
         const int wrow = ( is_q ? p.tile : p.tile - (int)a.q_tiles ) * kTileF;
         for ( int kb = p.k0; kb < p.k1 && ok; kb++, n++ ) {
-          const int s = n % kStages;
-          if ( n >= (uint32_t)kStages )
-            ok = mbar_wait( &bar_empty[s], ( n / kStages - 1 ) & 1, fail );
+          const int s = n % n_stages;
+          if ( n >= (uint32_t)n_stages )
+            ok = mbar_wait( &bar_empty[s], ( n / n_stages - 1 ) & 1, fail );
           if ( !ok )
             break;
-          uint8_t* sA = smem + s * kStageBytes;
+          uint8_t* sA = smem + s * stage_bytes;
           asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( &bar_full[s] ) ),
                         "r"( (uint32_t)( kATile + nb * 128 ) )
                         : "memory" );
@@ -205,12 +215,12 @@ __global__ void __launch_bounds__( kThreads, 1 )
           asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
         }
         for ( int kb = p.k0; kb < p.k1 && ok; kb++, n++ ) {
-          const int s = n % kStages;
-          ok = mbar_wait( &bar_full[s], ( n / kStages ) & 1, fail );
+          const int s = n % n_stages;
+          ok = mbar_wait( &bar_full[s], ( n / n_stages ) & 1, fail );
           if ( !ok )
             break;
           asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-          const uint32_t sA = smem_u32( smem + s * kStageBytes );
+          const uint32_t sA = smem_u32( smem + s * stage_bytes );
 #pragma unroll
           for ( int k = 0; k < kBK / 16; k++ )
             umma_f16( tmem_base + ab * kMaxNb, desc_kmajor( sA + k * 32 ), desc_kmajor( sA + kATile + k * 32 ), idesc,
@@ -225,46 +235,15 @@ __global__ void __launch_bounds__( kThreads, 1 )
         *fail = 1;
     }
   } else {
-    // =========================== epilogue (warps 0..3): thread r owns feature r of the tile ===========================
+    // =========================== accumulator read-out (warps 0..3): thread r owns feature r of the tile ===========================
+    // Every piece leaves its fp32 sums in its own workspace slot, [batch row][feature]; project_finish_kernel adds
+    // the pieces of a tile in their fixed order and does the rest.  Nobody counts arrivals or waits for anybody.
     const uint32_t lane_off = static_cast<uint32_t>( warp * 32 ) << 16; // this warp's quarter of the TMEM lanes
-    const int hs = a.sh.head_size;
-    const int dim = a.dim, kv_dim = a.sh.kv_dim, batch = a.batch;
-    const T* cos_t = static_cast<const T*>( a.rope_cos );
-    const T* sin_t = static_cast<const T*>( a.rope_sin );
-    const bool odd = ( r & 1 ) != 0;
-
-    // 32 batch rows of one feature: round to the storage type (the reference stores q and kv there), rotate the
-    // (even, odd) feature pair held by neighbouring lanes, and put the value where it belongs: q, or the slot row.
-    auto store_chunk = [&]( int tile, int cb, const float ( &v )[32] ) {
-      const int f = tile * kTileF + r;
-      const bool rotate = f < dim + kv_dim; // q and K; a tile never straddles two of q, K, V
-      const int d2 = ( f % hs ) >> 1;
-#pragma unroll 4
-      for ( int j = 0; j < 32; j++ ) {
-        const int i = cb * 32 + j;
-        if ( i >= batch )
-          break;
-        float x = Conv<T>::to_f32( Conv<T>::from_f32( v[j] ) );
-        if ( rotate ) {
-          const float other = __shfl_xor_sync( kFull, x, 1 );
-          const size_t ti = (size_t)pos_s[i] * ( hs / 2 ) + d2;
-          const float c = Conv<T>::to_f32( cos_t[ti] ), s = Conv<T>::to_f32( sin_t[ti] );
-          const float x0 = odd ? other : x, x1 = odd ? x : other;
-          // src/arch/amd64/llama2/ops.hh:150-162: separately rounded products
-          x = odd ? __fadd_rn( __fmul_rn( x0, s ), __fmul_rn( x1, c ) ) : __fsub_rn( __fmul_rn( x0, c ), __fmul_rn( x1, s ) );
-        }
-        const T o = Conv<T>::from_f32( x );
-        if ( f < dim ) {
-          static_cast<T*>( a.q_out )[(size_t)( a.batch0 + i ) * dim + f] = o;
-        } else if ( row_s[i] >= 0 ) {
-          *reinterpret_cast<T*>( a.arena + row_s[i] + (size_t)( f - dim ) * sizeof( T ) ) = o;
-        }
-      }
-    };
-
+    const int batch = a.batch;
+    const int n_chunks = ( batch + 31 ) / 32;
+    const size_t slot_floats = (size_t)n_chunks * 32 * kTileF;
     bool ok = true;
     uint32_t piece_i = 0;
-    const int n_chunks = ( batch + 31 ) / 32;
     for ( int u = u_begin; u < u_end; piece_i++ ) {
       const Piece p = piece_at( u, u_end, kblocks, upc );
       const int ab = piece_i & 1;
@@ -273,58 +252,16 @@ __global__ void __launch_bounds__( kThreads, 1 )
         break;
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
       const uint32_t tacc = tmem_base + ab * kMaxNb + lane_off;
-      if ( p.nsegs == 1 ) {
-        // ---- the whole tile was accumulated here
-        for ( int cb = 0; cb < n_chunks; cb++ ) {
-          float v[32];
-          tmem_ld32( tacc + cb * 32, v );
-          store_chunk( p.tile, cb, v );
-        }
-        asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
-        asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_acc_free[ab] ) ) : "memory" );
-      } else {
-        // ---- a piece of a tile: leave the partial sums in this piece's workspace slot, [batch row][feature]
-        float* slot = a.ws + ( (size_t)p.tile * a.max_segs + p.seg ) * ( (size_t)nb * kTileF );
-        for ( int cb = 0; cb < n_chunks; cb++ ) {
-          float v[32];
-          tmem_ld32( tacc + cb * 32, v );
+      float* slot = a.ws + ( (size_t)p.tile * a.max_segs + p.seg ) * slot_floats;
+      for ( int cb = 0; cb < n_chunks; cb++ ) {
+        float v[32];
+        tmem_ld32( tacc + cb * 32, v );
 #pragma unroll
-          for ( int j = 0; j < 32; j++ )
-            if ( cb * 32 + j < batch )
-              slot[(size_t)( cb * 32 + j ) * kTileF + r] = v[j];
-        }
-        asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
-        asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_acc_free[ab] ) ) : "memory" );
-        __threadfence();
-        asm volatile( "bar.sync 1, %0;" ::"n"( kTileF ) : "memory" );
-        if ( r == 0 ) {
-          const uint32_t arrived = atomicAdd( &a.seg_count[p.tile], 1u );
-          const bool last = arrived == (uint32_t)p.nsegs - 1;
-          if ( last )
-            a.seg_count[p.tile] = 0; // every piece has arrived: ready for the next launch
-          *last_flag = last ? 1 : 0;
-        }
-        asm volatile( "bar.sync 1, %0;" ::"n"( kTileF ) : "memory" );
-        if ( *last_flag != 0 ) {
-          // ---- this piece completed the tile: add the pieces in their fixed order and finish the tile
-          __threadfence();
-          const float* tile_ws = a.ws + (size_t)p.tile * a.max_segs * ( (size_t)nb * kTileF );
-          for ( int cb = 0; cb < n_chunks; cb++ ) {
-            float v[32];
-#pragma unroll
-            for ( int j = 0; j < 32; j++ )
-              v[j] = 0.f;
-            for ( int sgm = 0; sgm < p.nsegs; sgm++ ) {
-              const float* src = tile_ws + (size_t)sgm * ( (size_t)nb * kTileF );
-#pragma unroll
-              for ( int j = 0; j < 32; j++ )
-                if ( cb * 32 + j < batch )
-                  v[j] += __ldcg( src + (size_t)( cb * 32 + j ) * kTileF + r );
-            }
-            store_chunk( p.tile, cb, v );
-          }
-        }
+        for ( int j = 0; j < 32; j++ ) // (columns past the batch are never read back)
+          slot[(size_t)( cb * 32 + j ) * kTileF + r] = v[j];
       }
+      asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
+      asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( &bar_acc_free[ab] ) ) : "memory" );
       u += p.k1 - p.k0;
     }
     if ( !ok )
@@ -338,6 +275,63 @@ __global__ void __launch_bounds__( kThreads, 1 )
   if ( warp == 5 ) {
     __syncwarp();
     asm volatile( "tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"( tmem_base ), "r"( kTmemCols ) );
+  }
+}
+
+// Second step of the projection: one block = (tile of 128 features, 32 batch rows); a thread owns one (even, odd)
+// feature pair and walks 8 of the rows.  It adds the tile's pieces in their fixed order (deterministic), rounds to the
+// storage type (the reference stores q and kv there), rotates q and K pairs by the row's position with separately
+// rounded products (src/arch/amd64/llama2/ops.hh:150-162) and writes q, or K/V straight into the slot row.
+template<typename T>
+__global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArgs a )
+{
+  asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
+  const int tile = blockIdx.x;
+  const int pair = threadIdx.x & 63; // features 2 * pair, 2 * pair + 1 of the tile
+  const int sub = threadIdx.x >> 6;  // rows sub, sub + 4, ... of the block's 32
+  const int hs = a.sh.head_size;
+  const int dim = a.dim, kv_dim = a.sh.kv_dim, batch = a.batch;
+  const int f = tile * kTileF + 2 * pair;
+  const bool rotate = f < dim + kv_dim;
+  const int d2 = ( f % hs ) >> 1;
+  const int first = tile * (int)a.kblocks, last = first + (int)a.kblocks - 1;
+  const int nsegs = last / (int)a.units_per_cta - first / (int)a.units_per_cta + 1;
+  const size_t slot_floats = (size_t)( ( batch + 31 ) / 32 ) * 32 * kTileF;
+  const float* tile_ws = a.ws + (size_t)tile * a.max_segs * slot_floats;
+  const T* __restrict__ cos_t = static_cast<const T*>( a.rope_cos );
+  const T* __restrict__ sin_t = static_cast<const T*>( a.rope_sin );
+  // the partial sums come from the projection kernel, the kernel before this one in the stream
+  asm volatile( "griddepcontrol.wait;" ::: "memory" );
+#pragma unroll
+  for ( int k = 0; k < 8; k++ ) {
+    const int i = blockIdx.y * 32 + sub + 4 * k;
+    if ( i >= batch )
+      break;
+    const CtxMeta c = a.ctx[a.batch0 + i];
+    float2 acc = make_float2( 0.f, 0.f );
+    for ( int s = 0; s < nsegs; s++ ) {
+      const float2 part = __ldcg( reinterpret_cast<const float2*>( tile_ws + (size_t)s * slot_floats + (size_t)i * kTileF + 2 * pair ) );
+      acc.x += part.x;
+      acc.y += part.y;
+    }
+    float x0 = Conv<T>::to_f32( Conv<T>::from_f32( acc.x ) ), x1 = Conv<T>::to_f32( Conv<T>::from_f32( acc.y ) );
+    if ( rotate ) {
+      const size_t ti = (size_t)c.pos * ( hs / 2 ) + d2;
+      const float cs = Conv<T>::to_f32( cos_t[ti] ), sn = Conv<T>::to_f32( sin_t[ti] );
+      const float y0 = __fsub_rn( __fmul_rn( x0, cs ), __fmul_rn( x1, sn ) );
+      const float y1 = __fadd_rn( __fmul_rn( x0, sn ), __fmul_rn( x1, cs ) );
+      x0 = y0, x1 = y1;
+    }
+    const T o0 = Conv<T>::from_f32( x0 ), o1 = Conv<T>::from_f32( x1 );
+    const uint32_t bits = static_cast<uint32_t>( *reinterpret_cast<const uint16_t*>( &o0 ) )
+                          | ( static_cast<uint32_t>( *reinterpret_cast<const uint16_t*>( &o1 ) ) << 16 );
+    T* dst = nullptr;
+    if ( f < dim )
+      dst = static_cast<T*>( a.q_out ) + (size_t)( a.batch0 + i ) * dim + f;
+    else if ( c.kv_off != kInactive )
+      dst = reinterpret_cast<T*>( a.arena + c.kv_off + a.layer_off ) + (size_t)c.pos * a.sh.row_elems + ( f - dim );
+    if ( dst != nullptr )
+      *reinterpret_cast<uint32_t*>( dst ) = bits;
   }
 }
 
@@ -388,6 +382,9 @@ cudaError_t launch_rmsnorm( void* out, const void* x, const void* weight, uint32
 {
   if ( rows == 0 )
     return cudaSuccess;
+  const uint32_t per_piece = dtype == DT_F32 ? 4 : 8;
+  if ( dim % per_piece != 0 || dim > 256u * kNormPieces * per_piece )
+    return cudaErrorInvalidValue;
   switch ( dtype ) {
     case DT_F32:
       rmsnorm_kernel<float><<<rows, 256, 0, st>>>( static_cast<float*>( out ), static_cast<const float*>( x ),
@@ -430,6 +427,16 @@ cudaError_t launch_project( const ProjectArgs& a, uint32_t grid, const CUtensorM
     e = cudaLaunchKernelEx( &cfg, project_kernel<__nv_bfloat16>, a, *wq_map, *wkv_map, *xb_map );
   else
     return cudaErrorInvalidValue;
+  ( *launches )++;
+  if ( e != cudaSuccess )
+    return e;
+  cfg.gridDim = dim3( a.n_tiles, ( a.batch + 31 ) / 32 );
+  cfg.blockDim = dim3( 256 );
+  cfg.dynamicSmemBytes = 0;
+  if ( a.dtype == DT_F16 )
+    e = cudaLaunchKernelEx( &cfg, project_finish_kernel<__half>, a );
+  else
+    e = cudaLaunchKernelEx( &cfg, project_finish_kernel<__nv_bfloat16>, a );
   ( *launches )++;
   return e;
 }
