@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--static", action="store_true", help="fully resident slots instead of paged ones")
     ap.add_argument("--decode-chunk", type=int, default=0)
+    ap.add_argument("--producer", action="store_true",
+                    help="each layer-step also runs the stage's producer on the device (rmsnorm + q/kv projection with "
+                         "the RoPE + append epilogue, gh_attn_project_append) instead of taking q and K/V rows as given")
     return ap.parse_args()
 
 
@@ -278,6 +281,16 @@ def main():
     torch.cuda.synchronize()
     t_setup = time.perf_counter() - t_setup
 
+    if args.producer:  # residual stream, rmsnorm weights and per-layer projection matrices (random, scaled so q, k, v ~ N(0,1))
+        x_all = torch.randn((batch, sh.dim), device=dev).to(tdt)
+        rms_w = torch.ones(sh.dim, device=dev, dtype=tdt)
+        wq_all = torch.empty((n_layers, sh.dim, sh.dim), dtype=tdt, device=dev)
+        wkv_all = torch.empty((n_layers, row_elems, sh.dim), dtype=tdt, device=dev)
+        for l in range(n_layers):
+            wq_all[l] = (torch.randn((sh.dim, sh.dim), device=dev) / sh.dim ** 0.5).to(tdt)
+            wkv_all[l] = (torch.randn((row_elems, sh.dim), device=dev) / sh.dim ** 0.5).to(tdt)
+        E = 0  # the host-buffer entry point takes q and K/V rows, not the residual stream
+    torch.cuda.synchronize()
     pos = lens0.astype(np.uint32).copy()  # position of the token appended next = tokens cached so far
     stream = torch.cuda.current_stream()
 
@@ -293,13 +306,30 @@ def main():
     st_ptr = C.c_void_p(stream.cuda_stream)
     handle = stage._h
 
+    producer_events = []
+
     def device_step(record=None):
         """One token for every context through all layers.  With `record`, every 8th layer's decode launch is
         bracketed by events (the append and decode launches of the other layers stay back to back, which is what
         lets the decode kernel's prologue overlap the append kernel)."""
         stage.batch_begin(slots, pos)
         for l in range(n_layers):
-            if record is not None and l % 8 == min(3, n_layers - 1):
+            if args.producer:
+                timed = record is not None and l % 8 == min(3, n_layers - 1)
+                if timed:
+                    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    p0.record(stream)
+                stage.project_append(l, x_all, rms_w, wq_all[l], wkv_all[l], q_all[l])
+                if timed:
+                    p1.record(stream)
+                    producer_events.append((p0, p1))
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                stage.decode(l, q_all[l], xb_all[l])
+                if timed:
+                    e1.record(stream)
+                    record.append((e0, e1))
+            elif record is not None and l % 8 == min(3, n_layers - 1):
                 stage.append(l, q_all[l], kv_all[l])
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
@@ -327,6 +357,7 @@ def main():
     except Exception:  # noqa: BLE001
         pass
     launches0 = stage.stats().kernel_launches
+    producer_events.clear()
     decode_events, kv_tokens = [], []
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(uuid) as clocks:
@@ -396,9 +427,19 @@ def main():
     stats = stage.stats()
     if stats.device_error:
         raise SystemExit(f"device error flag {stats.device_error}")
+    producer = None
+    if args.producer:
+        pms = [a.elapsed_time(b) for a, b in producer_events]
+        pms_mean = sum(pms) / len(pms)
+        w_bytes = (sh.dim + row_elems) * sh.dim * elem
+        flops = 2.0 * batch * (sh.dim + row_elems) * sh.dim
+        producer = {"kernels": "rmsnorm_kernel + project_kernel (tcgen05) + project_finish_kernel",
+                    "ms_per_layer": pms_mean, "weight_bytes_per_layer": w_bytes,
+                    "weights_gbs": w_bytes / (pms_mean / 1e3) / 1e9, "tflops": flops / (pms_mean / 1e3) / 1e12,
+                    "weights_frac_of_measured_hbm": w_bytes / (pms_mean / 1e3) / 1e9 / peak}
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.producer:  # the CPU sample times the stage alone
         use_all_host_threads()
         cpu, _ = time_cpu_sample(wl, lens0, args.cpu_contexts, n_layers, args.seed, reps=3)
 
@@ -407,8 +448,11 @@ def main():
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": max(W, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": wl.dtype, "data": "synthetic",
-            "config": {"workload": wl.name, "description": wl.description, "layers": n_layers,
-                       "contexts_per_gpu": batch, "slots": "static" if args.static else "paged (2 MiB pages)",
+            "config": {"workload": wl.name + ("+producer" if args.producer else ""),
+                       "description": wl.description + (
+                           "; every layer-step starts from the residual stream: rmsnorm, q and kv projections, RoPE and "
+                           "append run fused on the device" if args.producer else ""),
+                       "layers": n_layers, "contexts_per_gpu": batch, "slots": "static" if args.static else "paged (2 MiB pages)",
                        "mean_cached_tokens": mean_tokens / batch, "kv_resident_gb": stats.bytes_mapped / 1e9,
                        "l2": "inputs larger than L2: each layer-step streams %.2f GB of KV" % (mean_tokens * row / 1e9),
                        "parallelism": f"contexts sharded by request over {world} GPU(s), no collective",
@@ -424,7 +468,7 @@ def main():
             "clocks": clocks.summary(),
             "e2e": e2e,
             "gpu_launches": int(launches),
-            "cpu_baseline": cpu,
+            "cpu_baseline": cpu, "producer": producer,
             "setup_s": t_setup,
         }
         print(json.dumps(out))
