@@ -48,6 +48,15 @@ __device__ __forceinline__ void tma_load_2d( void* dst, const CUtensorMap* map, 
                 : "memory" );
 }
 
+// The same with an L2 eviction policy (from createpolicy) for the fetched lines.
+__device__ __forceinline__ void tma_load_2d_hint( void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar, uint64_t policy )
+{
+  asm volatile( "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+                ::"r"( smem_u32( dst ) ),
+                "l"( reinterpret_cast<uint64_t>( map ) ), "r"( x ), "r"( y ), "r"( smem_u32( bar ) ), "l"( policy )
+                : "memory" );
+}
+
 __device__ __forceinline__ void tma_load_4d( void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar )
 {
   asm volatile( "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"

@@ -176,6 +176,8 @@ __global__ void __launch_bounds__( kThreads, 1 )
     if ( r == 4 * 32 ) {
       bool ok = true;
       uint32_t n = 0; // stages filled so far
+      uint64_t stream_policy;
+      asm volatile( "createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"( stream_policy ) );
       for ( int u = u_begin; u < u_end && ok; ) {
         const Piece p = piece_at( u, u_end, kblocks, upc );
         const bool is_q = p.tile < (int)a.q_tiles;
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__( kThreads, 1 )
           asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( &bar_full[s] ) ),
                         "r"( (uint32_t)( kATile + nb * 128 ) )
                         : "memory" );
-          tma_load_2d( sA, wmap, kb * kBK, wrow, &bar_full[s] );
+          tma_load_2d_hint( sA, wmap, kb * kBK, wrow, &bar_full[s], stream_policy ); // read once: do not keep in L2
           tma_load_2d( sA + kATile, &xb_map, kb * kBK, (int)a.batch0, &bar_full[s] ); // rows past the batch arrive as zeros
         }
         u += p.k1 - p.k0;
@@ -302,24 +304,47 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
   const T* __restrict__ sin_t = static_cast<const T*>( a.rope_sin );
   // the partial sums come from the projection kernel, the kernel before this one in the stream
   asm volatile( "griddepcontrol.wait;" ::: "memory" );
+  // three rounds of independent loads (row records, partial sums, table values), each with all eight rows in flight
+  CtxMeta c[8];
+  float2 acc[8];
+#pragma unroll
+  for ( int k = 0; k < 8; k++ ) {
+    const int i = blockIdx.y * 32 + sub + 4 * k;
+    if ( i < batch )
+      c[k] = a.ctx[a.batch0 + i];
+    acc[k] = make_float2( 0.f, 0.f );
+  }
+  for ( int s = 0; s < nsegs; s++ ) { // fixed order: the same bits on every run
+#pragma unroll
+    for ( int k = 0; k < 8; k++ ) {
+      const int i = blockIdx.y * 32 + sub + 4 * k;
+      if ( i < batch ) {
+        const float2 part
+          = __ldcg( reinterpret_cast<const float2*>( tile_ws + (size_t)s * slot_floats + (size_t)i * kTileF + 2 * pair ) );
+        acc[k].x += part.x;
+        acc[k].y += part.y;
+      }
+    }
+  }
+  float cs[8], sn[8];
+#pragma unroll
+  for ( int k = 0; k < 8; k++ ) {
+    const int i = blockIdx.y * 32 + sub + 4 * k;
+    if ( rotate && i < batch ) {
+      const size_t ti = (size_t)c[k].pos * ( hs / 2 ) + d2;
+      cs[k] = Conv<T>::to_f32( __ldg( cos_t + ti ) );
+      sn[k] = Conv<T>::to_f32( __ldg( sin_t + ti ) );
+    }
+  }
 #pragma unroll
   for ( int k = 0; k < 8; k++ ) {
     const int i = blockIdx.y * 32 + sub + 4 * k;
     if ( i >= batch )
-      break;
-    const CtxMeta c = a.ctx[a.batch0 + i];
-    float2 acc = make_float2( 0.f, 0.f );
-    for ( int s = 0; s < nsegs; s++ ) {
-      const float2 part = __ldcg( reinterpret_cast<const float2*>( tile_ws + (size_t)s * slot_floats + (size_t)i * kTileF + 2 * pair ) );
-      acc.x += part.x;
-      acc.y += part.y;
-    }
-    float x0 = Conv<T>::to_f32( Conv<T>::from_f32( acc.x ) ), x1 = Conv<T>::to_f32( Conv<T>::from_f32( acc.y ) );
+      continue;
+    float x0 = Conv<T>::to_f32( Conv<T>::from_f32( acc[k].x ) ), x1 = Conv<T>::to_f32( Conv<T>::from_f32( acc[k].y ) );
     if ( rotate ) {
-      const size_t ti = (size_t)c.pos * ( hs / 2 ) + d2;
-      const float cs = Conv<T>::to_f32( cos_t[ti] ), sn = Conv<T>::to_f32( sin_t[ti] );
-      const float y0 = __fsub_rn( __fmul_rn( x0, cs ), __fmul_rn( x1, sn ) );
-      const float y1 = __fadd_rn( __fmul_rn( x0, sn ), __fmul_rn( x1, cs ) );
+      const float y0 = __fsub_rn( __fmul_rn( x0, cs[k] ), __fmul_rn( x1, sn[k] ) );
+      const float y1 = __fadd_rn( __fmul_rn( x0, sn[k] ), __fmul_rn( x1, cs[k] ) );
       x0 = y0, x1 = y1;
     }
     const T o0 = Conv<T>::from_f32( x0 ), o1 = Conv<T>::from_f32( x1 );
@@ -328,8 +353,8 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
     T* dst = nullptr;
     if ( f < dim )
       dst = static_cast<T*>( a.q_out ) + (size_t)( a.batch0 + i ) * dim + f;
-    else if ( c.kv_off != kInactive )
-      dst = reinterpret_cast<T*>( a.arena + c.kv_off + a.layer_off ) + (size_t)c.pos * a.sh.row_elems + ( f - dim );
+    else if ( c[k].kv_off != kInactive )
+      dst = reinterpret_cast<T*>( a.arena + c[k].kv_off + a.layer_off ) + (size_t)c[k].pos * a.sh.row_elems + ( f - dim );
     if ( dst != nullptr )
       *reinterpret_cast<uint32_t*>( dst ) = bits;
   }
