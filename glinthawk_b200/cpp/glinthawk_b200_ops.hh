@@ -286,6 +286,27 @@ public:
     done();
   }
 
+  // Not a reference operation: Llama2::pre_attention_ops with the cache update followed by apply_rope
+  // (src/models/llama2/model.hh:326-360) as one call, for a model that wants the q / kv projections on the tcgen05
+  // path with K and V written straight into the contexts (no `kv` scratch).  fp16 / bf16, dim and kv_dim multiples of
+  // 128.
+  void pre_attention_rope_append( const uint64_t curr_batch_size,
+                                  const DType* x,
+                                  const DType* rms_att_weight,
+                                  const DType* wq,
+                                  const DType* wkv,
+                                  DType* state_q,
+                                  const uint32_t* token_positions,
+                                  const DType* freq_cis_real,
+                                  const DType* freq_cis_imag,
+                                  typename ContextType::TokenContextType token_contexts[] ) const
+  {
+    GH_B200_CHECK( h_, gh_op_project_append( h_, curr_batch_size, x, rms_att_weight, wq, wkv, state_q, token_positions,
+                                             freq_cis_real, freq_cis_imag, pointers( token_contexts, curr_batch_size, true ),
+                                             nullptr ) );
+    done();
+  }
+
   template<typename DTypeDst, typename DTypeSrc>
   void convert_and_copy( DTypeDst* dst, const DTypeSrc* src, const uint64_t size, const CopyType type ) const
   {

@@ -736,34 +736,29 @@ int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_n
   return ring_touch( h, h->cur, st );
 }
 
-int gh_attn_project_append( gh_attn_t h,
-                            uint32_t layer,
-                            const void* x,
-                            const void* rms_weight,
-                            const void* wq,
-                            const void* wkv,
-                            void* q_out,
-                            void* stream )
+// rmsnorm + projections + RoPE + append.  Destination rows either come from the current batch's slots (ctx != nullptr)
+// or are given as device pointers with their positions (token_rows / pos_dev, the reference's token contexts).
+static int project_common( gh_attn* h,
+                           uint32_t batch,
+                           const void* x,
+                           const void* rms_weight,
+                           const void* wq,
+                           const void* wkv,
+                           void* q_out,
+                           const void* rope_cos,
+                           const void* rope_sin,
+                           const CtxMeta* ctx,
+                           long long layer_off,
+                           void* const* token_rows,
+                           const uint32_t* pos_dev,
+                           cudaStream_t st )
 {
-  if ( h == nullptr || x == nullptr || rms_weight == nullptr || wq == nullptr || wkv == nullptr || q_out == nullptr )
-    return fail( h, GH_ERR_INVALID, "null argument" );
-  if ( !aligned16( x ) || !aligned16( rms_weight ) || !aligned16( wq ) || !aligned16( wkv ) || !aligned16( q_out ) )
-    return misaligned( h );
-  if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
-    return rc;
-  if ( h->rope_cos == nullptr )
-    return fail( h, GH_ERR_STATE, "RoPE tables not set" );
   if ( !h->use_mma || !project_supported( h->sh, h->cfg.dtype ) )
     return fail( h, GH_ERR_UNSUPPORTED,
                  "the fused projection needs fp16 or bf16 storage and dim, kv_dim that are multiples of 128" );
-  DeviceGuard guard( h->device );
-  const cudaStream_t st = static_cast<cudaStream_t>( stream );
   const DriverApi* api = driver_api( h->err );
   if ( api == nullptr )
     return GH_ERR_CUDA;
-  if ( const int rc = prepare_layer( h, layer ); rc != GH_OK )
-    return rc;
-
   const uint32_t dim = h->sh.n_heads * h->sh.head_size;
   ProjectArgs a {};
   uint32_t grid = 0;
@@ -777,7 +772,7 @@ int gh_attn_project_append( gh_attn_t h,
   }
 
   // rmsnorm for the whole batch (src/models/llama2/model.hh:331-335)
-  if ( const cudaError_t e = launch_rmsnorm( h->proj_xb, x, rms_weight, h->cur_batch, dim, h->cfg.dtype, st, &h->stats.kernel_launches );
+  if ( const cudaError_t e = launch_rmsnorm( h->proj_xb, x, rms_weight, batch, dim, h->cfg.dtype, st, &h->stats.kernel_launches );
        e != cudaSuccess )
     return cuda_fail( h, "rmsnorm launch", e );
 
@@ -802,26 +797,56 @@ int gh_attn_project_append( gh_attn_t h,
 
   a.sh = h->sh;
   a.dtype = h->cfg.dtype;
-  a.ctx = entry_ctx( h, h->ring[h->cur].dev );
+  a.ctx = ctx;
+  a.token_rows = token_rows;
+  a.pos = pos_dev;
   a.arena = h->pool.arena();
-  a.layer_off = h->pool.layer_offset( layer );
+  a.layer_off = layer_off;
   a.q_out = q_out;
-  a.rope_cos = h->rope_cos;
-  a.rope_sin = h->rope_sin;
+  a.rope_cos = rope_cos;
+  a.rope_sin = rope_sin;
   a.ws = h->proj_ws;
   a.dev_error = h->dev_error;
   // the MMA's N takes at most project_max_rows() batch rows: larger batches go in slices (the weights are then
   // streamed once per slice)
-  for ( uint32_t b0 = 0; b0 < h->cur_batch; b0 += project_max_rows() ) {
+  for ( uint32_t b0 = 0; b0 < batch; b0 += project_max_rows() ) {
     a.batch0 = b0;
-    a.batch = std::min( project_max_rows(), h->cur_batch - b0 );
+    a.batch = std::min( project_max_rows(), batch - b0 );
     a.nb = ( a.batch + 15 ) / 16 * 16;
-    if ( const int rc = encode( &xb_map, h->proj_xb, h->cur_batch, a.nb ); rc != GH_OK )
+    if ( const int rc = encode( &xb_map, h->proj_xb, batch, a.nb ); rc != GH_OK )
       return rc;
     if ( const cudaError_t e = launch_project( a, grid, &wq_map, &wkv_map, &xb_map, st, &h->stats.kernel_launches );
          e != cudaSuccess )
       return cuda_fail( h, "projection launch", e );
   }
+  return GH_OK;
+}
+
+int gh_attn_project_append( gh_attn_t h,
+                            uint32_t layer,
+                            const void* x,
+                            const void* rms_weight,
+                            const void* wq,
+                            const void* wkv,
+                            void* q_out,
+                            void* stream )
+{
+  if ( h == nullptr || x == nullptr || rms_weight == nullptr || wq == nullptr || wkv == nullptr || q_out == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( x ) || !aligned16( rms_weight ) || !aligned16( wq ) || !aligned16( wkv ) || !aligned16( q_out ) )
+    return misaligned( h );
+  if ( const int rc = check_batch_ready( h, layer ); rc != GH_OK )
+    return rc;
+  if ( h->rope_cos == nullptr )
+    return fail( h, GH_ERR_STATE, "RoPE tables not set" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  if ( const int rc = prepare_layer( h, layer ); rc != GH_OK )
+    return rc;
+  if ( const int rc = project_common( h, h->cur_batch, x, rms_weight, wq, wkv, q_out, h->rope_cos, h->rope_sin,
+                                      entry_ctx( h, h->ring[h->cur].dev ), h->pool.layer_offset( layer ), nullptr, nullptr, st );
+       rc != GH_OK )
+    return rc;
   return ring_touch( h, h->cur, st );
 }
 
@@ -1180,6 +1205,41 @@ int gh_op_apply_rope( gh_attn_t h,
   a.rope_sin = freq_cis_imag;
   if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
     return cuda_fail( h, "apply_rope launch", e );
+  return ring_touch( h, entry, st );
+}
+
+int gh_op_project_append( gh_attn_t h,
+                          uint64_t batch,
+                          const void* x,
+                          const void* rms_weight,
+                          const void* wq,
+                          const void* wkv,
+                          void* state_q,
+                          const uint32_t* pos,
+                          const void* freq_cis_real,
+                          const void* freq_cis_imag,
+                          void* const* token_rows,
+                          void* stream )
+{
+  if ( h == nullptr || x == nullptr || rms_weight == nullptr || wq == nullptr || wkv == nullptr || state_q == nullptr
+       || pos == nullptr || freq_cis_real == nullptr || freq_cis_imag == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( x ) || !aligned16( rms_weight ) || !aligned16( wq ) || !aligned16( wkv ) || !aligned16( state_q )
+       || ( batch <= h->cfg.max_batch && !rows_aligned16( token_rows, batch ) ) )
+    return misaligned( h );
+  for ( uint64_t i = 0; i < batch && i < h->cfg.max_batch; i++ )
+    if ( token_rows != nullptr && token_rows[i] != nullptr && pos[i] >= h->sh.seq_len )
+      return fail( h, GH_ERR_CAPACITY, "token position beyond the RoPE tables" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  int entry;
+  if ( const int rc = upload_ptrs( h, batch, const_cast<const void* const*>( token_rows ), pos, st, &entry ); rc != GH_OK )
+    return rc;
+  if ( const int rc = project_common( h, static_cast<uint32_t>( batch ), x, rms_weight, wq, wkv, state_q, freq_cis_real,
+                                      freq_cis_imag, nullptr, 0, entry_ptrs( h, h->ring[entry].dev ),
+                                      entry_pos( h, h->ring[entry].dev ), st );
+       rc != GH_OK )
+    return rc;
   return ring_touch( h, entry, st );
 }
 

@@ -86,7 +86,9 @@ struct ProjectArgs
   uint32_t batch0; // index of the first of them in the whole batch
   uint32_t nb;     // batch rounded up to a multiple of 16: the MMA's N
   uint32_t dim, n_tiles, q_tiles, kblocks, units_per_cta, max_segs; // set by project_plan()
-  const CtxMeta* ctx; // device, whole batch
+  const CtxMeta* ctx;      // device, whole batch; used when token_rows == nullptr
+  void* const* token_rows; // device array of destination row pointers (the reference's token contexts), or nullptr
+  const uint32_t* pos;     // device, [batch]; used together with token_rows
   char* arena;
   long long layer_off;
   void* q_out;          // [whole batch][dim]

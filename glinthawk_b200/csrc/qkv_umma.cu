@@ -304,14 +304,27 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
   const T* __restrict__ sin_t = static_cast<const T*>( a.rope_sin );
   // the partial sums come from the projection kernel, the kernel before this one in the stream
   asm volatile( "griddepcontrol.wait;" ::: "memory" );
-  // three rounds of independent loads (row records, partial sums, table values), each with all eight rows in flight
-  CtxMeta c[8];
+  // three rounds of independent loads (positions and row pointers, partial sums, table values), each with all eight
+  // rows in flight
+  uint32_t pos[8];
+  T* row[8]; // the prompt's slot row at its position; nullptr = inactive prompt
   float2 acc[8];
 #pragma unroll
   for ( int k = 0; k < 8; k++ ) {
     const int i = blockIdx.y * 32 + sub + 4 * k;
-    if ( i < batch )
-      c[k] = a.ctx[a.batch0 + i];
+    pos[k] = 0;
+    row[k] = nullptr;
+    if ( i < batch ) {
+      if ( a.token_rows != nullptr ) {
+        pos[k] = a.pos[a.batch0 + i];
+        row[k] = static_cast<T*>( a.token_rows[a.batch0 + i] );
+      } else {
+        const CtxMeta c = a.ctx[a.batch0 + i];
+        pos[k] = c.pos;
+        if ( c.kv_off != kInactive )
+          row[k] = reinterpret_cast<T*>( a.arena + c.kv_off + a.layer_off ) + (size_t)c.pos * a.sh.row_elems;
+      }
+    }
     acc[k] = make_float2( 0.f, 0.f );
   }
   for ( int s = 0; s < nsegs; s++ ) { // fixed order: the same bits on every run
@@ -331,7 +344,7 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
   for ( int k = 0; k < 8; k++ ) {
     const int i = blockIdx.y * 32 + sub + 4 * k;
     if ( rotate && i < batch ) {
-      const size_t ti = (size_t)c[k].pos * ( hs / 2 ) + d2;
+      const size_t ti = (size_t)pos[k] * ( hs / 2 ) + d2;
       cs[k] = Conv<T>::to_f32( __ldg( cos_t + ti ) );
       sn[k] = Conv<T>::to_f32( __ldg( sin_t + ti ) );
     }
@@ -353,8 +366,8 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
     T* dst = nullptr;
     if ( f < dim )
       dst = static_cast<T*>( a.q_out ) + (size_t)( a.batch0 + i ) * dim + f;
-    else if ( c[k].kv_off != kInactive )
-      dst = reinterpret_cast<T*>( a.arena + c[k].kv_off + a.layer_off ) + (size_t)c[k].pos * a.sh.row_elems + ( f - dim );
+    else if ( row[k] != nullptr )
+      dst = row[k] + ( f - dim );
     if ( dst != nullptr )
       *reinterpret_cast<uint32_t*>( dst ) = bits;
   }

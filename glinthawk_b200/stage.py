@@ -209,6 +209,15 @@ class AttentionStage:
         self._ck(lib.gh_op_apply_rope(self._h, batch_size, _ptr(pos), _ptr(freq_cis_real), _ptr(freq_cis_imag),
                                       _ptr(state_q), _ptr(rows), _stream(stream)))
 
+    def pre_attention_rope_append(self, batch_size: int, x, rms_att_weight, wq, wkv, state_q, token_positions,
+                                  freq_cis_real, freq_cis_imag, token_contexts, stream=None) -> None:
+        """pre_attention_ops (with the cache update) + apply_rope of the reference in one call, on tcgen05."""
+        rows = self._ptr_array(token_contexts)
+        pos = np.ascontiguousarray(token_positions, dtype=np.uint32)
+        self._ck(lib.gh_op_project_append(self._h, batch_size, _ptr(x), _ptr(rms_att_weight), _ptr(wq), _ptr(wkv),
+                                          _ptr(state_q), _ptr(pos), _ptr(freq_cis_real), _ptr(freq_cis_imag), _ptr(rows),
+                                          _stream(stream)))
+
     def attention_0_gemm(self, query, layer_contexts, att, batch_size: int, token_positions, stream=None) -> None:
         bases = self._ptr_array(layer_contexts)
         pos = np.ascontiguousarray(token_positions, dtype=np.uint32)

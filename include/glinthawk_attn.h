@@ -285,6 +285,23 @@ int gh_op_convert_and_copy( gh_attn_t h,
                             uint64_t n,
                             uint32_t copy_type );
 
+/* Llama2::pre_attention_ops with the cache update, followed by apply_rope, argument for argument
+ * (src/models/llama2/model.hh:326-360): the same fused producer as gh_attn_project_append, with the destination rows
+ * given the way copy_kv_cache and apply_rope receive them (`token_rows`, null = inactive prompt; `pos`; the RoPE
+ * tables).  state_q receives the rotated queries. */
+int gh_op_project_append( gh_attn_t h,
+                          uint64_t batch,
+                          const void* x,
+                          const void* rms_weight,
+                          const void* wq,
+                          const void* wkv,
+                          void* state_q,
+                          const uint32_t* pos,
+                          const void* freq_cis_real,
+                          const void* freq_cis_imag,
+                          void* const* token_rows,
+                          void* stream );
+
 /* ---- helpers for benchmarks and tests ------------------------------------------------------------- */
 
 /* Fills n elements of `dtype` at device pointer `dst` with N(0,1) values from a counter-based generator

@@ -137,6 +137,28 @@ def test_projection_then_decode_equals_the_reference_layer_step(oracle):
     st.close()
 
 
+def test_the_operation_level_entry_point_takes_the_reference_arguments(oracle):
+    """gh_op_project_append: destination rows as device pointers (what copy_kv_cache and apply_rope receive), a null
+    pointer for an inactive prompt, the RoPE tables as arguments."""
+    case = cases.make_proj_case("projop", "mini_g8", cases.F16, [0, 3, 77, 511, 200], seed=91)
+    want = oracle.pre_attention(case)
+    sh, B, dt = case.shape, case.B, case.dtype
+    st = AttentionStage(sh, torch.float16, n_layers_hosted=1, max_batch=B, max_contexts=B)
+    rows_d = torch.full((B, 2 * sh.kv_dim), float("nan"), device="cuda", dtype=torch.float16)
+    ptrs = [rows_d[i].data_ptr() for i in range(B)]
+    ptrs[2] = 0  # inactive
+    q_out = torch.zeros((B, sh.dim), device="cuda", dtype=torch.float16)
+    st.pre_attention_rope_append(B, gpu_util.to_dev(case.x, dt), gpu_util.to_dev(case.rms_w, dt), gpu_util.to_dev(case.wq, dt),
+                                 gpu_util.to_dev(case.wkv, dt), q_out, case.pos, gpu_util.to_dev(case.fcr, dt),
+                                 gpu_util.to_dev(case.fci, dt), ptrs)
+    torch.cuda.synchronize()
+    assert st.stats().device_error == 0
+    got = gpu_util.to_host(rows_d, dt)
+    assert np.isnan(got[2].astype(np.float32)).all(), "the inactive prompt's row is not touched"
+    _check(case, want, gpu_util.to_host(q_out, dt), [got[i] if i != 2 else None for i in range(B)])
+    st.close()
+
+
 def test_unsupported_shapes_are_refused():
     sh = SHAPES["tiny15m"]  # fp32, dim 288
     st = AttentionStage(sh, torch.float32, n_layers_hosted=1, max_batch=2, max_contexts=2)
