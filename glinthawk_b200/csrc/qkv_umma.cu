@@ -280,17 +280,19 @@ __global__ void __launch_bounds__( kThreads, 1 )
   }
 }
 
-// Second step of the projection: one block = (tile of 128 features, 32 batch rows); a thread owns one (even, odd)
-// feature pair and walks 8 of the rows.  It adds the tile's pieces in their fixed order (deterministic), rounds to the
+constexpr int kFinishRows = 16; // batch rows per block of the finishing kernel
+
+// Second step of the projection: one block = (tile of 128 features, 16 batch rows); a thread owns one (even, odd)
+// feature pair and walks 4 of the rows.  It adds the tile's pieces in their fixed order (deterministic), rounds to the
 // storage type (the reference stores q and kv there), rotates q and K pairs by the row's position with separately
 // rounded products (src/arch/amd64/llama2/ops.hh:150-162) and writes q, or K/V straight into the slot row.
 template<typename T>
-__global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArgs a )
+__global__ void __launch_bounds__( 256, 4 ) project_finish_kernel( const ProjectArgs a )
 {
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
   const int tile = blockIdx.x;
   const int pair = threadIdx.x & 63; // features 2 * pair, 2 * pair + 1 of the tile
-  const int sub = threadIdx.x >> 6;  // rows sub, sub + 4, ... of the block's 32
+  const int sub = threadIdx.x >> 6;  // rows sub, sub + 4, ... of the block's kFinishRows
   const int hs = a.sh.head_size;
   const int dim = a.dim, kv_dim = a.sh.kv_dim, batch = a.batch;
   const int f = tile * kTileF + 2 * pair;
@@ -304,14 +306,14 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
   const T* __restrict__ sin_t = static_cast<const T*>( a.rope_sin );
   // the partial sums come from the projection kernel, the kernel before this one in the stream
   asm volatile( "griddepcontrol.wait;" ::: "memory" );
-  // three rounds of independent loads (positions and row pointers, partial sums, table values), each with all eight
-  // rows in flight
-  uint32_t pos[8];
-  T* row[8]; // the prompt's slot row at its position; nullptr = inactive prompt
-  float2 acc[8];
+  // three rounds of independent loads (positions and row pointers, partial sums, table values), each with all of the
+  // thread's rows in flight
+  uint32_t pos[kFinishRows / 4];
+  T* row[kFinishRows / 4]; // the prompt's slot row at its position; nullptr = inactive prompt
+  float2 acc[kFinishRows / 4];
 #pragma unroll
-  for ( int k = 0; k < 8; k++ ) {
-    const int i = blockIdx.y * 32 + sub + 4 * k;
+  for ( int k = 0; k < kFinishRows / 4; k++ ) {
+    const int i = blockIdx.y * kFinishRows + sub + 4 * k;
     pos[k] = 0;
     row[k] = nullptr;
     if ( i < batch ) {
@@ -329,8 +331,8 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
   }
   for ( int s = 0; s < nsegs; s++ ) { // fixed order: the same bits on every run
 #pragma unroll
-    for ( int k = 0; k < 8; k++ ) {
-      const int i = blockIdx.y * 32 + sub + 4 * k;
+    for ( int k = 0; k < kFinishRows / 4; k++ ) {
+      const int i = blockIdx.y * kFinishRows + sub + 4 * k;
       if ( i < batch ) {
         const float2 part
           = __ldcg( reinterpret_cast<const float2*>( tile_ws + (size_t)s * slot_floats + (size_t)i * kTileF + 2 * pair ) );
@@ -339,10 +341,10 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
       }
     }
   }
-  float cs[8], sn[8];
+  float cs[kFinishRows / 4], sn[kFinishRows / 4];
 #pragma unroll
-  for ( int k = 0; k < 8; k++ ) {
-    const int i = blockIdx.y * 32 + sub + 4 * k;
+  for ( int k = 0; k < kFinishRows / 4; k++ ) {
+    const int i = blockIdx.y * kFinishRows + sub + 4 * k;
     if ( rotate && i < batch ) {
       const size_t ti = (size_t)pos[k] * ( hs / 2 ) + d2;
       cs[k] = Conv<T>::to_f32( __ldg( cos_t + ti ) );
@@ -350,8 +352,8 @@ __global__ void __launch_bounds__( 256 ) project_finish_kernel( const ProjectArg
     }
   }
 #pragma unroll
-  for ( int k = 0; k < 8; k++ ) {
-    const int i = blockIdx.y * 32 + sub + 4 * k;
+  for ( int k = 0; k < kFinishRows / 4; k++ ) {
+    const int i = blockIdx.y * kFinishRows + sub + 4 * k;
     if ( i >= batch )
       continue;
     float x0 = Conv<T>::to_f32( Conv<T>::from_f32( acc[k].x ) ), x1 = Conv<T>::to_f32( Conv<T>::from_f32( acc[k].y ) );
@@ -468,7 +470,7 @@ cudaError_t launch_project( const ProjectArgs& a, uint32_t grid, const CUtensorM
   ( *launches )++;
   if ( e != cudaSuccess )
     return e;
-  cfg.gridDim = dim3( a.n_tiles, ( a.batch + 31 ) / 32 );
+  cfg.gridDim = dim3( a.n_tiles, ( a.batch + kFinishRows - 1 ) / kFinishRows );
   cfg.blockDim = dim3( 256 );
   cfg.dynamicSmemBytes = 0;
   if ( a.dtype == DT_F16 )
