@@ -262,7 +262,13 @@ def main():
     row_elems = 2 * sh.kv_dim
     if n_pf:  # prompt chunks go into slots of their own, rewritten from position 0 every step
         pf_slots = stage.get_contexts(np.arange(batch + 1, batch + n_pf + 1, dtype=np.uint32))
-        pf_pos0 = np.zeros(n_pf, dtype=np.uint32)
+        pf_pos0 = np.full(n_pf, wl.prefill_pos0, dtype=np.uint32)
+        if wl.prefill_pos0:  # the part of the prompt that earlier chunks cached
+            for i in range(n_pf):
+                for l in range(n_layers):
+                    stage.prepare(int(pf_slots[i]), l, wl.prefill_pos0 - 1)
+                    stage.fill_normal(stage.layer_ptr(int(pf_slots[i]), l), wl.prefill_pos0 * row_elems, tdt, args.seed + 13,
+                                      offset=(i * n_layers + l) * sh.seq_len * row_elems)
         pf_q = torch.empty((n_layers, n_pf, t_pf, sh.dim), dtype=tdt, device=dev)
         pf_kv = torch.empty((n_layers, n_pf, t_pf, row_elems), dtype=tdt, device=dev)
         pf_xb = torch.zeros_like(pf_q)
@@ -306,7 +312,7 @@ def main():
     st_ptr = C.c_void_p(stream.cuda_stream)
     handle = stage._h
 
-    producer_events = []
+    producer_events, prefill_events = [], []
 
     def device_step(record=None):
         """One token for every context through all layers.  With `record`, every 8th layer's decode launch is
@@ -339,7 +345,13 @@ def main():
             elif ghlib.gh_attn_step(handle, l, q_ptr[l], kv_ptr[l], xb_ptr[l], st_ptr) != 0:
                 raise RuntimeError(ghlib.gh_attn_last_error(handle).decode())
             if n_pf:
+                if record is not None:
+                    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    f0.record(stream)
                 stage.prefill_chunk(l, pf_slots, pf_pos0, t_pf, pf_q[l], pf_kv[l], pf_xb[l])
+                if record is not None:
+                    f1.record(stream)
+                    prefill_events.append((f0, f1))
         pos[:] += 1
 
     def barrier():
@@ -358,6 +370,7 @@ def main():
         pass
     launches0 = stage.stats().kernel_launches
     producer_events.clear()
+    prefill_events.clear()
     decode_events, kv_tokens = [], []
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(uuid) as clocks:
@@ -427,6 +440,19 @@ def main():
     stats = stage.stats()
     if stats.device_error:
         raise SystemExit(f"device error flag {stats.device_error}")
+    prefill = None
+    if n_pf:
+        fms = [a.elapsed_time(b) for a, b in prefill_events]
+        fms_mean = sum(fms) / len(fms)
+        # causal attention of the chunk: every token against the cached prefix and the chunk's tokens up to itself
+        keys = n_pf * (t_pf * wl.prefill_pos0 + t_pf * (t_pf + 1) / 2)
+        flops = 4.0 * keys * sh.n_heads * sh.head_size
+        chunk_bytes = n_pf * t_pf * (2 * row_elems + 2 * sh.dim) * elem  # append: K/V rows and q, read and written
+        prefill = {"kernels": "append_chunk_kernel + " + ("decode_mma_kernel in chunk mode"
+                                                             if os.environ.get("GLINTHAWK_PREFILL") == "mma"
+                                                             else "prefill_umma_kernel (tcgen05)"),
+                   "ms_per_chunk_call": fms_mean, "prompt_tokens_per_call": n_pf * t_pf,
+                   "causal_attention_tflops": flops / (fms_mean / 1e3) / 1e12, "append_bytes": chunk_bytes}
     producer = None
     if args.producer:
         pms = [a.elapsed_time(b) for a, b in producer_events]
@@ -468,7 +494,7 @@ def main():
             "clocks": clocks.summary(),
             "e2e": e2e,
             "gpu_launches": int(launches),
-            "cpu_baseline": cpu, "producer": producer,
+            "cpu_baseline": cpu, "producer": producer, "prefill": prefill,
             "setup_s": t_setup,
         }
         print(json.dumps(out))

@@ -26,6 +26,7 @@ class Workload:
     description: str
     prefill_contexts: int = 0   # additional contexts that append a prompt chunk into a fresh slot every step
     prefill_tokens: int = 0     # tokens per prompt chunk
+    prefill_pos0: int = 0       # tokens those slots already hold when the chunk arrives (0 = fresh slots)
 
     def lengths(self, seed: int, headroom: int = 0) -> np.ndarray:
         """Cached tokens per context before the first step; every context keeps `headroom` free positions."""
@@ -56,6 +57,10 @@ WORKLOADS = {w.name: w for w in [
              "Llama3-8B GQA mixed prefill + decode, one layer, bf16, 32 q / 8 kv heads, head 128, slots of 8192: "
              "448 contexts decode one token each (lengths uniform 256..8192), 64 contexts append a 512-token prompt "
              "chunk into fresh slots", prefill_contexts=64, prefill_tokens=512),
+    Workload("llama3_8b_late_chunk", SHAPES["l3_8b_8k"], "bf16", 1, 64, "uniform_256_8191",
+             "Llama3-8B GQA, one layer, bf16: 32 contexts append the last 512-token chunk of a 4096-token prompt "
+             "(3584 tokens already cached) next to 64 contexts decoding one token each (lengths uniform 256..8192)",
+             prefill_contexts=32, prefill_tokens=512, prefill_pos0=3584),
 ]}
 
 
