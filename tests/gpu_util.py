@@ -4,7 +4,8 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from glinthawk_b200.stage import AttentionStage
+from glinthawk_b200._lib import GH_ERR_CAPACITY  # noqa: F401  (re-exported for the tests)
+from glinthawk_b200.stage import AttentionStage, GlinthawkAttnError  # noqa: F401
 from tests import cases
 
 TORCH_DT = {cases.F16: torch.float16, cases.F32: torch.float32, cases.BF16: torch.bfloat16}
@@ -172,3 +173,43 @@ def check_prefill(oracle, shape_name, dtype, pos0, chunk_lens, k_ramp=0.0, seed=
     kernel = st.stats().last_kernel
     st.close()
     return kernel
+
+
+# One rounding of a sum of magnitude ~1 to the storage type may flip in the last place (the GPU adds the products in
+# another order than the reference's serial loop): 2^-10 relative for fp16, 2^-7 for bf16; the rotation then mixes
+# two such values.
+PROJ_RTOL = {cases.F16: 1e-3, cases.BF16: 8e-3}
+PROJ_ATOL = {cases.F16: 4e-3, cases.BF16: 3e-2}
+
+
+def run_project(case: cases.ProjCase, inactive=()):
+    """project_append on fresh slots; returns q_out, the appended rows (None where inactive) and the stage."""
+    sh, B, dt = case.shape, case.B, case.dtype
+    tdt = TORCH_DT[dt]
+    st = AttentionStage(sh, tdt, n_layers_hosted=2, max_batch=B, max_contexts=B, paged=True)
+    st.set_rope_tables(to_dev(case.fcr, dt), to_dev(case.fci, dt))
+    slots = st.get_contexts(np.arange(1, B + 1, dtype=np.uint32)).astype(np.int32)
+    slots[list(inactive)] = -1
+    st.batch_begin(slots, case.pos)
+    q_out = torch.full((B, sh.dim), float("nan"), device="cuda", dtype=tdt)
+    st.project_append(1, to_dev(case.x, dt), to_dev(case.rms_w, dt), to_dev(case.wq, dt),
+                      to_dev(case.wkv, dt), q_out)
+    torch.cuda.synchronize()
+    assert st.stats().device_error == 0
+    rows = []
+    for i in range(B):
+        if slots[i] < 0:
+            rows.append(None)
+            continue
+        p = int(case.pos[i])
+        rows.append(to_host(st.layer_view(int(slots[i]), 1, p + 1), dt)[p])
+    return to_host(q_out, dt), rows, st, slots
+
+
+def check_project(case, want, q_out, rows):
+    dt = case.dtype
+    np.testing.assert_allclose(cases.as_f32(q_out, dt), cases.as_f32(want.q_rot, dt), rtol=PROJ_RTOL[dt], atol=PROJ_ATOL[dt])
+    for i, row in enumerate(rows):
+        if row is not None:
+            np.testing.assert_allclose(cases.as_f32(row, dt), cases.as_f32(want.rows[i], dt), rtol=PROJ_RTOL[dt], atol=PROJ_ATOL[dt],
+                                       err_msg=f"slot row of prompt {i}")

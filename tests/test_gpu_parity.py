@@ -255,6 +255,48 @@ def test_prefill_with_scores_that_keep_growing_along_the_keys(oracle, shape_name
     gpu_util.check_prefill(oracle, shape_name, dtype, pos0=[0, 150], chunk_lens=[200], k_ramp=0.125, seed=5, exact_attention=True)
 
 
+def test_prefill_skips_inactive_contexts_and_refuses_chunks_past_the_slot(oracle):
+    """Slot -1 = inactive prompt: nothing of it is appended or written, the others are unaffected.  A chunk that would
+    run past the slot capacity is refused before anything is launched."""
+    shape_name, dtype, T = "mini_g4", cases.F16, 40
+    sh = cases.SHAPES[shape_name]
+    pos0 = [0, 30, 11]
+    base = cases.make_case("pfi", shape_name, dtype, [p + T - 1 for p in pos0], seed=21)
+    rng = np.random.default_rng(8)
+    q = cases.store(rng.standard_normal((3, T, sh.dim), dtype=np.float32), dtype)
+    kv = cases.store(rng.standard_normal((3, T, 2 * sh.kv_dim), dtype=np.float32), dtype)
+    st = gpu_util.make_stage(base, layers=1, paged=True)
+    slots = st.get_contexts(np.arange(1, 4, dtype=np.uint32)).astype(np.int32)
+    for i, p in enumerate(pos0):
+        st.prepare(int(slots[i]), 0, max(p, 1) - 1, False)
+        if p > 0:
+            st.layer_view(int(slots[i]), 0, p).copy_(gpu_util.to_dev(base.cache[i][:p], dtype))
+    q_d, kv_d = gpu_util.to_dev(q, dtype), gpu_util.to_dev(kv, dtype)
+    xb_all, xb_two = torch.zeros_like(q_d), torch.full_like(q_d, 7.0)
+    st.prefill_chunk(0, slots, pos0, T, q_d.clone(), kv_d, xb_all)      # everybody
+    with_middle = gpu_util.to_host(xb_all, dtype)
+    mapped = st.stats().bytes_mapped
+    for i, p in enumerate(pos0):  # start again from the same prefixes
+        st.layer_view(int(slots[i]), 0, p + T)[p:].zero_()
+    masked = slots.copy()
+    masked[1] = -1
+    q_in = q_d.clone()
+    st.prefill_chunk(0, masked, pos0, T, q_in, kv_d, xb_two)            # the middle one inactive
+    torch.cuda.synchronize()
+    got = gpu_util.to_host(xb_two, dtype)
+    assert np.array_equal(got[0], with_middle[0]) and np.array_equal(got[2], with_middle[2])
+    assert (got[1].astype(np.float32) == 7.0).all(), "xb of the inactive prompt is not written"
+    assert torch.equal(q_in[1], q_d[1]), "q of the inactive prompt is not rotated"
+    assert not st.layer_view(int(slots[1]), 0, pos0[1] + T)[pos0[1]:].any(), "nothing is appended for it"
+    assert st.stats().bytes_mapped == mapped
+    launches = st.stats().kernel_launches
+    with pytest.raises(gpu_util.GlinthawkAttnError) as e:
+        st.prefill_chunk(0, slots, [0, sh.seq_len - T + 1, 0], T, q_d, kv_d, xb_all)
+    assert e.value.status == gpu_util.GH_ERR_CAPACITY and st.stats().kernel_launches == launches
+    assert st.stats().device_error == 0
+    st.close()
+
+
 @pytest.mark.parametrize("force_generic", [False, True])
 def test_garbage_beyond_the_current_position_is_never_read_into_the_result(oracle, force_generic):
     """A slot keeps whatever its previous owner left behind the current position (the reference never clears

@@ -11,44 +11,7 @@ from tests import cases, gpu_util
 
 pytestmark = pytest.mark.gpu
 
-# One rounding of a sum of magnitude ~1 to the storage type may flip in the last place (the GPU adds the products in
-# another order than the reference's serial loop): 2^-10 relative for fp16, 2^-7 for bf16; the rotation then mixes
-# two such values.
-RTOL = {cases.F16: 1e-3, cases.BF16: 8e-3}
-ATOL = {cases.F16: 4e-3, cases.BF16: 3e-2}
-
-
-def _run(case: cases.ProjCase, inactive=()):
-    """project_append on fresh slots; returns q_out, the appended rows (None where inactive) and the stage."""
-    sh, B, dt = case.shape, case.B, case.dtype
-    tdt = gpu_util.TORCH_DT[dt]
-    st = AttentionStage(sh, tdt, n_layers_hosted=2, max_batch=B, max_contexts=B, paged=True)
-    st.set_rope_tables(gpu_util.to_dev(case.fcr, dt), gpu_util.to_dev(case.fci, dt))
-    slots = st.get_contexts(np.arange(1, B + 1, dtype=np.uint32)).astype(np.int32)
-    slots[list(inactive)] = -1
-    st.batch_begin(slots, case.pos)
-    q_out = torch.full((B, sh.dim), float("nan"), device="cuda", dtype=tdt)
-    st.project_append(1, gpu_util.to_dev(case.x, dt), gpu_util.to_dev(case.rms_w, dt), gpu_util.to_dev(case.wq, dt),
-                      gpu_util.to_dev(case.wkv, dt), q_out)
-    torch.cuda.synchronize()
-    assert st.stats().device_error == 0
-    rows = []
-    for i in range(B):
-        if slots[i] < 0:
-            rows.append(None)
-            continue
-        p = int(case.pos[i])
-        rows.append(gpu_util.to_host(st.layer_view(int(slots[i]), 1, p + 1), dt)[p])
-    return gpu_util.to_host(q_out, dt), rows, st, slots
-
-
-def _check(case, want, q_out, rows):
-    dt = case.dtype
-    np.testing.assert_allclose(cases.as_f32(q_out, dt), cases.as_f32(want.q_rot, dt), rtol=RTOL[dt], atol=ATOL[dt])
-    for i, row in enumerate(rows):
-        if row is not None:
-            np.testing.assert_allclose(cases.as_f32(row, dt), cases.as_f32(want.rows[i], dt), rtol=RTOL[dt], atol=ATOL[dt],
-                                       err_msg=f"slot row of prompt {i}")
+_run, _check = gpu_util.run_project, gpu_util.check_project
 
 
 @pytest.mark.parametrize("shape_name,dtype,n", [("mini_mha", cases.F16, 5), ("mini_g4", cases.F16, 7), ("mini_g4", cases.BF16, 33),
@@ -72,9 +35,9 @@ def test_projection_fixture_from_the_reference(oracle):
         gold = np.load(Path(__file__).resolve().parent / "golden" / f"{case.name}.npz")
         q_out, rows, st, _ = _run(case)
         np.testing.assert_allclose(cases.as_f32(q_out, case.dtype), cases.as_f32(gold["q_rot"], case.dtype),
-                                   rtol=RTOL[case.dtype], atol=ATOL[case.dtype])
+                                   rtol=gpu_util.PROJ_RTOL[case.dtype], atol=gpu_util.PROJ_ATOL[case.dtype])
         np.testing.assert_allclose(cases.as_f32(np.stack(rows), case.dtype), cases.as_f32(gold["rows"], case.dtype),
-                                   rtol=RTOL[case.dtype], atol=ATOL[case.dtype])
+                                   rtol=gpu_util.PROJ_RTOL[case.dtype], atol=gpu_util.PROJ_ATOL[case.dtype])
         st.close()
 
 
