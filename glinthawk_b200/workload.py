@@ -47,6 +47,9 @@ WORKLOADS = {w.name: w for w in [
     Workload("llama2_70b_gqa", SHAPES["l70b_4k"], "f16", 80, 256, "lognormal_1024_0.8",
              "Llama2-70B GQA attention stage, 80 layers, fp16, 64 q / 8 kv heads, head 128, slots of 4096, "
              "256 contexts, lengths lognormal(median 1024, sigma 0.8) clipped to 16..4096"),
+    Workload("llama2_70b_long", SHAPES["l70b_4k"], "f16", 4, 256, "uniform_2048_4095",
+             "Llama2-70B GQA attention stage, 4 layers, fp16, 256 contexts, lengths uniform 2048..4096 (the same kernel "
+             "without the short contexts of the lognormal mix)"),
     Workload("llama2_7b_layer", SHAPES["l7b_4k"], "f16", 1, 64, "uniform_128_4095",
              "Llama2-7B attention layer, fp16, 32 heads (MHA), head 128, 64 contexts, lengths uniform 128..4096"),
     Workload("llama2_13b", SHAPES["l13b_4k"], "f16", 40, 128, "uniform_512_4095",
