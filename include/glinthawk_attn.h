@@ -189,7 +189,9 @@ int gh_attn_step( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_new
  * not exist: K and V go from the tensor cores' accumulators into the slots.  Values are rounded to the storage type
  * where the reference rounds them (xb, q, kv before the rotation, and after it).
  * fp16 / bf16 with dim and kv_dim multiples of 128 only (GH_ERR_UNSUPPORTED otherwise).  The first call allocates
- * scratch (batch x dim activations and a few tens of MB of partial sums). */
+ * scratch (batch x dim activations and a few tens of MB of partial sums), which every later call of the handle
+ * reuses: calls on different streams must not overlap (decode launches may, they have scratch sets of their own).
+ * Batches of more than 256 prompts are processed in slices of 256, each streaming the weights once. */
 int gh_attn_project_append( gh_attn_t h,
                             uint32_t layer,
                             const void* x,
