@@ -64,6 +64,7 @@ _PROTOS = {
     "gh_attn_step": (C.c_int, [_P, _U32, _P, _P, _P, _P]),
     "gh_attn_prefill_chunk": (C.c_int, [_P, _U32, _U64, _P, _P, _U32, _P, _P, _P, _P]),
     "gh_attn_project_append": (C.c_int, [_P, _U32, _P, _P, _P, _P, _P, _P]),
+    "gh_plan_projection": (C.c_int, [_U32, _U32, _U32, _U32, _P, _P, _U32, _P]),
     "gh_op_project_append": (C.c_int, [_P, _U64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "gh_attn_forward_attention_host": (C.c_int, [_P, _U32, _U32, _P, _P, _P, _P]),
     "gh_op_copy_kv_cache": (C.c_int, [_P, _P, _P, _U64, _P]),

@@ -1449,6 +1449,41 @@ int gh_plan_batch( uint32_t blocks_per_item,
   return GH_OK;
 }
 
+int gh_plan_projection( uint32_t n_heads,
+                        uint32_t head_size,
+                        uint32_t kv_dim,
+                        uint32_t sm_count,
+                        uint32_t* plan_out,
+                        int32_t* pieces_out,
+                        uint32_t max_pieces,
+                        uint32_t* n_pieces )
+{
+  if ( plan_out == nullptr || pieces_out == nullptr || n_pieces == nullptr || n_heads == 0 || head_size == 0 || sm_count == 0 )
+    return GH_ERR_INVALID;
+  Shape sh {};
+  sh.n_heads = n_heads;
+  sh.head_size = head_size;
+  sh.kv_dim = kv_dim;
+  if ( !project_supported( sh, DT_F16 ) )
+    return GH_ERR_UNSUPPORTED;
+  ProjectArgs a {};
+  uint32_t grid = 0;
+  project_plan( sh, sm_count, &a, &grid );
+  plan_out[0] = grid, plan_out[1] = a.units_per_cta, plan_out[2] = a.max_segs, plan_out[3] = a.n_tiles, plan_out[4] = a.kblocks;
+  uint32_t n = 0;
+  std::vector<int32_t> tmp( 5 * ( a.n_tiles + 2 ) ); // a CTA touches every tile at most once
+  for ( uint32_t c = 0; c < grid; c++ ) {
+    const uint32_t k = project_pieces( a, c, tmp.data(), a.n_tiles + 2 );
+    for ( uint32_t i = 0; i < k; i++, n++ )
+      if ( n < max_pieces ) {
+        pieces_out[6 * n] = static_cast<int32_t>( c );
+        std::memcpy( pieces_out + 6 * n + 1, tmp.data() + 5 * i, 5 * sizeof( int32_t ) );
+      }
+  }
+  *n_pieces = n;
+  return n <= max_pieces ? GH_OK : GH_ERR_CAPACITY;
+}
+
 int gh_fill_normal( gh_attn_t h, void* dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t offset, void* stream )
 {
   if ( h == nullptr || dst == nullptr || !dtype_ok( dtype ) )

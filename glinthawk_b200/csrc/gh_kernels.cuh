@@ -102,6 +102,8 @@ uint32_t project_max_rows();
 cudaError_t project_prepare();
 void project_plan( const Shape& sh, uint32_t sm_count, ProjectArgs* a, uint32_t* grid );
 size_t project_workspace_bytes( const ProjectArgs& a );
+// host copy of the walk every role of CTA `cta` does: records {tile, k0, k1, piece index, pieces of the tile}
+uint32_t project_pieces( const ProjectArgs& a, uint32_t cta, int32_t* out, uint32_t cap );
 cudaError_t launch_rmsnorm( void* out, const void* x, const void* weight, uint32_t rows, uint32_t dim, uint32_t dtype,
                             cudaStream_t st, uint64_t* launches );
 // wq_map / wkv_map: the weight matrices as [rows][dim] with box [128][64]; xb_map: the normalised activations as

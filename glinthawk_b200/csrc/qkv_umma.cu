@@ -107,12 +107,12 @@ struct Piece
   int seg, nsegs;   // index of this piece among the tile's pieces, and how many there are
 };
 
-__device__ __forceinline__ Piece piece_at( int u, int u_end, int kblocks, int upc )
+__host__ __device__ __forceinline__ Piece piece_at( int u, int u_end, int kblocks, int upc )
 {
   Piece p;
   p.tile = u / kblocks;
   p.k0 = u - p.tile * kblocks;
-  p.k1 = min( kblocks, p.k0 + ( u_end - u ) );
+  p.k1 = p.k0 + ( u_end - u ) < kblocks ? p.k0 + ( u_end - u ) : kblocks;
   const int first = p.tile * kblocks, last = first + kblocks - 1; // the tile's units; cuts fall on multiples of upc
   p.seg = u / upc - first / upc;
   p.nsegs = last / upc - first / upc + 1;
@@ -410,6 +410,23 @@ void project_plan( const Shape& sh, uint32_t sm_count, ProjectArgs* a, uint32_t*
   a->units_per_cta = ( units + ctas - 1 ) / ctas;
   *grid = ( units + a->units_per_cta - 1 ) / a->units_per_cta;
   a->max_segs = ( a->kblocks + a->units_per_cta - 1 ) / a->units_per_cta + 1;
+}
+
+uint32_t project_pieces( const ProjectArgs& a, uint32_t cta, int32_t* out, uint32_t cap )
+{
+  const int upc = a.units_per_cta, kblocks = a.kblocks;
+  const int u_begin = cta * upc, u_end = std::min<int>( a.n_tiles * a.kblocks, u_begin + upc );
+  uint32_t n = 0;
+  for ( int u = u_begin; u < u_end; ) {
+    const Piece p = piece_at( u, u_end, kblocks, upc );
+    if ( n < cap ) {
+      int32_t* rec = out + 5 * n;
+      rec[0] = p.tile, rec[1] = p.k0, rec[2] = p.k1, rec[3] = p.seg, rec[4] = p.nsegs;
+    }
+    n++;
+    u += p.k1 - p.k0;
+  }
+  return n;
 }
 
 size_t project_workspace_bytes( const ProjectArgs& a )

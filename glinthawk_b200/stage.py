@@ -263,6 +263,20 @@ def plan_batch(pos, *, blocks_per_item: int, sm_count: int = 148, tile: int = 64
     return items[: n.value].copy(), chunk.value
 
 
+def plan_projection(shape: AttnShape, *, sm_count: int = 148, max_pieces: int = 8192):
+    """Host-only view of how the fused projection deals (feature tile, k-block) units to the SMs: returns
+    (plan dict, pieces[n, 6] = {cta, tile, k0, k1, piece index, pieces of the tile})."""
+    plan = np.zeros(5, dtype=np.uint32)
+    pieces = np.zeros((max_pieces, 6), dtype=np.int32)
+    n = C.c_uint32(0)
+    rc = lib.gh_plan_projection(shape.n_heads, shape.head_size, shape.kv_dim, sm_count, _ptr(plan), _ptr(pieces),
+                                max_pieces, C.byref(n))
+    if rc != _lib.GH_OK:
+        raise GlinthawkAttnError(rc, "gh_plan_projection")
+    keys = ("ctas", "units_per_cta", "max_segs", "n_tiles", "kblocks")
+    return dict(zip(keys, (int(v) for v in plan))), pieces[: n.value].copy()
+
+
 def decode_noalloc(shape: AttnShape, dtype, layer_contexts, token_positions, query, xb, stream=None) -> None:
     """``gh_decode_noalloc``: fused decode attention for callers that must not allocate device memory (a worker
     whose GPU memory is fully handed out at start-up, a loop that cannot take cudaMalloc's device-wide

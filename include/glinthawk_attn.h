@@ -304,6 +304,20 @@ int gh_op_project_append( gh_attn_t h,
                           void* const* token_rows,
                           void* stream );
 
+/* Host-only (touches no device): how gh_attn_project_append deals its work to the SMs.  plan_out receives
+ * {CTAs, work units per CTA, most pieces a tile is cut into, feature tiles, k-blocks per tile}; pieces_out receives
+ * one record {CTA, tile, first k-block, end k-block, index of the piece within its tile, pieces of that tile} per
+ * piece, CTA by CTA in processing order.  No reference counterpart (the reference calls cuBLAS,
+ * src/arch/cuda/common/ops.cuh:616-693). */
+int gh_plan_projection( uint32_t n_heads,
+                        uint32_t head_size,
+                        uint32_t kv_dim,
+                        uint32_t sm_count,
+                        uint32_t* plan_out,
+                        int32_t* pieces_out,
+                        uint32_t max_pieces,
+                        uint32_t* n_pieces );
+
 /* ---- helpers for benchmarks and tests ------------------------------------------------------------- */
 
 /* Fills n elements of `dtype` at device pointer `dst` with N(0,1) values from a counter-based generator

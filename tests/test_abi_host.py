@@ -7,7 +7,8 @@ import pytest
 import torch
 
 from glinthawk_b200 import _lib
-from glinthawk_b200.stage import plan_batch
+from glinthawk_b200.shapes import SHAPES
+from glinthawk_b200.stage import GlinthawkAttnError, plan_batch, plan_projection
 
 
 def test_library_exports_every_declared_symbol():
@@ -114,3 +115,43 @@ def test_plan_cuts_contexts_only_when_it_pays():
     items, chunk = plan_batch(pos, blocks_per_item=8)
     assert 256 <= chunk < 4096
     _check_plan(pos, items, chunk, 64)
+
+
+@pytest.mark.parametrize("shape_name", ["mini_mha", "mini_g4", "mini_g16", "l7b_4k", "l70b_4k", "l3_8b_8k", "l3_405b"])
+@pytest.mark.parametrize("sm_count", [148, 132, 1, 7])
+def test_projection_work_is_dealt_completely_and_evenly(shape_name, sm_count):
+    """The fused projection deals (feature tile, k-block) units to the CTAs as contiguous runs.  Every unit must be
+    covered exactly once, the runs must differ by at most one unit's worth, and the piece numbering the finishing
+    kernel relies on (piece index within its tile, pieces per tile, bounded by max_segs) must be consistent."""
+    sh = SHAPES[shape_name]
+    plan, pieces = plan_projection(sh, sm_count=sm_count, max_pieces=1 << 16)
+    n_tiles, kb = plan["n_tiles"], plan["kblocks"]
+    assert n_tiles == (sh.dim + 2 * sh.kv_dim) // 128 and kb == sh.dim // 64
+    assert plan["ctas"] <= sm_count
+    covered = np.zeros((n_tiles, kb), dtype=np.int32)
+    per_cta = np.zeros(plan["ctas"], dtype=np.int64)
+    seen = {}
+    for cta, tile, k0, k1, seg, nsegs in pieces:
+        assert 0 <= k0 < k1 <= kb and 0 <= seg < nsegs <= plan["max_segs"]
+        covered[tile, k0:k1] += 1
+        per_cta[cta] += k1 - k0
+        seen.setdefault(tile, []).append((k0, k1, seg, nsegs))
+    assert (covered == 1).all(), "every (tile, k-block) unit exactly once"
+    assert per_cta.max() == plan["units_per_cta"] and per_cta.sum() == n_tiles * kb
+    assert (per_cta[:-1] == plan["units_per_cta"]).all(), "only the last CTA may run short"
+    for tile, segs in seen.items():
+        segs.sort()
+        assert [s[2] for s in segs] == list(range(len(segs))), "pieces are numbered in k order"
+        assert all(s[3] == len(segs) for s in segs), "every piece knows how many pieces its tile has"
+    # the order inside a CTA is the order of the units
+    for cta in range(plan["ctas"]):
+        mine = pieces[pieces[:, 0] == cta]
+        start = mine[:, 1] * kb + mine[:, 2]
+        assert (np.diff(start) > 0).all()
+
+
+def test_projection_plan_refuses_shapes_the_kernel_does_not_take():
+    with pytest.raises(GlinthawkAttnError) as e:
+        plan_projection(SHAPES["tiny15m"])
+    assert e.value.status == _lib.GH_ERR_UNSUPPORTED
+
