@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--static", action="store_true", help="fully resident slots instead of paged ones")
     ap.add_argument("--decode-chunk", type=int, default=0)
+    ap.add_argument("--overlap-prefill", action="store_true",
+                    help="mixed workloads: issue the prompt chunks on a second stream so that they run beside the decode "
+                         "launches of the same step instead of after them")
     ap.add_argument("--producer", action="store_true",
                     help="each layer-step also runs the stage's producer on the device (rmsnorm + q/kv projection with "
                          "the RoPE + append epilogue, gh_attn_project_append) instead of taking q and K/V rows as given")
@@ -313,13 +316,30 @@ def main():
     handle = stage._h
 
     producer_events, prefill_events = [], []
+    pf_stream = torch.cuda.Stream(device=dev) if (n_pf and args.overlap_prefill) else None
+
+    def issue_chunk(l, record):
+        ps = pf_stream if pf_stream is not None else stream
+        if record is not None:
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(ps)
+        stage.prefill_chunk(l, pf_slots, pf_pos0, t_pf, pf_q[l], pf_kv[l], pf_xb[l], stream=ps)
+        if record is not None:
+            f1.record(ps)
+            prefill_events.append((f0, f1))
 
     def device_step(record=None):
         """One token for every context through all layers.  With `record`, every 8th layer's decode launch is
         bracketed by events (the append and decode launches of the other layers stay back to back, which is what
         lets the decode kernel's prologue overlap the append kernel)."""
         stage.batch_begin(slots, pos)
+        if pf_stream is not None:  # the chunks of this step may start once the previous step has been issued ...
+            fork = torch.cuda.Event()
+            fork.record(stream)
+            pf_stream.wait_event(fork)
         for l in range(n_layers):
+            if pf_stream is not None:
+                issue_chunk(l, record)
             if args.producer:
                 timed = record is not None and l % 8 == min(3, n_layers - 1)
                 if timed:
@@ -344,14 +364,12 @@ def main():
                 record.append((e0, e1))
             elif ghlib.gh_attn_step(handle, l, q_ptr[l], kv_ptr[l], xb_ptr[l], st_ptr) != 0:
                 raise RuntimeError(ghlib.gh_attn_last_error(handle).decode())
-            if n_pf:
-                if record is not None:
-                    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    f0.record(stream)
-                stage.prefill_chunk(l, pf_slots, pf_pos0, t_pf, pf_q[l], pf_kv[l], pf_xb[l])
-                if record is not None:
-                    f1.record(stream)
-                    prefill_events.append((f0, f1))
+            if n_pf and pf_stream is None:
+                issue_chunk(l, record)
+        if pf_stream is not None:  # ... and the step is over when both streams are
+            join = torch.cuda.Event()
+            join.record(pf_stream)
+            stream.wait_event(join)
         pos[:] += 1
 
     def barrier():
