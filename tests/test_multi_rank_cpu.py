@@ -121,3 +121,30 @@ def test_stage_handoff_protocol_between_two_ranks():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == {"dense": True, "attention": True}
+
+
+def test_reference_arm_under_torchrun_prints_one_line_from_rank_zero(tmp_path):
+    """`bench.py --impl reference` launched the way the multi-GPU runs launch it: rank 0 times the reference's CPU
+    code and prints the JSON line, the other rank leaves with status 0 and prints nothing.  (No GPU involved.)"""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import pytest
+
+    from tests import cases
+    if cases.Reference.try_load() is None:
+        pytest.skip("the reference library is not built here")
+    root = Path(__file__).resolve().parents[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), str(root / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+           "--warmup", "1", "--layers", "1", "--cpu-contexts", "2"]
+    res = subprocess.run(cmd, cwd=tmp_path, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, res.stdout
+    out = json.loads(lines[0])
+    assert out["impl"] == "reference" and out["n_gpus"] == 2 and out["value"] > 0
+    assert out["cpu_baseline"]["kind"] in ("reference", "port") and out["e2e"]["h2d_bytes_per_step"] == 0
+
