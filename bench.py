@@ -68,6 +68,26 @@ def parse_args():
 # ------------------------------------------------------------------------------------------------------------
 # clocks
 
+def bind_near_gpu(index: int) -> str:
+    """With several ranks on one host, keep each rank's threads (and, by first touch, its pinned host buffers) on the
+    CPUs NVML reports as closest to its GPU, so that the host<->device copies of the end-to-end path do not cross
+    sockets.  Changes this process's CPU affinity only; nothing on the GPU."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        pick = near & allowed
+        if not pick or pick == allowed:
+            return "unchanged (%d cpus)" % len(allowed)
+        os.sched_setaffinity(0, pick)
+        return "%d of %d cpus, those nearest the GPU" % (len(pick), len(allowed))
+    except Exception as e:  # noqa: BLE001
+        return "unchanged (%s)" % type(e).__name__
+
+
 class ClockSampler:
     """Samples SM clock, power and throttle reasons of one GPU through NVML (read-only) while a region runs."""
 
@@ -242,6 +262,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the attention stage has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    host_affinity = bind_near_gpu(local_rank) if world > 1 else "unchanged (single rank)"
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -466,7 +487,7 @@ def main():
         keys = n_pf * (t_pf * wl.prefill_pos0 + t_pf * (t_pf + 1) / 2)
         flops = 4.0 * keys * sh.n_heads * sh.head_size
         chunk_bytes = n_pf * t_pf * (2 * row_elems + 2 * sh.dim) * elem  # append: K/V rows and q, read and written
-        prefill = {"kernels": "append_chunk_kernel + " + ("decode_mma_kernel in chunk mode"
+        prefill = {"kernels": "append_ordered_kernel + " + ("decode_mma_kernel in chunk mode"
                                                              if os.environ.get("GLINTHAWK_PREFILL") == "mma"
                                                              else "prefill_umma_kernel (tcgen05)"),
                    "ms_per_chunk_call": fms_mean, "prompt_tokens_per_call": n_pf * t_pf,
@@ -500,6 +521,7 @@ def main():
                        "mean_cached_tokens": mean_tokens / batch, "kv_resident_gb": stats.bytes_mapped / 1e9,
                        "l2": "inputs larger than L2: each layer-step streams %.2f GB of KV" % (mean_tokens * row / 1e9),
                        "parallelism": f"contexts sharded by request over {world} GPU(s), no collective",
+                       "host_affinity": host_affinity,
                        "seed": args.seed, "split_chunk_tokens": stats.last_chunk, "work_items": stats.last_items},
             "value_per_gpu": value / world,
             "hbm_gbs_step": step_bytes / (ms_per_step / 1e3) / 1e9,

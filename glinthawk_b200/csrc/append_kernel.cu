@@ -95,11 +95,12 @@ __global__ void __launch_bounds__( 256 ) append_kernel( const AppendArgs a )
   }
 }
 
-// Prompt chunks: the same arithmetic over hundreds of MB, so bandwidth-bound work.  The units of a token are taken
-// in address order (a warp reads and writes 512 consecutive bytes) and one thread carries its unit through TB
-// consecutive tokens of a context with their loads in flight together.
+// The same arithmetic with the units of a token taken in address order (a warp reads and writes 512 consecutive
+// bytes); one thread carries its unit through TB consecutive tokens of a context with their loads in flight together.
+// Used for decode steps (TB = 1) and prompt chunks (TB = 2: hundreds of MB, bandwidth-bound) whenever the rows go to
+// the arena's own slots; append_kernel above stays for the reference's pointer-array operations.
 template<typename T, int TB>
-__global__ void __launch_bounds__( 256, 6 ) append_chunk_kernel( const AppendArgs a )
+__global__ void __launch_bounds__( 256, 6 ) append_ordered_kernel( const AppendArgs a )
 {
   constexpr int N = Vec16<T>::N;
   const Shape& sh = a.sh;
@@ -184,19 +185,28 @@ cudaError_t launch_append( const AppendArgs& args, cudaStream_t st, uint64_t* la
   const unsigned n16 = a.dtype == DT_F32 ? 4 : 8;
   const unsigned units = ( a.sh.kv_dim / n16 ) * ( 2 + a.sh.group );
   const unsigned tokens = a.tokens_per_ctx > 0 ? a.tokens_per_ctx : 1;
-  // prompt chunks with rotation, new rows and the arena's own slots (what the chunk entry point passes)
-  // prompt chunks with rotation, new rows and the arena's own slots (what the chunk entry point passes).  Two
-  // tokens per thread measured best on B200 (1, 2, 3, 4, 8, 16 tried): more tokens per thread cost more in
-  // occupancy than they gain in loads in flight.
-  constexpr int TB = 2;
-  if ( tokens >= TB && a.token_rows == nullptr && a.kv_new != nullptr && a.rope_cos != nullptr ) {
+  // Rotation + new rows + the arena's own slots (what gh_attn_append and the chunk entry point pass): the kernel
+  // that walks a token's units in address order.  Two tokens per thread measured best for prompt chunks on B200
+  // (1, 2, 3, 4, 8, 16 tried: more tokens per thread cost more in occupancy than they gain in loads in flight); a
+  // decode step has one token per context, and the address order alone shortens its launch by about a fifth.
+  if ( a.token_rows == nullptr && a.kv_new != nullptr && a.rope_cos != nullptr ) {
     const unsigned cunits = 2 * ( a.sh.kv_dim / n16 ) + ( a.q != nullptr ? a.sh.n_heads * a.sh.head_size / n16 : 0 );
-    const dim3 cgrid( a.batch * ( ( tokens + TB - 1 ) / TB ), ( cunits + 255 ) / 256 );
-    switch ( a.dtype ) {
-      case DT_F32: append_chunk_kernel<float, TB><<<cgrid, 256, 0, st>>>( a ); break;
-      case DT_F16: append_chunk_kernel<__half, TB><<<cgrid, 256, 0, st>>>( a ); break;
-      case DT_BF16: append_chunk_kernel<__nv_bfloat16, TB><<<cgrid, 256, 0, st>>>( a ); break;
-      default: return cudaErrorInvalidValue;
+    const unsigned tb = tokens >= 2 ? 2 : 1;
+    const dim3 cgrid( a.batch * ( ( tokens + tb - 1 ) / tb ), ( cunits + 255 ) / 256 );
+    if ( tb == 2 ) {
+      switch ( a.dtype ) {
+        case DT_F32: append_ordered_kernel<float, 2><<<cgrid, 256, 0, st>>>( a ); break;
+        case DT_F16: append_ordered_kernel<__half, 2><<<cgrid, 256, 0, st>>>( a ); break;
+        case DT_BF16: append_ordered_kernel<__nv_bfloat16, 2><<<cgrid, 256, 0, st>>>( a ); break;
+        default: return cudaErrorInvalidValue;
+      }
+    } else {
+      switch ( a.dtype ) {
+        case DT_F32: append_ordered_kernel<float, 1><<<cgrid, 256, 0, st>>>( a ); break;
+        case DT_F16: append_ordered_kernel<__half, 1><<<cgrid, 256, 0, st>>>( a ); break;
+        case DT_BF16: append_ordered_kernel<__nv_bfloat16, 1><<<cgrid, 256, 0, st>>>( a ); break;
+        default: return cudaErrorInvalidValue;
+      }
     }
     ( *launches )++;
     return cudaGetLastError();
