@@ -56,12 +56,14 @@ def test_inactive_prompts_get_no_row_and_large_batches_go_in_slices(oracle):
     st.close()
 
 
-def test_full_size_weights_cut_across_all_sms(oracle):
-    """Llama2-70B's matrices (8192 x 8192 and 2048 x 8192): 80 tiles of 128 k-blocks dealt to one CTA per SM, so
-    most tiles are finished from two CTAs' partial sums."""
-    sh = SHAPES["l70b_4k"]
-    pos = np.array([0, 1, 100, 1000, 4095, 17, 33, 2048], dtype=np.uint32)
-    case = cases.make_proj_case("proj70b", "l70b_4k", cases.F16, pos, seed=5)
+@pytest.mark.parametrize("shape_name,dtype", [("l70b_4k", cases.F16), ("l3_8b_8k", cases.BF16), ("l3_405b", cases.F16)])
+def test_full_size_weights_cut_across_all_sms(oracle, shape_name, dtype):
+    """The real matrices (Llama2-70B: 8192 x 8192 and 2048 x 8192, 80 tiles of 128 k-blocks; Llama3-8B; Llama3-405B:
+    16384 x 16384, 144 tiles of 256 k-blocks) dealt to one CTA per SM, so most tiles are finished from several CTAs'
+    partial sums."""
+    sh = SHAPES[shape_name]
+    pos = np.array([0, 1, 100, 1000, sh.seq_len - 1, 17, 33, sh.seq_len // 2], dtype=np.uint32)
+    case = cases.make_proj_case("projfull", shape_name, dtype, pos, seed=5)
     want = oracle.pre_attention(case)
     q_out, rows, st, _ = _run(case)
     _check(case, want, q_out, rows)
