@@ -170,7 +170,7 @@ def cpu_layer_step_timer(wl, lens_sample, seed):
     if ref is not None and wl.shape.name in ref.names:
         runner, kind, cores = ref, "reference", ref.threads()
     else:
-        runner, kind, cores = cases.Oracle(), "port", os.cpu_count() or 1
+        runner, kind, cores = cases.Oracle(), "port", usable_cpus()
     return (lambda: runner.layer_step(case)), kind, cores
 
 
@@ -198,10 +198,18 @@ def time_cpu_sample(wl, lens, n_ctx, n_layers, seed, reps):
     }, times
 
 
+def usable_cpus() -> int:
+    """CPUs this process may run on (a container's cpuset can be much smaller than the machine)."""
+    try:
+        return len(os.sched_getaffinity(0)) or 1
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def use_all_host_threads():
     """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every core, so
     the variable is put back before the OpenMP runtime of the reference library starts."""
-    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(usable_cpus())
 
 
 def run_reference_arm(args, wl, n_layers, batch):
