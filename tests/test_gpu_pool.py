@@ -149,6 +149,32 @@ def test_misaligned_device_buffers_are_refused_before_any_launch():
     st.close()
 
 
+def test_a_batch_of_inactive_prompts_only_is_a_no_op():
+    """The reference's batches keep their size when prompts finish: a batch can consist of empty contexts only
+    (src/compute/contextman.hh:128-171).  Every entry point then succeeds and writes nothing."""
+    sh = SHAPES["mini_g4"]
+    st = AttentionStage(sh, torch.float16, n_layers_hosted=1, max_batch=3, max_contexts=3, paged=True)
+    cos = torch.ones(sh.seq_len, sh.head_size // 2, device="cuda", dtype=torch.float16)
+    st.set_rope_tables(cos, torch.zeros_like(cos))
+    st.batch_begin([-1, -1, -1], [0, 5, 9])
+    q = torch.ones(3, sh.dim, device="cuda", dtype=torch.float16)
+    kv = torch.ones(3, 2 * sh.kv_dim, device="cuda", dtype=torch.float16)
+    xb = torch.full_like(q, 3.0)
+    st.step(0, q, kv, xb)
+    st.prefill_chunk(0, [-1, -1], [0, 0], 4, torch.ones(2, 4, sh.dim, device="cuda", dtype=torch.float16),
+                     torch.ones(2, 4, 2 * sh.kv_dim, device="cuda", dtype=torch.float16),
+                     torch.full((2, 4, sh.dim), 3.0, device="cuda", dtype=torch.float16))
+    x = torch.ones(3, sh.dim, device="cuda", dtype=torch.float16)
+    w = torch.zeros(sh.dim, sh.dim, device="cuda", dtype=torch.float16)
+    st.project_append(0, x, x[0].contiguous(), w, torch.zeros(2 * sh.kv_dim, sh.dim, device="cuda", dtype=torch.float16),
+                      torch.empty_like(q))
+    torch.cuda.synchronize()
+    stats = st.stats()
+    assert stats.device_error == 0 and stats.bytes_mapped == 0, "no page was mapped for anybody"
+    assert (xb == 3.0).all() and (q == 1.0).all()
+    st.close()
+
+
 def test_fill_normal_statistics():
     sh = SHAPES["tiny15m"]
     st = AttentionStage(sh, torch.float32, n_layers_hosted=1, max_batch=1, max_contexts=1)
