@@ -1,17 +1,17 @@
 // The producer of the attention stage fused to it: rmsnorm, the q and kv projections on the 5th-generation tensor
-// cores (tcgen05 + TMEM), and RoPE + K/V append straight from the accumulators.
+// cores (tcgen05 + TMEM), and RoPE + K/V append from the fp32 sums.
 //
 // Replaces, per layer-step, the reference's
 //   rmsnorm( xb, x, rms_att_weight ); matmul( q, xb, wq ); matmul( kv, xb, wkv );   src/models/llama2/model.hh:326-343
 //   copy_kv_cache( token_contexts, kv ); apply_rope( pos, fcr, fci, q, token_contexts )            model.hh:345-360
-// (operations: src/arch/amd64/common/ops.hh:141-170, 212-229; src/arch/amd64/llama2/ops.hh:138-164, 300-352).  The kv
-// scratch buffer in the storage type disappears: K and V go from the fp32 sums into the slot rows.  Rounding points are the reference's: xb, q and
-// kv are rounded to the storage type, the rotation is done in fp32 on those rounded values with separately rounded
-// products and rounded once more.
+// (operations: src/arch/amd64/common/ops.hh:141-170, 212-229; src/arch/amd64/llama2/ops.hh:138-164, 300-352).  The
+// kv scratch buffer in the storage type disappears: K and V go from the fp32 sums into the slot rows.  Rounding points
+// are the reference's: xb, q and kv are rounded to the storage type, the rotation is done in fp32 on those rounded
+// values with separately rounded products and rounded once more.
 //
 // The GEMM is skinny (a decode batch of at most a few hundred rows against [dim + 2 kv_dim] x [dim] weights), so the
 // weight stream is what has to be kept flowing and the weights take the MMA's M side:
-//   D[128 features x Nb batch rows] += W[128 x 64] . XB[Nb x 64]^T          tcgen05.mma M = 128, N = Nb <= 256, fp32 in TMEM
+//   D[128 features x Nb batch rows] += W[128 x 64] . XB[Nb x 64]^T     tcgen05.mma M = 128, N = Nb <= 256, fp32 in TMEM
 // Work unit = (tile of 128 output features, block of 64 k).  The units are dealt to the CTAs (one per SM) as equal
 // contiguous runs, so a CTA works through the tail of one tile, some whole tiles and the head of another
 // ("stream-K"): all SMs stream weights for the same time whatever the number of tiles.  Every piece leaves its fp32
@@ -21,8 +21,8 @@
 // rotation it cost 70 us of tail at 256 rows; the wide kernel costs a few.)
 //
 // Roles per CTA: warps 0..3 = read-out (thread r owns feature r of the tile = TMEM lane r), one lane of warp 4 = TMA
-// producer (ring of W and XB tiles, 4 to 10 stages deep, 128-byte swizzle), one lane of warp 5 = MMA issuer.  Two TMEM accumulators
-// so that the next piece is multiplied while the previous one is written out.  Every wait is bounded.
+// producer (ring of W and XB tiles, 4 to 10 stages deep, 128-byte swizzle), one lane of warp 5 = MMA issuer.  Two TMEM
+// accumulators so that the next piece is multiplied while the previous one is written out.  Every wait is bounded.
 #include <algorithm>
 #include <type_traits>
 
