@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--static", action="store_true", help="fully resident slots instead of paged ones")
     ap.add_argument("--decode-chunk", type=int, default=0)
+    ap.add_argument("--pipeline-steps", action="store_true",
+                    help="create the stage with pipeline_steps = 1: the append launch of layer l+1 may start while the "
+                         "decode launch of layer l runs (the layers of a step use separate buffers and rows)")
     ap.add_argument("--overlap-prefill", action="store_true",
                     help="mixed workloads: issue the prompt chunks on a second stream so that they run beside the decode "
                          "launches of the same step instead of after them")
@@ -287,7 +290,8 @@ def main():
     t_setup = time.perf_counter()
     n_pf, t_pf = wl.prefill_contexts, wl.prefill_tokens
     stage = AttentionStage(sh, tdt, n_layers_hosted=n_layers, max_batch=max(batch, n_pf), max_contexts=batch + n_pf,
-                           paged=not args.static, device=local_rank, decode_chunk=args.decode_chunk)
+                           paged=not args.static, device=local_rank, decode_chunk=args.decode_chunk,
+                           pipeline_steps=args.pipeline_steps)
     cos, sin = rope_tables(sh.head_size, sh.seq_len, sh.rope_theta)
     stage.set_rope_tables(torch.from_numpy(cos).to(dev).to(tdt), torch.from_numpy(sin).to(dev).to(tdt))
     slots = stage.get_contexts(np.arange(1, batch + 1, dtype=np.uint32))
@@ -529,7 +533,7 @@ def main():
                        "mean_cached_tokens": mean_tokens / batch, "kv_resident_gb": stats.bytes_mapped / 1e9,
                        "l2": "inputs larger than L2: each layer-step streams %.2f GB of KV" % (mean_tokens * row / 1e9),
                        "parallelism": f"contexts sharded by request over {world} GPU(s), no collective",
-                       "host_affinity": host_affinity,
+                       "host_affinity": host_affinity, "pipeline_steps": bool(args.pipeline_steps),
                        "seed": args.seed, "split_chunk_tokens": stats.last_chunk, "work_items": stats.last_items},
             "value_per_gpu": value / world,
             "hbm_gbs_step": step_bytes / (ms_per_step / 1e3) / 1e9,

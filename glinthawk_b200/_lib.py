@@ -26,7 +26,7 @@ class Config(C.Structure):
                 ("head_size", C.c_uint32), ("seq_len", C.c_uint32), ("n_layers_hosted", C.c_uint32),
                 ("dtype", C.c_uint32), ("max_batch", C.c_uint32), ("max_contexts", C.c_uint32),
                 ("backing", C.c_uint32), ("device", C.c_int32), ("decode_chunk", C.c_uint32),
-                ("page_budget", C.c_uint64), ("force_generic", C.c_uint32), ("reserved", C.c_uint32)]
+                ("page_budget", C.c_uint64), ("force_generic", C.c_uint32), ("pipeline_steps", C.c_uint32)]
 
 
 class NoallocShape(C.Structure):

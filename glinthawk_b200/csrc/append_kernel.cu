@@ -193,6 +193,28 @@ cudaError_t launch_append( const AppendArgs& args, cudaStream_t st, uint64_t* la
     const unsigned cunits = 2 * ( a.sh.kv_dim / n16 ) + ( a.q != nullptr ? a.sh.n_heads * a.sh.head_size / n16 : 0 );
     const unsigned tb = tokens >= 2 ? 2 : 1;
     const dim3 cgrid( a.batch * ( ( tokens + tb - 1 ) / tb ), ( cunits + 255 ) / 256 );
+    if ( a.dependent_launch != 0 && tb == 1 ) {
+      // The caller declared consecutive steps independent: this launch may begin while the decode kernel before it
+      // in the stream is still running (that kernel releases its dependents at once in this mode).
+      cudaLaunchConfig_t cfg {};
+      cfg.gridDim = cgrid;
+      cfg.blockDim = dim3( 256 );
+      cfg.stream = st;
+      cudaLaunchAttribute attr {};
+      attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr.val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      cudaError_t e;
+      switch ( a.dtype ) {
+        case DT_F32: e = cudaLaunchKernelEx( &cfg, append_ordered_kernel<float, 1>, a ); break;
+        case DT_F16: e = cudaLaunchKernelEx( &cfg, append_ordered_kernel<__half, 1>, a ); break;
+        case DT_BF16: e = cudaLaunchKernelEx( &cfg, append_ordered_kernel<__nv_bfloat16, 1>, a ); break;
+        default: return cudaErrorInvalidValue;
+      }
+      ( *launches )++;
+      return e;
+    }
     if ( tb == 2 ) {
       switch ( a.dtype ) {
         case DT_F32: append_ordered_kernel<float, 2><<<cgrid, 256, 0, st>>>( a ); break;

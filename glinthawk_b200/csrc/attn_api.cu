@@ -306,6 +306,8 @@ DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, uint32_t n_spli
   a.xb = xb;
   a.dev_error = h->dev_error;
   a.sm_count = h->sm_count;
+  // (a merge launch behind the decode kernel has to wait for all of it, so nothing could start early anyway)
+  a.trigger_early = ( h->cfg.pipeline_steps != 0 && n_split == 0 ) ? 1u : 0u;
   return a;
 }
 
@@ -730,6 +732,7 @@ int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_n
   a.kv_new = kv_new;
   a.rope_cos = h->rope_cos;
   a.rope_sin = h->rope_sin;
+  a.dependent_launch = h->cfg.pipeline_steps != 0 ? 1u : 0u;
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
   if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
     return cuda_fail( h, "append kernel launch", e );

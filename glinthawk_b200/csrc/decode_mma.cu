@@ -171,6 +171,8 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   constexpr bool ROWS16 = G16 || CHUNK;
   constexpr int kTile = G::kTile, kConsumerWarps = G::kConsumerWarps, kConsumers = G::kConsumers;
   constexpr int kBoxBytes = G::kBoxBytes, kStageBytes = G::kStageBytes, kStages = G::kStages;
+  if ( a.trigger_early ) // the caller declared the next step independent of this one: let its append launch begin
+    asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kStages];
   __shared__ uint64_t bar_empty[kStages];

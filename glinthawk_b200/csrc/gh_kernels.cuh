@@ -24,6 +24,7 @@ struct AppendArgs
   const void* kv_new;   // [batch][2 * kv_dim]; nullptr = rotate the row already in the slot (apply_rope alone)
   const void* rope_cos; // [seq_len][head_size / 2]; nullptr = copy without rotation (copy_kv_cache alone)
   const void* rope_sin;
+  uint32_t dependent_launch; // 1 = launch as a programmatic dependent of the kernel before it (pipeline_steps)
 };
 
 struct DecodeArgs
@@ -44,6 +45,7 @@ struct DecodeArgs
   uint32_t* dev_error;
   uint32_t sm_count;
   uint32_t chunk_tokens; // 0 = decode step; T = prefill chunk of T tokens per context (tensor-core kernel only)
+  uint32_t trigger_early; // 1 = release the next programmatic dependent launch at once (gh_attn_config.pipeline_steps)
 };
 
 struct ScoreArgs // the reference's three unfused operations

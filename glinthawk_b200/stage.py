@@ -62,7 +62,8 @@ class AttentionStage:
 
     def __init__(self, shape: AttnShape, dtype, *, n_layers_hosted: int | None = None, max_batch: int = 64,
                  max_contexts: int = 64, paged: bool = False, device: int = 0, decode_chunk: int = 0,
-                 page_budget: int = 0, force_generic: bool = False, seq_len: int | None = None):
+                 page_budget: int = 0, force_generic: bool = False, seq_len: int | None = None,
+                 pipeline_steps: bool = False):
         self.shape = shape
         self.dtype_code = dtype_code(dtype)
         self.torch_dtype = _TORCH_DTYPE[self.dtype_code]
@@ -73,7 +74,7 @@ class AttentionStage:
         cfg = _lib.Config(C.sizeof(_lib.Config), shape.n_heads, shape.n_kv_heads, shape.head_size, self.seq_len,
                           self.n_layers, self.dtype_code, max_batch, max_contexts,
                           _lib.GH_BACKING_PAGED if paged else _lib.GH_BACKING_STATIC, device, decode_chunk,
-                          page_budget, 1 if force_generic else 0, 0)
+                          page_budget, 1 if force_generic else 0, 1 if pipeline_steps else 0)
         self._h = C.c_void_p(0)
         rc = lib.gh_attn_create(C.byref(cfg), C.byref(self._h))
         if rc != _lib.GH_OK:

@@ -89,7 +89,11 @@ typedef struct gh_attn_config
   uint32_t decode_chunk;    /* tokens per split of a long context; 0 = chosen per batch */
   uint64_t page_budget;     /* PAGED only: upper bound on mapped bytes, 0 = no bound */
   uint32_t force_generic;   /* 1 = always use the CUDA-core decode kernel (testing) */
-  uint32_t reserved;
+  uint32_t pipeline_steps;  /* 1 = the append launch of a gh_attn_append / gh_attn_step call may start while the decode
+                             * launch of the call before it on the same stream is still running (programmatic
+                             * dependent launch).  For callers whose consecutive calls are independent of each other:
+                             * another layer or another batch, and q / kv_new / xb buffers that the previous call
+                             * neither reads nor writes.  0 (default) = calls execute strictly one after the other. */
 } gh_attn_config;
 
 typedef struct gh_attn_stats

@@ -174,3 +174,34 @@ def test_full_llama2_70b_batch_many_steps_stay_finite_and_consistent():
         pos += 1
     assert st.stats().bytes_mapped > mapped0 and st.stats().device_error == 0
     st.close()
+
+
+def test_pipelined_layer_steps_give_the_same_bits_as_strict_ones():
+    """pipeline_steps = 1 lets the append launch of the next layer-step begin while the decode launch before it is
+    still running.  With separate q / kv / xb buffers per layer (what the option demands) every layer's output and
+    every appended row must be bit-identical to the strictly ordered run, over several steps of 8 layers at the
+    benchmark's batch."""
+    outs = []
+    for pipelined in (False, True):
+        wl, st, slots, lens, q, kv = build("llama2_70b_gqa", batch=256, layers=8, headroom=8, pipeline_steps=pipelined)
+        sh = wl.shape
+        tdt = q.dtype
+        qs = torch.empty((8, *q.shape), dtype=tdt, device="cuda")
+        kvs = torch.empty((8, *kv.shape), dtype=tdt, device="cuda")
+        st.fill_normal(qs, qs.numel(), tdt, 31)
+        st.fill_normal(kvs, kvs.numel(), tdt, 32)
+        xbs = torch.zeros_like(qs)
+        pos = lens.astype(np.uint32).copy()
+        for _ in range(3):
+            st.batch_begin(slots, pos)
+            for l in range(8):
+                st.step(l, qs[l], kvs[l], xbs[l])
+            pos += 1
+        torch.cuda.synchronize()
+        assert st.stats().device_error == 0
+        rows = torch.stack([st.layer_view(int(slots[i]), 7, int(pos[i]))[-3:].clone() for i in range(0, 256, 17)])
+        outs.append((xbs.clone(), qs.clone(), rows))
+        st.close()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
