@@ -54,6 +54,37 @@ constexpr int kTmemCols = 256;             // S buffers: columns 0..63 and 64..1
 constexpr float kGrowLog2 = 8.f;           // a row's maximum may lag its true maximum by this much (log2 units)
 using namespace umma;
 
+// Two fp32 values in one 64-bit register for the packed fp32 instructions of sm_100 (fma.rn.f32x2, add.rn.f32x2):
+// the row owners are short of issue slots, and these halve the scale-and-shift and the row-sum instructions.
+__device__ __forceinline__ unsigned long long pack_f2( float lo, float hi )
+{
+  unsigned long long r;
+  asm( "mov.b64 %0, {%1, %2};" : "=l"( r ) : "f"( lo ), "f"( hi ) );
+  return r;
+}
+__device__ __forceinline__ void unpack_f2( unsigned long long v, float& lo, float& hi )
+{
+  asm( "mov.b64 {%0, %1}, %2;" : "=f"( lo ), "=f"( hi ) : "l"( v ) );
+}
+__device__ __forceinline__ unsigned long long fma_f2( unsigned long long a, unsigned long long b, unsigned long long c )
+{
+  unsigned long long r;
+  asm( "fma.rn.f32x2 %0, %1, %2, %3;" : "=l"( r ) : "l"( a ), "l"( b ), "l"( c ) );
+  return r;
+}
+__device__ __forceinline__ unsigned long long add_f2( unsigned long long a, unsigned long long b )
+{
+  unsigned long long r;
+  asm( "add.rn.f32x2 %0, %1, %2;" : "=l"( r ) : "l"( a ), "l"( b ) );
+  return r;
+}
+__device__ __forceinline__ float max3( float a, float b, float c )
+{
+  float r;
+  asm( "max.f32 %0, %1, %2, %3;" : "=f"( r ) : "f"( a ), "f"( b ), "f"( c ) );
+  return r;
+}
+
 // MN-major operand (V: [keys][64 dims] regions): the next 64 dims are one region further, the next 8 keys 1024 B.
 __device__ __forceinline__ uint64_t desc_mnmajor( uint32_t saddr )
 {
@@ -311,7 +342,7 @@ __global__ void __launch_bounds__( kThreads, 2 )
       if ( full_tile ) {
 #pragma unroll
         for ( int j = 0; j < 32; j++ )
-          tmax = fmaxf( tmax, fmaxf( sc[j], sc[32 + j] ) );
+          tmax = max3( tmax, sc[j], sc[32 + j] );
       } else {
 #pragma unroll
         for ( int j = 0; j < 32; j++ ) {
@@ -333,14 +364,21 @@ __global__ void __launch_bounds__( kThreads, 2 )
       const float neg_m = ( m == -INFINITY ) ? 0.f : -m; // a row that sees nothing carries zeros, not NaNs
       uint32_t pk[32];
       if ( full_tile ) {
+        const unsigned long long scale2 = pack_f2( scale_log2, scale_log2 ), shift2 = pack_f2( neg_m, neg_m );
+        unsigned long long l2 = pack_f2( 0.f, 0.f );
 #pragma unroll
         for ( int j = 0; j < 32; j += 2 ) {
-          const float a0 = fast_exp2( fmaf( sc[j], scale_log2, neg_m ) ), a1 = fast_exp2( fmaf( sc[j + 1], scale_log2, neg_m ) );
-          const float b0 = fast_exp2( fmaf( sc[32 + j], scale_log2, neg_m ) ), b1 = fast_exp2( fmaf( sc[33 + j], scale_log2, neg_m ) );
-          l += ( a0 + a1 ) + ( b0 + b1 );
+          float xa0, xa1, xb0, xb1;
+          unpack_f2( fma_f2( pack_f2( sc[j], sc[j + 1] ), scale2, shift2 ), xa0, xa1 );
+          unpack_f2( fma_f2( pack_f2( sc[32 + j], sc[33 + j] ), scale2, shift2 ), xb0, xb1 );
+          const float a0 = fast_exp2( xa0 ), a1 = fast_exp2( xa1 ), b0 = fast_exp2( xb0 ), b1 = fast_exp2( xb1 );
+          l2 = add_f2( l2, add_f2( pack_f2( a0, a1 ), pack_f2( b0, b1 ) ) );
           pk[j >> 1] = pack2<T>( a0, a1 );
           pk[16 + ( j >> 1 )] = pack2<T>( b0, b1 );
         }
+        float l_lo, l_hi;
+        unpack_f2( l2, l_lo, l_hi );
+        l += l_lo + l_hi;
       } else {
 #pragma unroll
         for ( int j = 0; j < 32; j += 2 ) {
