@@ -38,7 +38,8 @@ class Stats(C.Structure):
     _fields_ = [("kernel_launches", C.c_uint64), ("bytes_mapped", C.c_uint64), ("bytes_reserved", C.c_uint64),
                 ("scratch_bytes", C.c_uint64), ("slots_free", C.c_uint32), ("slots_allocated", C.c_uint32),
                 ("last_items", C.c_uint32), ("last_chunk", C.c_uint32), ("last_kernel", C.c_uint32),
-                ("device_error", C.c_uint32)]
+                ("device_error", C.c_uint32), ("last_split_contexts", C.c_uint32), ("pad", C.c_uint32),
+                ("batch_plans", C.c_uint64)]
 
 
 _P, _U32, _U64, _I32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32
@@ -49,6 +50,8 @@ _PROTOS = {
     "gh_status_string": (C.c_char_p, [C.c_int]),
     "gh_attn_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "gh_attn_synchronize": (C.c_int, [_P, _P]),
+    "gh_attn_clear_device_error": (C.c_int, [_P]),
+    "gh_attn_inject_device_error": (C.c_int, [_P, _U32]),
     "gh_attn_set_rope_tables": (C.c_int, [_P, _P, _P]),
     "gh_slot_acquire": (C.c_int, [_P, _U32, C.POINTER(_I32)]),
     "gh_slots_acquire_batch": (C.c_int, [_P, _U64, _P, _P]),
@@ -69,6 +72,7 @@ _PROTOS = {
     "gh_attn_forward_attention_host": (C.c_int, [_P, _U32, _U32, _P, _P, _P, _P]),
     "gh_op_copy_kv_cache": (C.c_int, [_P, _P, _P, _U64, _P]),
     "gh_op_apply_rope": (C.c_int, [_P, _U64, _P, _P, _P, _P, _P, _P]),
+    "gh_op_copy_kv_cache_apply_rope": (C.c_int, [_P, _U64, _P, _P, _P, _P, _P, _P, _P]),
     "gh_op_attention_0_gemm": (C.c_int, [_P, _P, _P, _P, _U64, _P, _P]),
     "gh_op_attention_softmax": (C.c_int, [_P, _P, _P, _P, _U64, _P]),
     "gh_op_attention_2_gemm": (C.c_int, [_P, _P, _P, _P, _U64, _P, _P]),

@@ -11,8 +11,9 @@
 // the six attention-stage operations and the context type below forward to the C ABI of glinthawk_attn.h.
 //
 //   reference interface                                   -> what it calls
-//   LlamaOperations::copy_kv_cache       (ops.cuh:435-453)    gh_op_copy_kv_cache
-//   LlamaOperations::apply_rope          (ops.cuh:413-433)    gh_op_apply_rope
+//   LlamaOperations::copy_kv_cache       (ops.cuh:435-453)    held back until apply_rope names the same rows, then
+//   LlamaOperations::apply_rope          (ops.cuh:413-433)    gh_op_copy_kv_cache_apply_rope (one kernel for both); each
+//                                                             on its own: gh_op_copy_kv_cache / gh_op_apply_rope
 //   LlamaOperations::attention_0_gemm    (ops.cuh:272-324)    remembered; see attention_2_gemm
 //   LlamaOperations::attention_softmax   (ops.cuh:385-411)    nothing (fused) / gh_op_attention_softmax
 //   LlamaOperations::attention_2_gemm    (ops.cuh:326-383)    gh_op_attention_fused / gh_op_attention_2_gemm
@@ -23,6 +24,7 @@
 // (CHECK_CUDA -> LOG(FATAL), src/arch/cuda/common/ops.cu:5-19), so a non-zero status is turned into LOG(FATAL).
 #pragma once
 
+#include <algorithm>
 #include <atomic>
 #include <cstdint>
 #include <mutex>
@@ -80,7 +82,7 @@ public:
       cfg.max_batch = static_cast<uint32_t>( settings.concurrency_limit );
       cfg.max_contexts = static_cast<uint32_t>( settings.max_context_count );
       cfg.backing = paged() ? GH_BACKING_PAGED : GH_BACKING_STATIC;
-      cfg.device = 0; // the reference's CUDA backend uses device 0 implicitly (vmem.cuh:29,92)
+      cfg.device = device(); // 0 unless set: the reference's CUDA backend uses device 0 implicitly (vmem.cuh:29,92)
       const int rc = gh_attn_create( &cfg, &h );
       if ( rc != GH_OK )
         LOG( FATAL ) << "gh_attn_create failed: " << gh_status_string( rc );
@@ -99,6 +101,13 @@ public:
   {
     static bool p = false;
     return p;
+  }
+
+  // The CUDA device the stage is created on; set it before the first model or context is constructed.
+  static int& device()
+  {
+    static int d = 0;
+    return d;
   }
 
   static uint32_t next_context_id()
@@ -179,6 +188,10 @@ private:
   bool blocking_ { false };
   mutable const DType* pending_query_ { nullptr };
   mutable std::vector<void*> ptrs_;
+  // copy_kv_cache is the last operation of pre_attention_ops and apply_rope the first of attention_ops
+  // (src/models/llama2/model.hh:345-364): the copy is held back so that the two run as one kernel launch.
+  mutable std::vector<void*> pending_copy_rows_;
+  mutable const DType* pending_copy_kv_ { nullptr };
 
   template<typename View>
   void* const* pointers( const View views[], const uint64_t n, const bool token_rows ) const
@@ -213,11 +226,23 @@ public:
   // operations run on the host (on managed or mapped memory) and therefore are not ordered by the CUDA stream.
   void set_blocking( const bool blocking ) { blocking_ = blocking; }
 
+  ~LlamaOperations() { flush_copy(); }
+
 private:
   void done() const
   {
     if ( blocking_ )
       GH_B200_CHECK( h_, gh_attn_synchronize( h_, nullptr ) );
+  }
+
+  // issues a copy_kv_cache that no apply_rope picked up
+  void flush_copy() const
+  {
+    if ( pending_copy_kv_ == nullptr )
+      return;
+    GH_B200_CHECK( h_, gh_op_copy_kv_cache( h_, pending_copy_rows_.data(), pending_copy_kv_, pending_copy_rows_.size(),
+                                            nullptr ) );
+    pending_copy_kv_ = nullptr;
   }
 
 public:
@@ -228,6 +253,7 @@ public:
                          const uint64_t batch_size,
                          const uint32_t* token_positions ) const
   {
+    flush_copy();
     if ( fused_ ) {
       pending_query_ = query; // consumed by attention_2_gemm, which has every other argument
       return;
@@ -240,6 +266,7 @@ public:
   void attention_softmax( DType* att, const uint32_t* token_positions, DType* temp_buffer, const uint64_t batch_size )
     const
   {
+    flush_copy();
     if ( fused_ )
       return;
     GH_B200_CHECK( h_, gh_op_attention_softmax( h_, att, token_positions, temp_buffer, batch_size, nullptr ) );
@@ -252,6 +279,7 @@ public:
                          const uint64_t batch_size,
                          const uint32_t* token_positions ) const
   {
+    flush_copy();
     if ( fused_ ) {
       CHECK( pending_query_ != nullptr ) << "attention_2_gemm without a preceding attention_0_gemm";
       GH_B200_CHECK( h_, gh_op_attention_fused( h_, pending_query_, pointers( layer_contexts, batch_size, false ), xb,
@@ -272,8 +300,19 @@ public:
                    DType* state_q,
                    typename ContextType::TokenContextType token_contexts[] ) const
   {
+    void* const* rows = pointers( token_contexts, curr_batch_size, true );
+    if ( pending_copy_kv_ != nullptr && pending_copy_rows_.size() == curr_batch_size
+         && std::equal( pending_copy_rows_.begin(), pending_copy_rows_.end(), rows ) ) {
+      const DType* state_kv = pending_copy_kv_;
+      pending_copy_kv_ = nullptr;
+      GH_B200_CHECK( h_, gh_op_copy_kv_cache_apply_rope( h_, curr_batch_size, token_positions, freq_cis_real,
+                                                         freq_cis_imag, state_q, rows, state_kv, nullptr ) );
+      done();
+      return;
+    }
+    flush_copy();
     GH_B200_CHECK( h_, gh_op_apply_rope( h_, curr_batch_size, token_positions, freq_cis_real, freq_cis_imag, state_q,
-                                         pointers( token_contexts, curr_batch_size, true ), nullptr ) );
+                                         rows, nullptr ) );
     done();
   }
 
@@ -281,9 +320,15 @@ public:
                       const DType* state_kv,
                       const uint64_t batch_size ) const
   {
-    GH_B200_CHECK( h_, gh_op_copy_kv_cache( h_, pointers( token_contexts, batch_size, true ), state_kv, batch_size,
-                                            nullptr ) );
-    done();
+    flush_copy();
+    void* const* rows = pointers( token_contexts, batch_size, true );
+    if ( blocking_ ) { // the caller may read the rows on the host right away
+      GH_B200_CHECK( h_, gh_op_copy_kv_cache( h_, rows, state_kv, batch_size, nullptr ) );
+      done();
+      return;
+    }
+    pending_copy_rows_.assign( rows, rows + batch_size );
+    pending_copy_kv_ = state_kv;
   }
 
   // Not a reference operation: Llama2::pre_attention_ops with the cache update followed by apply_rope
@@ -301,6 +346,7 @@ public:
                                   const DType* freq_cis_imag,
                                   typename ContextType::TokenContextType token_contexts[] ) const
   {
+    flush_copy();
     GH_B200_CHECK( h_, gh_op_project_append( h_, curr_batch_size, x, rms_att_weight, wq, wkv, state_q, token_positions,
                                              freq_cis_real, freq_cis_imag, pointers( token_contexts, curr_batch_size, true ),
                                              nullptr ) );
@@ -310,6 +356,7 @@ public:
   template<typename DTypeDst, typename DTypeSrc>
   void convert_and_copy( DTypeDst* dst, const DTypeSrc* src, const uint64_t size, const CopyType type ) const
   {
+    flush_copy();
     if constexpr ( std::is_void_v<DTypeDst> || std::is_void_v<DTypeSrc> ) {
       LOG( FATAL ) << "convert_and_copy needs concrete element types";
     } else {

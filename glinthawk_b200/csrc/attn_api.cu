@@ -3,7 +3,6 @@
 
 #include <algorithm>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -19,6 +18,8 @@ using namespace gh;
 namespace {
 
 constexpr uint32_t kRing = 16;       // batch descriptions that may be in flight at once
+constexpr uint32_t kBatchRing = 4;   // of those, the first kBatchRing hold only what gh_attn_batch_begin uploads,
+constexpr uint32_t kOpRing = 2;      // the next kOpRing the description the gh_op_* calls of a layer-step share
 constexpr uint32_t kHostStages = 4;  // staging sets for the host-buffer entry point
 constexpr uint32_t kExtraItems = 1024;
 constexpr uint32_t kScratchSets = 4; // decode launches of one handle that may be in flight on different streams
@@ -95,11 +96,22 @@ struct gh_attn
   uint32_t max_items = 0;
   size_t off_split = 0, off_items = 0, off_ptrs = 0, off_pos = 0, entry_bytes = 0;
   RingEntry ring[kRing];
-  uint32_t ring_next = 0;
+  uint32_t ring_next = 0;       // next transient entry, counted from kBatchRing + kOpRing
+  uint32_t batch_ring_next = 0; // next entry for gh_attn_batch_begin
+  uint32_t op_ring_next = 0;    // next entry for the description shared by gh_op_* calls
+  // The batch the gh_op_* calls were last made for, when their pointer arrays named rows of this handle's own slots
+  // (every layer of a step names the same slots and positions): its uploaded description is reused.
+  int op_entry = -1;
+  uint32_t op_items = 0, op_split = 0;
+  std::vector<int32_t> op_slots, op_slots_tmp;
+  std::vector<uint32_t> op_pos, op_pos_tmp;
   int cur = -1; // ring entry of the batch set up last, -1 = none
   uint32_t cur_batch = 0, cur_items = 0, cur_split = 0;
   std::vector<int32_t> cur_slots;
   std::vector<uint32_t> cur_pos;
+  std::vector<uint8_t> cur_layer_ready; // per hosted layer: the current batch's rows are known to be mapped
+  uint64_t cur_ready_generation = 0;    // pool reset count those marks were taken at
+  bool device_error_seen = false;       // a kernel's bounded wait ran out; calls are refused until it is cleared
 
   // split partials
   ScratchSet scratch[kScratchSets];
@@ -165,11 +177,24 @@ int drain_stream( gh_attn* h, cudaEvent_t ev, cudaStream_t st )
   return GH_OK;
 }
 
-// Claims the next batch-description buffer, waiting (on the host) only if the device may still read it.
-int ring_claim( gh_attn* h, int* idx )
+// Claims the next batch-description buffer, waiting (on the host) only if the device may still read it.  The
+// description of the current batch (gh_attn_batch_begin) lives in entries of its own, which the transient
+// uploads of the other entry points never recycle: it stays valid however many of those follow it.
+enum RingKind { RING_TRANSIENT, RING_BATCH, RING_OP };
+
+int ring_claim( gh_attn* h, int* idx, RingKind kind = RING_TRANSIENT )
 {
-  const uint32_t k = h->ring_next;
-  h->ring_next = ( k + 1 ) % kRing;
+  uint32_t k;
+  if ( kind == RING_BATCH ) {
+    k = h->batch_ring_next;
+    h->batch_ring_next = ( k + 1 ) % kBatchRing;
+  } else if ( kind == RING_OP ) {
+    k = kBatchRing + h->op_ring_next;
+    h->op_ring_next = ( h->op_ring_next + 1 ) % kOpRing;
+  } else {
+    k = kBatchRing + kOpRing + h->ring_next;
+    h->ring_next = ( h->ring_next + 1 ) % ( kRing - kBatchRing - kOpRing );
+  }
   RingEntry& r = h->ring[k];
   if ( r.many_streams ) {
     GH_CUDA( h, cudaDeviceSynchronize() );
@@ -222,7 +247,7 @@ uint32_t* entry_pos( gh_attn* h, char* base )
 
 // Plans `ctx` (kv_off and pos filled in by the caller) and uploads the description into a fresh ring entry.
 int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int* entry, uint32_t* n_items,
-                     uint32_t* n_split )
+                     uint32_t* n_split, RingKind kind = RING_TRANSIENT )
 {
   PlanParams pp;
   pp.n_kv_heads = h->use_mma ? h->sh.n_kv_heads : h->sh.n_heads;
@@ -236,7 +261,7 @@ int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int
     return fail( h, GH_ERR_INVALID, "batch does not fit the work-item buffer" );
 
   int idx;
-  if ( const int rc = ring_claim( h, &idx ); rc != GH_OK )
+  if ( const int rc = ring_claim( h, &idx, kind ); rc != GH_OK )
     return rc;
   RingEntry& r = h->ring[idx];
   std::memcpy( entry_ctx( h, r.host ), ctx.data(), ctx.size() * sizeof( CtxMeta ) );
@@ -251,6 +276,8 @@ int plan_and_upload( gh_attn* h, std::vector<CtxMeta>& ctx, cudaStream_t st, int
   *n_items = static_cast<uint32_t>( plan.items.size() );
   *n_split = static_cast<uint32_t>( plan.split_ctx.size() );
   h->stats.last_items = *n_items;
+  h->stats.last_split_contexts = *n_split;
+  h->stats.batch_plans++;
   h->stats.last_chunk = plan.chunk;
   return GH_OK;
 }
@@ -331,8 +358,21 @@ int run_decode( gh_attn* h, DecodeArgs a, bool allow_mma, cudaStream_t st )
   return scratch_release( h, set, st );
 }
 
+// Once a kernel has reported that one of its bounded waits ran out, its outputs cannot be trusted: every compute
+// entry point refuses to go on until gh_attn_clear_device_error has been called.
+int check_device_ok( gh_attn* h )
+{
+  if ( h->device_error_seen )
+    return fail( h, GH_ERR_CUDA,
+                 "a kernel reported a timed-out wait (gh_attn_stats.device_error = " + std::to_string( h->stats.device_error )
+                   + "); call gh_attn_clear_device_error" );
+  return GH_OK;
+}
+
 int check_batch_ready( gh_attn* h, uint32_t layer )
 {
+  if ( const int rc = check_device_ok( h ); rc != GH_OK )
+    return rc;
   if ( h->cur < 0 )
     return fail( h, GH_ERR_STATE, "no batch: call gh_attn_batch_begin first" );
   if ( layer >= h->sh.n_layers )
@@ -341,18 +381,23 @@ int check_batch_ready( gh_attn* h, uint32_t layer )
 }
 
 // Context::prepare for every active prompt of the current batch (src/models/llama2/model.hh:617-621).
+// The batch is walked once per (batch, layer): the append and decode calls of a layer-step share the result, which
+// stays valid until a slot is reset.
 int prepare_layer( gh_attn* h, uint32_t layer )
 {
   if ( !h->pool.paged() )
     return GH_OK;
-  for ( uint32_t i = 0; i < h->cur_batch; i++ ) {
-    if ( h->cur_slots[i] < 0 )
-      continue;
-    const int rc = h->pool.prepare( h->cur_slots[i], layer, h->cur_pos[i], false, h->err );
-    if ( rc != GH_OK )
-      return rc;
+  const uint64_t generation = h->pool.reset_generation();
+  if ( generation != h->cur_ready_generation ) {
+    std::fill( h->cur_layer_ready.begin(), h->cur_layer_ready.end(), 0 );
+    h->cur_ready_generation = generation;
   }
-  return GH_OK;
+  if ( h->cur_layer_ready[layer] )
+    return GH_OK;
+  const int rc = h->pool.prepare_batch( h->cur_batch, h->cur_slots.data(), h->cur_pos.data(), layer, h->err );
+  if ( rc == GH_OK )
+    h->cur_layer_ready[layer] = 1;
+  return rc;
 }
 
 } // namespace
@@ -553,6 +598,7 @@ int gh_attn_get_stats( gh_attn_t h, gh_attn_stats* out )
   uint32_t flag = 0;
   GH_CUDA( h, cudaMemcpy( &flag, h->dev_error, sizeof( flag ), cudaMemcpyDeviceToHost ) );
   h->stats.device_error = flag;
+  h->device_error_seen = flag != 0;
   *out = h->stats;
   return GH_OK;
 }
@@ -562,7 +608,40 @@ int gh_attn_synchronize( gh_attn_t h, void* stream )
   if ( h == nullptr )
     return GH_ERR_INVALID;
   DeviceGuard guard( h->device );
-  GH_CUDA( h, cudaStreamSynchronize( static_cast<cudaStream_t>( stream ) ) );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  uint32_t flag = 0; // the kernels' error word rides along: the caller learns of a timed-out wait where it waits anyway
+  GH_CUDA( h, cudaMemcpyAsync( &flag, h->dev_error, sizeof( flag ), cudaMemcpyDeviceToHost, st ) );
+  GH_CUDA( h, cudaStreamSynchronize( st ) );
+  if ( flag != 0 ) {
+    h->stats.device_error = flag;
+    h->device_error_seen = true;
+    return check_device_ok( h );
+  }
+  return GH_OK;
+}
+
+int gh_attn_inject_device_error( gh_attn_t h, uint32_t bits )
+{
+  if ( h == nullptr )
+    return GH_ERR_INVALID;
+  DeviceGuard guard( h->device );
+  uint32_t flag = 0;
+  GH_CUDA( h, cudaDeviceSynchronize() );
+  GH_CUDA( h, cudaMemcpy( &flag, h->dev_error, sizeof( flag ), cudaMemcpyDeviceToHost ) );
+  flag |= bits;
+  GH_CUDA( h, cudaMemcpy( h->dev_error, &flag, sizeof( flag ), cudaMemcpyHostToDevice ) );
+  return GH_OK;
+}
+
+int gh_attn_clear_device_error( gh_attn_t h )
+{
+  if ( h == nullptr )
+    return GH_ERR_INVALID;
+  DeviceGuard guard( h->device );
+  GH_CUDA( h, cudaDeviceSynchronize() );
+  GH_CUDA( h, cudaMemset( h->dev_error, 0, sizeof( uint32_t ) ) );
+  h->stats.device_error = 0;
+  h->device_error_seen = false;
   return GH_OK;
 }
 
@@ -581,16 +660,14 @@ int gh_slot_acquire( gh_attn_t h, uint32_t context_id, int32_t* slot )
 {
   if ( h == nullptr || slot == nullptr )
     return GH_ERR_INVALID;
-  const int rc = h->pool.acquire( context_id, slot );
-  return rc == GH_OK ? rc : fail( h, rc, "no free context slot" );
+  return h->pool.acquire( context_id, slot ); // status only: may run beside the thread that owns the handle
 }
 
 int gh_slots_acquire_batch( gh_attn_t h, uint64_t batch, const uint32_t* context_ids, int32_t* slots )
 {
   if ( h == nullptr || ( batch > 0 && ( context_ids == nullptr || slots == nullptr ) ) )
     return GH_ERR_INVALID;
-  const int rc = h->pool.acquire_batch( batch, context_ids, slots );
-  return rc == GH_OK ? rc : fail( h, rc, "not enough free context slots for the batch" );
+  return h->pool.acquire_batch( batch, context_ids, slots ); // status only, as above
 }
 
 int gh_slot_lookup( gh_attn_t h, uint32_t context_id, int32_t* slot )
@@ -678,10 +755,11 @@ int gh_attn_batch_begin( gh_attn_t h, uint64_t batch, const int32_t* slots, cons
   h->cur = -1;
   int entry;
   uint32_t n_items, n_split;
-  if ( const int rc = plan_and_upload( h, ctx, static_cast<cudaStream_t>( stream ), &entry, &n_items, &n_split );
+  if ( const int rc = plan_and_upload( h, ctx, static_cast<cudaStream_t>( stream ), &entry, &n_items, &n_split, RING_BATCH );
        rc != GH_OK )
     return rc;
   h->cur = entry;
+  h->cur_layer_ready.assign( h->sh.n_layers, 0 );
   h->cur_batch = static_cast<uint32_t>( batch );
   h->cur_items = n_items;
   h->cur_split = n_split;
@@ -898,6 +976,8 @@ int gh_attn_prefill_chunk( gh_attn_t h,
     return fail( h, GH_ERR_INVALID, "layer is not hosted" );
   if ( h->rope_cos == nullptr )
     return fail( h, GH_ERR_STATE, "RoPE tables not set" );
+  if ( const int rc = check_device_ok( h ); rc != GH_OK )
+    return rc;
   DeviceGuard guard( h->device );
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
 
@@ -947,13 +1027,9 @@ int gh_attn_prefill_chunk( gh_attn_t h,
 
   // 2a. tensor-core kernels: consecutive tokens of a context share one block per kv head, so they share every K/V
   //     fetch.  Work item = (context, token group), never cut.  The tcgen05 kernel packs
-  //     128 / group tokens into a block; the warp-level kernel in chunk mode packs 16 / group (kept for comparison
-  //     runs: GLINTHAWK_PREFILL=mma).
-  static const bool prefer_warp_mma = [] {
-    const char* e = std::getenv( "GLINTHAWK_PREFILL" );
-    return e != nullptr && std::string( e ) == "mma";
-  }();
-  const bool umma = h->use_mma && prefill_umma_supported( h->sh, h->cfg.dtype ) && !prefer_warp_mma;
+  //     128 / group tokens into a block; the warp-level kernel in chunk mode packs 16 / group (groups the tcgen05
+  //     kernel does not take).
+  const bool umma = h->use_mma && prefill_umma_supported( h->sh, h->cfg.dtype );
   CUtensorMap q_map {}, xb_map {};
   if ( umma ) {
     const DriverApi* api = driver_api( h->err );
@@ -1137,6 +1213,96 @@ int upload_ptrs( gh_attn* h, uint64_t batch, const void* const* ptrs, const uint
   return GH_OK;
 }
 
+// The reference hands its operations host arrays of row pointers (src/models/llama2/base.hh:197-202).  When every
+// non-null pointer names a row of this handle's own slots, all in one hosted layer, the call can run on the same
+// kernels and the same kind of batch description as gh_attn_append / gh_attn_decode, and nothing but the first call
+// of a step has to upload anything.  `token_rows`: the pointers are token rows (their position is part of the address;
+// it must agree with pos[] where that is given); otherwise they are layer bases and pos[] gives the positions.
+// Fills h->op_slots_tmp / op_pos_tmp and *layer; false = some pointer is foreign memory (or nothing is active).
+bool resolve_own_rows( gh_attn* h, uint64_t batch, const void* const* ptrs, const uint32_t* pos, bool token_rows,
+                       uint32_t* layer )
+{
+  const PoolGeometry& g = h->pool.geometry();
+  const char* arena = h->pool.arena();
+  const size_t arena_bytes = h->pool.arena_bytes();
+  h->op_slots_tmp.resize( batch );
+  h->op_pos_tmp.resize( batch );
+  long long the_layer = -1;
+  for ( uint64_t i = 0; i < batch; i++ ) {
+    if ( ptrs[i] == nullptr ) {
+      h->op_slots_tmp[i] = -1;
+      h->op_pos_tmp[i] = pos != nullptr ? pos[i] : 0;
+      continue;
+    }
+    const char* p = static_cast<const char*>( ptrs[i] );
+    if ( p < arena || p >= arena + arena_bytes )
+      return false;
+    const size_t off = static_cast<size_t>( p - arena );
+    const size_t slot = off / g.slot_stride, within = off % g.slot_stride;
+    if ( within >= g.slot_bytes )
+      return false;
+    const size_t l = within / g.layer_bytes, rem = within % g.layer_bytes;
+    if ( rem % g.row_bytes != 0 || ( the_layer >= 0 && static_cast<long long>( l ) != the_layer ) )
+      return false;
+    const uint32_t row = static_cast<uint32_t>( rem / g.row_bytes );
+    if ( token_rows ? ( pos != nullptr && pos[i] != row ) : ( row != 0 ) )
+      return false;
+    the_layer = static_cast<long long>( l );
+    h->op_slots_tmp[i] = static_cast<int32_t>( slot );
+    h->op_pos_tmp[i] = token_rows ? row : pos[i];
+  }
+  if ( the_layer < 0 )
+    return false;
+  *layer = static_cast<uint32_t>( the_layer );
+  return true;
+}
+
+// The uploaded description for (op_slots_tmp, op_pos_tmp): the one already on the device when they equal the last
+// call's, else a fresh plan and upload.
+int op_batch_entry( gh_attn* h, uint64_t batch, cudaStream_t st )
+{
+  if ( h->op_entry >= 0 && h->op_slots == h->op_slots_tmp && h->op_pos == h->op_pos_tmp )
+    return GH_OK;
+  h->op_entry = -1;
+  std::vector<CtxMeta> ctx( batch );
+  for ( uint64_t i = 0; i < batch; i++ ) {
+    ctx[i] = CtxMeta {};
+    ctx[i].pos = h->op_pos_tmp[i];
+    ctx[i].kv_off = h->op_slots_tmp[i] < 0 ? kInactive : h->pool.slot_offset( h->op_slots_tmp[i] );
+  }
+  int entry;
+  if ( const int rc = plan_and_upload( h, ctx, st, &entry, &h->op_items, &h->op_split, RING_OP ); rc != GH_OK )
+    return rc;
+  h->op_entry = entry;
+  h->op_slots.swap( h->op_slots_tmp );
+  h->op_pos.swap( h->op_pos_tmp );
+  return GH_OK;
+}
+
+// copy_kv_cache and / or apply_rope on rows of the handle's own slots: the append kernels driven by the shared
+// description, no pointer array on the device.
+int append_own_rows( gh_attn* h, uint64_t batch, uint32_t layer, void* q, const void* kv_new, const void* rope_cos,
+                     const void* rope_sin, cudaStream_t st )
+{
+  if ( const int rc = op_batch_entry( h, batch, st ); rc != GH_OK )
+    return rc;
+  AppendArgs a {};
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.batch = static_cast<uint32_t>( batch );
+  a.ctx = entry_ctx( h, h->ring[h->op_entry].dev );
+  a.arena = h->pool.arena();
+  a.layer_off = h->pool.layer_offset( layer );
+  a.q = q;
+  a.kv_new = kv_new;
+  a.rope_cos = rope_cos;
+  a.rope_sin = rope_sin;
+  a.dependent_launch = h->cfg.pipeline_steps != 0 ? 1u : 0u;
+  if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
+    return cuda_fail( h, "append kernel launch", e );
+  return ring_touch( h, h->op_entry, st );
+}
+
 ScoreArgs score_args( gh_attn* h, int entry, uint64_t batch, const void* q, void* att, void* xb )
 {
   ScoreArgs a {};
@@ -1161,6 +1327,10 @@ int gh_op_copy_kv_cache( gh_attn_t h, void* const* token_rows, const void* state
     return misaligned( h );
   DeviceGuard guard( h->device );
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  uint32_t layer;
+  if ( batch > 0 && batch <= h->cfg.max_batch && token_rows != nullptr
+       && resolve_own_rows( h, batch, const_cast<const void* const*>( token_rows ), nullptr, true, &layer ) )
+    return append_own_rows( h, batch, layer, nullptr, state_kv, nullptr, nullptr, st );
   int entry;
   if ( const int rc = upload_ptrs( h, batch, const_cast<const void* const*>( token_rows ), nullptr, st, &entry ); rc != GH_OK )
     return rc;
@@ -1194,6 +1364,10 @@ int gh_op_apply_rope( gh_attn_t h,
       return fail( h, GH_ERR_CAPACITY, "token position beyond the RoPE tables" );
   DeviceGuard guard( h->device );
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  uint32_t layer;
+  if ( batch > 0 && batch <= h->cfg.max_batch && token_rows != nullptr
+       && resolve_own_rows( h, batch, const_cast<const void* const*>( token_rows ), pos, true, &layer ) )
+    return append_own_rows( h, batch, layer, state_q, nullptr, freq_cis_real, freq_cis_imag, st );
   int entry;
   if ( const int rc = upload_ptrs( h, batch, const_cast<const void* const*>( token_rows ), pos, st, &entry ); rc != GH_OK )
     return rc;
@@ -1208,6 +1382,49 @@ int gh_op_apply_rope( gh_attn_t h,
   a.rope_sin = freq_cis_imag;
   if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
     return cuda_fail( h, "apply_rope launch", e );
+  return ring_touch( h, entry, st );
+}
+
+int gh_op_copy_kv_cache_apply_rope( gh_attn_t h,
+                                    uint64_t batch,
+                                    const uint32_t* pos,
+                                    const void* freq_cis_real,
+                                    const void* freq_cis_imag,
+                                    void* state_q,
+                                    void* const* token_rows,
+                                    const void* state_kv,
+                                    void* stream )
+{
+  if ( h == nullptr || pos == nullptr || freq_cis_real == nullptr || freq_cis_imag == nullptr || state_q == nullptr
+       || state_kv == nullptr )
+    return fail( h, GH_ERR_INVALID, "null argument" );
+  if ( !aligned16( state_q ) || !aligned16( state_kv ) || !aligned16( freq_cis_real ) || !aligned16( freq_cis_imag )
+       || ( batch <= h->cfg.max_batch && !rows_aligned16( token_rows, batch ) ) )
+    return misaligned( h );
+  for ( uint64_t i = 0; i < batch && i < h->cfg.max_batch; i++ )
+    if ( token_rows != nullptr && token_rows[i] != nullptr && pos[i] >= h->sh.seq_len )
+      return fail( h, GH_ERR_CAPACITY, "token position beyond the RoPE tables" );
+  DeviceGuard guard( h->device );
+  const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  uint32_t layer;
+  if ( batch > 0 && batch <= h->cfg.max_batch && token_rows != nullptr
+       && resolve_own_rows( h, batch, const_cast<const void* const*>( token_rows ), pos, true, &layer ) )
+    return append_own_rows( h, batch, layer, state_q, state_kv, freq_cis_real, freq_cis_imag, st );
+  int entry;
+  if ( const int rc = upload_ptrs( h, batch, const_cast<const void* const*>( token_rows ), pos, st, &entry ); rc != GH_OK )
+    return rc;
+  AppendArgs a {};
+  a.sh = h->sh;
+  a.dtype = h->cfg.dtype;
+  a.batch = static_cast<uint32_t>( batch );
+  a.token_rows = entry_ptrs( h, h->ring[entry].dev );
+  a.pos = entry_pos( h, h->ring[entry].dev );
+  a.q = state_q;
+  a.kv_new = state_kv;
+  a.rope_cos = freq_cis_real;
+  a.rope_sin = freq_cis_imag;
+  if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
+    return cuda_fail( h, "copy_kv_cache + apply_rope launch", e );
   return ring_touch( h, entry, st );
 }
 
@@ -1233,6 +1450,8 @@ int gh_op_project_append( gh_attn_t h,
   for ( uint64_t i = 0; i < batch && i < h->cfg.max_batch; i++ )
     if ( token_rows != nullptr && token_rows[i] != nullptr && pos[i] >= h->sh.seq_len )
       return fail( h, GH_ERR_CAPACITY, "token position beyond the RoPE tables" );
+  if ( const int rc = check_device_ok( h ); rc != GH_OK )
+    return rc;
   DeviceGuard guard( h->device );
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
   int entry;
@@ -1335,10 +1554,22 @@ int gh_op_attention_fused( gh_attn_t h,
     return fail( h, GH_ERR_INVALID, "null argument" );
   if ( const int rc = check_positions( h, batch, layer_bases, pos ); rc != GH_OK )
     return rc;
+  if ( const int rc = check_device_ok( h ); rc != GH_OK )
+    return rc;
   if ( !aligned16( query ) || !aligned16( xb ) || !rows_aligned16( const_cast<void* const*>( layer_bases ), batch ) )
     return misaligned( h );
   DeviceGuard guard( h->device );
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  uint32_t own_layer;
+  if ( resolve_own_rows( h, batch, layer_bases, pos, false, &own_layer ) ) {
+    // every layer of a step names the same slots and positions: one plan and one upload serve them all
+    if ( const int rc = op_batch_entry( h, batch, st ); rc != GH_OK )
+      return rc;
+    const DecodeArgs a = decode_args( h, h->op_entry, h->op_items, h->op_split, h->pool.layer_offset( own_layer ), query, xb );
+    if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
+      return rc;
+    return ring_touch( h, h->op_entry, st );
+  }
   const char* arena = h->pool.arena();
   const size_t row_bytes = h->pool.geometry().row_bytes;
   bool in_arena = true;

@@ -21,8 +21,6 @@
 // The path is HBM-bound: 512 B of K+V per (token, kv head) against 2 x 16 x 128 x 2 tensor flops.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a sticky error word and leaves.
-#include <cstdlib>
-
 #include "gh_kernels.cuh"
 #include "gh_merge.cuh"
 
@@ -386,9 +384,22 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       mbar_arrive( &bar_empty[s] );
   }
 
-  // ---- combine the four warps' states through shared memory (the ring is free once every warp is here)
-  asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
-  if ( !ok || *reinterpret_cast<volatile uint32_t*>( a.dev_error ) != 0 ) {
+  // ---- combine the warps' states through shared memory (the ring is free once every warp is here)
+  // The consumers meet at two more barriers below, so they must all stay or all leave: one thread reads the error
+  // word, and the barrier itself ORs every thread's verdict into one that is the same for the whole block.
+  uint32_t bad = ok ? 0u : 1u;
+  if ( threadIdx.x == 0 && *reinterpret_cast<volatile uint32_t*>( a.dev_error ) != 0 )
+    bad = 1u;
+  asm volatile( "{\n"
+                ".reg .pred p, q;\n"
+                "setp.ne.u32 p, %0, 0;\n"
+                "barrier.cta.red.or.pred q, 1, %1, p;\n"
+                "selp.u32 %0, 1, 0, q;\n"
+                "}\n"
+                : "+r"( bad )
+                : "n"( kConsumers )
+                : "memory" );
+  if ( bad ) {
     // A wait ran out somewhere in this block or another: give any copy still in flight time to land, then leave.
     __nanosleep( 1000000 );
     return;
@@ -472,33 +483,15 @@ cudaError_t launch_g( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t 
   return e;
 }
 
-// Kernel geometries that are built.  Variant 0 is the default (fastest measured on B200: four small blocks per SM
-// overlap one block's fill and drain with three others' streaming); the others exist for tuning runs
-// (environment variable GLINTHAWK_DECODE_VARIANT, read once).
+// The geometry that is built: four small blocks per SM overlap one block's fill and drain with three others'
+// streaming, the fastest of the geometries measured on B200 (64-token tiles with a 96 KiB ring and two blocks per
+// SM, 32-token tiles with 64 KiB and three blocks, and with 96 KiB and two blocks were all slower).
 using Geo0 = Geo<2, 3, 4>; // 32-token tiles, 48 KiB ring, 4 blocks per SM
-using Geo1 = Geo<4, 3, 2>; // 64-token tiles, 96 KiB ring, 2 blocks per SM
-using Geo2 = Geo<2, 4, 3>; // 32-token tiles, 64 KiB ring, 3 blocks per SM
-using Geo3 = Geo<2, 6, 2>; // 32-token tiles, 96 KiB ring, 2 blocks per SM
-
-int variant()
-{
-  static const int v = [] {
-    const char* e = std::getenv( "GLINTHAWK_DECODE_VARIANT" );
-    const int x = e != nullptr ? std::atoi( e ) : 0;
-    return ( x >= 0 && x <= 3 ) ? x : 0;
-  }();
-  return v;
-}
 
 template<typename T>
 cudaError_t launch_t( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t st )
 {
-  switch ( variant() ) {
-    case 1: return launch_g<T, Geo1>( a, map, st );
-    case 2: return launch_g<T, Geo2>( a, map, st );
-    case 3: return launch_g<T, Geo3>( a, map, st );
-    default: return launch_g<T, Geo0>( a, map, st );
-  }
+  return launch_g<T, Geo0>( a, map, st );
 }
 
 template<typename T, bool G16, typename G>
@@ -550,14 +543,7 @@ bool decode_mma_chunk_supported( const Shape& sh )
 
 cudaError_t decode_mma_prepare()
 {
-  cudaError_t e = allow_smem_all<Geo0>();
-  if ( e == cudaSuccess )
-    e = allow_smem_all<Geo1>();
-  if ( e == cudaSuccess )
-    e = allow_smem_all<Geo2>();
-  if ( e == cudaSuccess )
-    e = allow_smem_all<Geo3>();
-  return e;
+  return allow_smem_all<Geo0>();
 }
 
 cudaError_t launch_decode_mma( const DecodeArgs& a, const CUtensorMap* kv_map, cudaStream_t st, uint64_t* launches )

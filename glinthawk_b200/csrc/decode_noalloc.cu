@@ -17,6 +17,8 @@
 //     message from gh_decode_noalloc_error().
 //   * The first call on each device looks up the device address of the array.  Make that first call during
 //     set-up, before any stream capture begins on that device.
+//   * Do not call it while `stream` is being captured: the batch description is uploaded from arrays on the
+//     caller's stack, which are gone when the call returns.  Such a call is refused with GH_ERR_STATE.
 //   * All calls on a device share the one array, which still holds whatever the previous call left there.
 //     Nothing in it has to start at zero: the batch description is uploaded on `stream` before the launch, and
 //     every partial record that is read was written earlier in the same call.  Two calls whose kernels could
@@ -297,6 +299,13 @@ int gh_decode_noalloc( const gh_noalloc_shape* shape,
     return rc;
 
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if ( cudaStreamIsCapturing( st, &capturing ) != cudaSuccess )
+    (void)cudaGetLastError();
+  else if ( capturing != cudaStreamCaptureStatusNone ) {
+    std::snprintf( g_error, sizeof( g_error ), "called during stream capture: the batch description is uploaded from the stack" );
+    return GH_ERR_STATE;
+  }
   cudaError_t e = cudaMemcpyAsync( scratch + kOffCtx, ctx, sizeof( CtxMeta ) * batch, cudaMemcpyHostToDevice, st );
   if ( e == cudaSuccess )
     e = cudaMemcpyAsync( scratch + kOffItems, items, sizeof( WorkItem ) * n_items, cudaMemcpyHostToDevice, st );

@@ -118,7 +118,7 @@ void KvPool::destroy()
     const DriverApi* api = driver_api( err );
     if ( api != nullptr ) {
       for ( int32_t s = 0; s < static_cast<int32_t>( slots_.size() ); s++ )
-        reset_slot( s, err );
+        reset_slot_locked( s, err );
       for ( auto h : free_pages_ )
         api->MemRelease( h );
       free_pages_.clear();
@@ -133,6 +133,36 @@ void KvPool::destroy()
 // ---- id -> slot map -------------------------------------------------------------------------------------
 
 int KvPool::acquire( uint32_t context_id, int32_t* slot )
+{
+  std::lock_guard<std::mutex> lock( mu_ );
+  return acquire_locked( context_id, slot );
+}
+
+uint32_t KvPool::slots_free() const
+{
+  std::lock_guard<std::mutex> lock( mu_ );
+  return static_cast<uint32_t>( free_slots_.size() );
+}
+
+uint32_t KvPool::slots_allocated() const
+{
+  std::lock_guard<std::mutex> lock( mu_ );
+  return static_cast<uint32_t>( id2slot_.size() );
+}
+
+uint64_t KvPool::bytes_mapped() const
+{
+  std::lock_guard<std::mutex> lock( mu_ );
+  return bytes_mapped_;
+}
+
+uint64_t KvPool::reset_generation() const
+{
+  std::lock_guard<std::mutex> lock( mu_ );
+  return reset_generation_;
+}
+
+int KvPool::acquire_locked( uint32_t context_id, int32_t* slot )
 {
   if ( context_id == 0 ) { // NULL_CONTEXT: the empty context
     *slot = -1;
@@ -154,6 +184,7 @@ int KvPool::acquire( uint32_t context_id, int32_t* slot )
 
 int KvPool::acquire_batch( uint64_t n, const uint32_t* ids, int32_t* slots )
 {
+  std::lock_guard<std::mutex> lock( mu_ );
   // First make sure every prompt of the batch can be served; bind nothing otherwise.
   size_t need = 0;
   std::vector<uint32_t> fresh;
@@ -167,7 +198,7 @@ int KvPool::acquire_batch( uint64_t n, const uint32_t* ids, int32_t* slots )
   if ( need > free_slots_.size() )
     return GH_ERR_NO_SLOT;
   for ( uint64_t i = 0; i < n; i++ ) {
-    const int rc = acquire( ids[i], &slots[i] );
+    const int rc = acquire_locked( ids[i], &slots[i] );
     if ( rc != GH_OK )
       return rc;
   }
@@ -176,6 +207,7 @@ int KvPool::acquire_batch( uint64_t n, const uint32_t* ids, int32_t* slots )
 
 int KvPool::lookup( uint32_t context_id, int32_t* slot ) const
 {
+  std::lock_guard<std::mutex> lock( mu_ );
   const auto it = id2slot_.find( context_id );
   if ( it == id2slot_.end() )
     return GH_ERR_NOT_FOUND;
@@ -185,6 +217,7 @@ int KvPool::lookup( uint32_t context_id, int32_t* slot ) const
 
 int KvPool::release( uint32_t context_id, std::string& err )
 {
+  std::lock_guard<std::mutex> lock( mu_ );
   const auto it = id2slot_.find( context_id );
   if ( it == id2slot_.end() )
     return GH_ERR_NOT_FOUND;
@@ -192,15 +225,22 @@ int KvPool::release( uint32_t context_id, std::string& err )
   id2slot_.erase( it );
   slot_owner_[slot] = 0;
   free_slots_.push_back( slot );
-  return reset_slot( slot, err );
+  return reset_slot_locked( slot, err );
 }
 
 // ---- storage --------------------------------------------------------------------------------------------
 
 int KvPool::reset_slot( int32_t slot, std::string& err )
 {
+  std::lock_guard<std::mutex> lock( mu_ );
+  return reset_slot_locked( slot, err );
+}
+
+int KvPool::reset_slot_locked( int32_t slot, std::string& err )
+{
   if ( !valid_slot( slot ) )
     return GH_ERR_INVALID;
+  reset_generation_++;
   if ( !paged_ )
     return GH_OK;
   const DriverApi* api = driver_api( err );
@@ -281,6 +321,27 @@ int KvPool::commit( int32_t slot, size_t begin, size_t end, std::string& err )
 
 int KvPool::prepare( int32_t slot, uint32_t layer, uint32_t pos, bool can_release, std::string& err )
 {
+  std::lock_guard<std::mutex> lock( mu_ );
+  return prepare_locked( slot, layer, pos, can_release, err );
+}
+
+int KvPool::prepare_batch( uint64_t n, const int32_t* slots, const uint32_t* pos, uint32_t layer, std::string& err )
+{
+  if ( !paged_ )
+    return GH_OK;
+  std::lock_guard<std::mutex> lock( mu_ );
+  for ( uint64_t i = 0; i < n; i++ ) {
+    if ( slots[i] < 0 )
+      continue;
+    const int rc = prepare_locked( slots[i], layer, pos[i], false, err );
+    if ( rc != GH_OK )
+      return rc;
+  }
+  return GH_OK;
+}
+
+int KvPool::prepare_locked( int32_t slot, uint32_t layer, uint32_t pos, bool can_release, std::string& err )
+{
   if ( !valid_slot( slot ) || layer >= geo_.n_layers )
     return GH_ERR_INVALID;
   if ( pos >= geo_.seq_len )
@@ -288,7 +349,7 @@ int KvPool::prepare( int32_t slot, uint32_t layer, uint32_t pos, bool can_releas
   if ( !paged_ )
     return GH_OK;
   if ( can_release ) {
-    const int rc = reset_slot( slot, err );
+    const int rc = reset_slot_locked( slot, err );
     if ( rc != GH_OK )
       return rc;
   }

@@ -19,6 +19,7 @@
 
 #include <cstdint>
 #include <deque>
+#include <mutex>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -48,18 +49,26 @@ public:
   int init( const PoolGeometry& g, bool paged, int device, uint64_t page_budget, uint32_t tile_rows, std::string& err );
   void destroy();
 
+  // Every public member below takes the pool's mutex, as the reference's context manager does around its map
+  // (src/compute/contextman.hh:82, 108, 134, 184): a bookkeeping thread may bind and look up contexts while the
+  // execution thread prepares rows and launches kernels.
+
   // ---- id -> slot map ----
   int acquire( uint32_t context_id, int32_t* slot );
   int acquire_batch( uint64_t n, const uint32_t* ids, int32_t* slots );
   int lookup( uint32_t context_id, int32_t* slot ) const;
   int release( uint32_t context_id, std::string& err );
-  uint32_t slots_free() const { return static_cast<uint32_t>( free_slots_.size() ); }
-  uint32_t slots_allocated() const { return static_cast<uint32_t>( id2slot_.size() ); }
+  uint32_t slots_free() const;
+  uint32_t slots_allocated() const;
 
   // ---- storage ----
   // make rows [0, pos] of (slot, layer) usable (rounded up to the tile the kernels read)
   int prepare( int32_t slot, uint32_t layer, uint32_t pos, bool can_release, std::string& err );
+  // the same for a whole batch under one lock; slots[i] < 0 = inactive prompt
+  int prepare_batch( uint64_t n, const int32_t* slots, const uint32_t* pos, uint32_t layer, std::string& err );
   int reset_slot( int32_t slot, std::string& err );
+  // Counts the slot resets so far: rows that were prepared before a reset may be gone after it.
+  uint64_t reset_generation() const;
   bool valid_slot( int32_t slot ) const { return slot >= 0 && static_cast<uint32_t>( slot ) < geo_.max_contexts; }
 
   char* arena() const { return reinterpret_cast<char*>( arena_ ); }
@@ -67,7 +76,7 @@ public:
   long long slot_offset( int32_t slot ) const { return static_cast<long long>( slot ) * geo_.slot_stride; }
   long long layer_offset( uint32_t layer ) const { return static_cast<long long>( layer ) * geo_.layer_bytes; }
   const PoolGeometry& geometry() const { return geo_; }
-  uint64_t bytes_mapped() const { return bytes_mapped_; }
+  uint64_t bytes_mapped() const;
   bool paged() const { return paged_; }
 
 private:
@@ -84,7 +93,13 @@ private:
     std::vector<Mapping> mappings;
   };
 
+  int acquire_locked( uint32_t context_id, int32_t* slot );
+  int prepare_locked( int32_t slot, uint32_t layer, uint32_t pos, bool can_release, std::string& err );
+  int reset_slot_locked( int32_t slot, std::string& err );
   int commit( int32_t slot, size_t begin, size_t end, std::string& err );
+
+  mutable std::mutex mu_;
+  uint64_t reset_generation_ = 0;
 
   PoolGeometry geo_ {};
   bool paged_ = false;

@@ -92,23 +92,6 @@ __device__ __forceinline__ uint64_t desc_mnmajor( uint32_t saddr )
 }
 
 
-// Developer aid, compiled out unless GH_PREFILL_TRACE is defined: the three roles of one chosen block record
-// (clock, tag) pairs, read back with gh_debug_prefill_trace().
-#ifdef GH_PREFILL_TRACE
-__device__ unsigned long long g_trace[3][1024];
-__device__ int g_trace_block = 0;
-#define GH_TRACE_DECL int trace_n = 0
-#define GH_TRACE( role, tag )                                                                                          \
-  do {                                                                                                                 \
-    if ( (int)blockIdx.x == g_trace_block && trace_n < 1023 ) {                                                       \
-      g_trace[role][trace_n++] = ( static_cast<unsigned long long>( clock64() ) << 8 ) | ( tag );                      \
-      g_trace[role][trace_n] = 0;                                                                                      \
-    }                                                                                                                  \
-  } while ( 0 )
-#else
-#define GH_TRACE_DECL
-#define GH_TRACE( role, tag )
-#endif
 
 // One work item = (context, query block): `split` is the query block's index, t_end the number of keys its last
 // token sees.  Warps 0..3: thread r owns row r = (token r / group, head r % group) of the query block and does its
@@ -212,21 +195,17 @@ __global__ void __launch_bounds__( kThreads, 2 )
   if ( warp == 4 ) {
     // =========================== TMA lane: the remaining K/V tiles, as their stages fall free ===========================
     if ( r == 4 * 32 ) {
-      GH_TRACE_DECL;
-      GH_TRACE( 1, 2 );
       // in the order the MMA lane needs them: K(t+2) once S(t) has completed, V(t+1) once P.V(t-1) has
       bool ok = true;
       for ( int t = 0; t < n_tiles && ok; t++ ) {
         if ( t + 2 < n_tiles ) {
           ok = mbar_wait( &bar_kfree[t & 1], ( t >> 1 ) & 1, fail );
-          GH_TRACE( 1, 3 );
           if ( ok )
             load_k( t + 2 );
         }
         if ( ok && t + 1 < n_tiles ) {
           if ( t >= 1 )
             ok = mbar_wait( &bar_vfree[( t + 1 ) & 1], ( ( t - 1 ) >> 1 ) & 1, fail );
-          GH_TRACE( 1, 4 );
           if ( ok )
             load_v( t + 1 );
         }
@@ -254,12 +233,8 @@ __global__ void __launch_bounds__( kThreads, 2 )
         umma_commit( &bar_s[b] );
         umma_commit( &bar_kfree[b] );
       };
-      GH_TRACE_DECL;
-      GH_TRACE( 2, 1 );
       bool ok = mbar_wait( bar_q, 0, fail );
-      GH_TRACE( 2, 2 );
       ok = ok && mbar_wait( &bar_k[0], 0, fail );
-      GH_TRACE( 2, 3 );
       if ( ok ) {
         asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
         issue_s( 0 );
@@ -272,14 +247,10 @@ __global__ void __launch_bounds__( kThreads, 2 )
           ok = mbar_wait( &bar_k[b ^ 1], ( ( t + 1 ) >> 1 ) & 1, fail );
           if ( !ok )
             break;
-          GH_TRACE( 2, 4 );
           issue_s( t + 1 );
-          GH_TRACE( 2, 5 );
         }
         ok = mbar_wait( bar_p, t & 1, fail );
-        GH_TRACE( 2, 6 );
         ok = ok && mbar_wait( &bar_v[b], ( t >> 1 ) & 1, fail );
-        GH_TRACE( 2, 7 );
         if ( !ok )
           break;
         asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
@@ -290,7 +261,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
         }
         umma_commit( bar_pv );
         umma_commit( &bar_vfree[b] );
-        GH_TRACE( 2, 8 );
       }
       if ( !ok )
         *fail = 1;
@@ -301,12 +271,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
     const bool row_live = row_tok < n_tok;
     const int row_limit = row_live ? n_keys - ( n_tok - 1 - row_tok ) : 0; // keys seen by this row's token
     const float scale_log2 = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
-    GH_TRACE_DECL;
-#define GH_TRACE0( tag )                                                                                               \
-  if ( r == 0 )                                                                                                        \
-  GH_TRACE( 0, tag )
-    GH_TRACE0( 1 );
-
     const uint32_t lane_off = static_cast<uint32_t>( warp * 32 ) << 16; // this warp's quarter of the TMEM lanes
     const uint32_t tmem_s = tmem_base + lane_off;                       // + 64 for the second buffer
     const uint32_t tmem_o = tmem_base + lane_off + 128;
@@ -322,7 +286,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
       if ( !ok )
         break;
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
-      GH_TRACE0( 3 );
 
       // ---- scores of this thread's row; tcgen05.ld is warp-wide, so whether to load a column block is decided per
       //      warp
@@ -337,7 +300,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
         for ( int j = 0; j < 64; j++ )
           sc[j] = 0.f;
       }
-      GH_TRACE0( 4 );
       float tmax = -INFINITY;
       if ( full_tile ) {
 #pragma unroll
@@ -392,7 +354,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
         }
       }
 
-      GH_TRACE0( 5 );
       // ---- O may be rescaled once the previous tile's P.V has completed
       if ( t > 0 && warp_grow ) {
         ok = __all_sync( kFull, mbar_wait( bar_pv, ( t - 1 ) & 1, fail ) );
@@ -409,7 +370,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
           tmem_st32( tmem_o + cb * 32, o );
         }
       }
-      GH_TRACE0( 6 );
       // ---- P replaces S in tensor memory: 64 keys of 16 bits = the first 32 columns of this tile's S buffer, from
       //      where the P.V MMAs take it as their A operand.  (Tile 0 has nothing to rescale: its first MMA
       //      overwrites O.)
@@ -432,13 +392,11 @@ __global__ void __launch_bounds__( kThreads, 2 )
       asm volatile( "fence.proxy.async.shared::cta;" ::: "memory" ); // the cleared V rows -> tensor-core proxy
       asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
       asm volatile( "mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"( smem_u32( bar_p ) ) : "memory" );
-      GH_TRACE0( 7 );
     }
 
     // ---- epilogue: O / l -> xb
     if ( ok )
       ok = __all_sync( kFull, mbar_wait( bar_pv, ( n_tiles - 1 ) & 1, fail ) );
-    GH_TRACE0( 8 );
     if ( ok ) {
       asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
       // O / l goes through the Q block's shared memory (free since the last S completed), in the same row-major
@@ -469,7 +427,6 @@ __global__ void __launch_bounds__( kThreads, 2 )
     } else {
       *fail = 1;
     }
-    GH_TRACE0( 9 );
   }
 
   asm volatile( "tcgen05.fence::before_thread_sync;" ::: "memory" );
@@ -538,15 +495,3 @@ cudaError_t launch_prefill_umma( const DecodeArgs& a, const CUtensorMap* kv_map,
 
 } // namespace gh
 
-#ifdef GH_PREFILL_TRACE
-// out: 3 x 1024 words of (clock << 8 | tag), zero-terminated per role; block = the block to trace next
-extern "C" int gh_debug_prefill_trace( unsigned long long* out, int block )
-{
-  cudaError_t e = cudaDeviceSynchronize();
-  if ( e == cudaSuccess )
-    e = cudaMemcpyFromSymbol( out, gh::g_trace, sizeof( gh::g_trace ) );
-  if ( e == cudaSuccess )
-    e = cudaMemcpyToSymbol( gh::g_trace_block, &block, sizeof( int ) );
-  return static_cast<int>( e );
-}
-#endif

@@ -345,7 +345,10 @@ __global__ void __launch_bounds__( 256, 4 ) project_finish_kernel( const Project
 #pragma unroll
   for ( int k = 0; k < kFinishRows / 4; k++ ) {
     const int i = blockIdx.y * kFinishRows + sub + 4 * k;
-    if ( rotate && i < batch ) {
+    // An inactive prompt's position is not checked by the host (it may be any value): its q is don't-care and its
+    // K goes nowhere, so nothing of the tables is read for it.
+    cs[k] = 1.f, sn[k] = 0.f;
+    if ( rotate && i < batch && row[k] != nullptr ) {
       const size_t ti = (size_t)pos[k] * ( hs / 2 ) + d2;
       cs[k] = Conv<T>::to_f32( __ldg( cos_t + ti ) );
       sn[k] = Conv<T>::to_f32( __ldg( sin_t + ti ) );

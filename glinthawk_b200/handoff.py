@@ -5,7 +5,9 @@ that ran the dense pre-attention stage, and returns the attention output to the 
 stage; the tensors travel as a serialized ``BatchedInferenceState`` over TCP, through host memory on both sides
 (src/worker/worker.hh:728-757, src/models/common/state.hh:561-594, src/models/llama2/model.hh:632-722).  Here the
 same three tensors move device to device with ``torch.distributed`` P2P operations; the attention path itself still
-has no collective.  The classes work on any backend, so the protocol is tested with gloo on CPU ranks.
+has no collective.  What the attention side runs on the tensors once they are on its GPU is ``gh_attn_step``, the
+device-buffer form of ``Llama2::forward_attention``.  The classes work on any backend, so the protocol is tested with
+gloo on CPU ranks; ``bench.py`` times it on pairs of GPUs.
 """
 from __future__ import annotations
 
@@ -53,6 +55,44 @@ class AttentionLink:
         return dist.batch_isend_irecv([dist.P2POp(dist.isend, xb, self.peer)])
 
 
+@dataclass
+class LayerLink:
+    """A pair's two directions as process groups of their own (each gets its own NCCL communicator and stream):
+    `inputs` carries q and the new K/V rows to the attention side, `outputs` carries xb back.  Traffic of one direction
+    never queues behind traffic of the other, so the inputs of later layers arrive while earlier layers compute."""
+    peer: int
+    inputs: object
+    outputs: object
+
+
+def attention_side_step(link: LayerLink, n_layers: int, q_all, kv_all, xb_all, step_layer) -> None:
+    """Attention side of one decode step over all layers.  The receives of every layer's q / K,V rows are posted up
+    front, in layer order (the order the dense side sends them in); layer l's kernels are enqueued once its inputs
+    are in (`step_layer(l)` reads q_all[l], kv_all[l] and writes xb_all[l] on the current stream), and xb_all[l] goes
+    back while layer l+1 computes.  On NCCL a wait only orders streams; the host runs ahead."""
+    recvs = [dist.batch_isend_irecv([dist.P2POp(dist.irecv, q_all[l], link.peer, group=link.inputs),
+                                     dist.P2POp(dist.irecv, kv_all[l], link.peer, group=link.inputs)])
+             for l in range(n_layers)]
+    sends = []
+    for l in range(n_layers):
+        wait_all(recvs[l])
+        step_layer(l)
+        sends.append(dist.isend(xb_all[l], link.peer, group=link.outputs))
+    wait_all(sends)
+
+
+def dense_side_step(link: LayerLink, n_layers: int, q_all, kv_all, xb_rx) -> None:
+    """Dense-stage side, mirroring attention_side_step: every layer's inputs go out in layer order, every layer's xb
+    is received into xb_rx[l] in layer order."""
+    sends = [dist.batch_isend_irecv([dist.P2POp(dist.isend, q_all[l], link.peer, group=link.inputs),
+                                     dist.P2POp(dist.isend, kv_all[l], link.peer, group=link.inputs)])
+             for l in range(n_layers)]
+    recvs = [dist.irecv(xb_rx[l], link.peer, group=link.outputs) for l in range(n_layers)]
+    for s_ in sends:
+        wait_all(s_)
+    wait_all(recvs)
+
+
 def wait_all(reqs) -> None:
     for r in reqs:
         r.wait()
@@ -90,93 +130,3 @@ def run_dense_rank(link: AttentionLink, n_layers: int, make_inputs, consume_outp
         wait_all(dist.batch_isend_irecv(ops))
         if g >= 1:
             consume_output(g - 1, xb)
-
-
-def main() -> None:
-    """Two ranks, one GPU each (launch with torch.distributed.run): rank 0 plays the dense stages, rank 1 owns the
-    contexts and runs the attention stage; q / new K,V rows / xb cross NVLink once per layer.  Prints one JSON line
-    with the step time, and checks the returned xb against the attention rank's own copy."""
-    import argparse
-    import json
-    import os
-
-    import numpy as np
-
-    from .rope import rope_tables
-    from .stage import AttentionStage
-    from .workload import WORKLOADS
-
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="llama2_70b_gqa")
-    ap.add_argument("--layers", type=int, default=8)
-    ap.add_argument("--steps", type=int, default=5)
-    args = ap.parse_args()
-
-    rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    from datetime import timedelta
-
-    dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=60))  # fail fast, never hang
-    wl = WORKLOADS[args.workload]
-    sh = wl.shape
-    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[wl.dtype]
-    B, L = wl.batch, args.layers
-    shapes = StageShapes(B, sh.dim, 2 * sh.kv_dim, tdt, dev)
-    link = AttentionLink(1 - rank, shapes)
-    gen = torch.Generator(device=dev).manual_seed(1234)
-    q_all = torch.randn((L, B, sh.dim), device=dev, generator=gen).to(tdt)
-    kv_all = torch.randn((L, B, 2 * sh.kv_dim), device=dev, generator=gen).to(tdt)  # same seed on both ranks
-    times = []
-    if rank == 1:
-        lens = wl.lengths(7, args.steps + 2)
-        stage = AttentionStage(sh, tdt, n_layers_hosted=L, max_batch=B, max_contexts=B, paged=True, device=local)
-        cos, sin = rope_tables(sh.head_size, sh.seq_len, sh.rope_theta)
-        stage.set_rope_tables(torch.from_numpy(cos).to(dev).to(tdt), torch.from_numpy(sin).to(dev).to(tdt))
-        slots = stage.get_contexts(np.arange(1, B + 1, dtype=np.uint32))
-        for i in range(B):
-            for l in range(L):
-                stage.prepare(int(slots[i]), l, int(lens[i]) + args.steps)
-                stage.fill_normal(stage.layer_ptr(int(slots[i]), l), int(lens[i]) * 2 * sh.kv_dim, tdt, 5,
-                                  offset=(i * L + l) * sh.seq_len * 2 * sh.kv_dim)
-        pos = lens.astype(np.uint32)
-        outs = {}
-
-        def step_fn(layer, q, kv):
-            xb = torch.empty_like(q)
-            stage.step(layer, q, kv, xb)
-            outs[layer] = xb
-            return xb
-
-    for step in range(args.steps):
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        if rank == 1:
-            stage.batch_begin(slots, pos)
-            run_attention_rank(link, L, step_fn)
-            pos += 1
-        else:
-            got = {}
-            run_dense_rank(link, L, lambda l: (q_all[l].clone(), kv_all[l]), lambda l, xb: got.__setitem__(l, xb))
-        e1.record()
-        torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
-    # verification: the attention rank sends its last step's outputs once more through a plain collective
-    check = torch.zeros((L, B, sh.dim), dtype=tdt, device=dev)
-    if rank == 1:
-        check = torch.stack([outs[l] for l in range(L)])
-    dist.broadcast(check, src=1)
-    if rank == 0:
-        same = all(torch.equal(got[l], check[l]) for l in range(L))
-        per_layer = (B * sh.dim * 2 + B * 2 * sh.kv_dim) * q_all.element_size()
-        print(json.dumps({"mode": "stage hand-off over NCCL P2P", "workload": wl.name, "layers": L, "contexts": B,
-                          "ms_per_step": min(times), "ms_per_layer": min(times) / L, "handoff_bytes_per_layer": per_layer,
-                          "outputs_identical": bool(same)}))
-    dist.barrier()
-    dist.destroy_process_group()
-
-
-if __name__ == "__main__":
-    main()

@@ -104,6 +104,13 @@ class AttentionStage:
         self._ck(lib.gh_attn_get_stats(self._h, C.byref(s)))
         return s
 
+    def synchronize(self, stream=None) -> None:
+        """Waits for `stream`; raises when a kernel of this stage has reported a timed-out wait."""
+        self._ck(lib.gh_attn_synchronize(self._h, _stream(stream)))
+
+    def clear_device_error(self) -> None:
+        self._ck(lib.gh_attn_clear_device_error(self._h))
+
     def set_rope_tables(self, freq_cis_real: torch.Tensor, freq_cis_imag: torch.Tensor) -> None:
         assert freq_cis_real.dtype == self.torch_dtype and freq_cis_imag.dtype == self.torch_dtype
         self._rope = (freq_cis_real.contiguous(), freq_cis_imag.contiguous())  # keep them alive
@@ -209,6 +216,14 @@ class AttentionStage:
         pos = np.ascontiguousarray(token_positions, dtype=np.uint32)
         self._ck(lib.gh_op_apply_rope(self._h, batch_size, _ptr(pos), _ptr(freq_cis_real), _ptr(freq_cis_imag),
                                       _ptr(state_q), _ptr(rows), _stream(stream)))
+
+    def copy_kv_cache_apply_rope(self, batch_size: int, token_positions, freq_cis_real, freq_cis_imag, state_q,
+                                 token_contexts, state_kv, stream=None) -> None:
+        """copy_kv_cache then apply_rope on the same rows, as one launch."""
+        rows = self._ptr_array(token_contexts)
+        pos = np.ascontiguousarray(token_positions, dtype=np.uint32)
+        self._ck(lib.gh_op_copy_kv_cache_apply_rope(self._h, batch_size, _ptr(pos), _ptr(freq_cis_real), _ptr(freq_cis_imag),
+                                                    _ptr(state_q), _ptr(rows), _ptr(state_kv), _stream(stream)))
 
     def pre_attention_rope_append(self, batch_size: int, x, rms_att_weight, wq, wkv, state_q, token_positions,
                                   freq_cis_real, freq_cis_imag, token_contexts, stream=None) -> None:

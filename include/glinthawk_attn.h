@@ -15,7 +15,11 @@
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  All compute calls are
  *     asynchronous with respect to the host unless stated otherwise.
  *   - A handle is used by one host thread at a time (the reference calls its operations from one execution
- *     thread per model instance, src/compute/kernel.hh:103-136).
+ *     thread per model instance, src/compute/kernel.hh:103-136), with one exception that the reference has too
+ *     (src/compute/kernel.hh:139-170 looks contexts up on a bookkeeping thread, under the context manager's mutex,
+ *     src/compute/contextman.hh:82-184): gh_slot_acquire, gh_slots_acquire_batch and gh_slot_lookup may be called
+ *     from another thread while the owning thread submits work.  Those three report through their status code only
+ *     and never change the text gh_attn_last_error returns.
  */
 #ifndef GLINTHAWK_ATTN_H
 #define GLINTHAWK_ATTN_H
@@ -108,6 +112,9 @@ typedef struct gh_attn_stats
   uint32_t last_chunk;      /* split length used by the most recent batch */
   uint32_t last_kernel;     /* 0 = CUDA-core decode kernel, 1 = TMA + warp tensor-core kernel, 2 = tcgen05 prefill kernel */
   uint32_t device_error;    /* sticky flag written by kernels whose bounded waits ran out */
+  uint32_t last_split_contexts; /* contexts of the most recent batch that were cut into several work items */
+  uint32_t pad;
+  uint64_t batch_plans;     /* batch descriptions planned and uploaded since creation */
 } gh_attn_stats;
 
 /* ---- lifetime ------------------------------------------------------------------------------------- */
@@ -123,8 +130,16 @@ int gh_attn_get_stats( gh_attn_t h, gh_attn_stats* out );
 
 /* Blocks the host until everything submitted to `stream` has finished (cudaStreamSynchronize).  For callers whose
  * other operations run on the host and are therefore not ordered by the stream; the reference's CUDA backend gets
- * the same effect from its blocking cudaMemcpy calls (src/arch/cuda/llama2/ops.cuh:455-492). */
+ * the same effect from its blocking cudaMemcpy calls (src/arch/cuda/llama2/ops.cuh:455-492).  Returns GH_ERR_CUDA
+ * when a kernel of this handle has reported a timed-out wait (see gh_attn_clear_device_error). */
 int gh_attn_synchronize( gh_attn_t h, void* stream );
+
+/* Every wait inside the kernels is bounded.  A kernel whose wait ran out raises gh_attn_stats.device_error and skips
+ * its stores, so the outputs of that launch (and of launches that were already queued behind it) are not valid.
+ * Once the host has seen the flag (gh_attn_synchronize or gh_attn_get_stats) every compute entry point of the handle
+ * returns GH_ERR_CUDA until this call: it waits for the device to drain and clears the flag.  No reference
+ * counterpart (the reference aborts the process on any CUDA error, src/arch/cuda/common/ops.cu:5-19). */
+int gh_attn_clear_device_error( gh_attn_t h );
 
 /* RoPE tables [seq_len][head_size/2] of the handle's dtype, device pointers, not owned.  They are what
  * `apply_rope` receives as freq_cis_real / freq_cis_imag (src/models/llama2/base.hh:110-112). */
@@ -139,13 +154,16 @@ int gh_slot_acquire( gh_attn_t h, uint32_t context_id, int32_t* slot );
 int gh_slots_acquire_batch( gh_attn_t h, uint64_t batch, const uint32_t* context_ids, int32_t* slots );
 int gh_slot_lookup( gh_attn_t h, uint32_t context_id, int32_t* slot );
 /* release_context (contextman.hh:180-196; fatal in the reference, supported here): unbinds the id and, for
- * PAGED backing, returns the slot's pages to the pool. */
+ * PAGED backing, unmaps the slot's pages at once and returns them to the pool.  Every kernel that reads or writes
+ * the slot must have FINISHED (not merely been submitted) before this call: synchronize the streams that carry
+ * them first, e.g. with gh_attn_synchronize.  Call it from the thread that owns the handle. */
 int gh_slot_release( gh_attn_t h, uint32_t context_id );
 
 /* ---- context views: Context / LayerContext / TokenContext (src/models/llama2/context.hh:61-190) ---- */
 
 /* Context::prepare( layer, token_pos, can_release ) (context.hh:164-169, 221-248): make sure the slot can
- * hold token `pos` of hosted layer `layer`; can_release drops what the slot held before. */
+ * hold token `pos` of hosted layer `layer`; can_release drops what the slot held before (its pages are unmapped
+ * at once, so, as for gh_slot_release, all work on the slot must have finished). */
 int gh_slot_prepare( gh_attn_t h, int32_t slot, uint32_t layer, uint32_t pos, int can_release );
 /* Context::layer( l ) -> LayerContext (context.hh:171): device pointer of the layer's first token row. */
 int gh_slot_layer_ptr( gh_attn_t h, int32_t slot, uint32_t layer, void** ptr );
@@ -241,7 +259,11 @@ int gh_attn_forward_attention_host( gh_attn_t h,
 /* `token_rows` / `layer_bases` are HOST arrays of device pointers (what TokenContext::key() and
  * LayerContext::token(0).key() return); a null entry means "inactive, skip" (ops.hh:195,250,314,344).
  * `pos` is a host array.  These materialise the score matrix `att` [batch][n_heads][seq_len] exactly as the
- * reference does and round where it rounds. */
+ * reference does and round where it rounds.
+ * When the pointers name rows of the handle's own slots (what the adapter's Context hands out), copy_kv_cache,
+ * apply_rope and the fused attention call run on the kernels of gh_attn_append / gh_attn_decode, and the batch
+ * description they share is planned and uploaded once per step, by the first call that names new slots or positions;
+ * pointers into other device memory take a slower path that uploads the pointer array with every call. */
 
 /* copy_kv_cache( token_contexts[], state_kv, batch ) — src/arch/cuda/llama2/ops.cuh:435-453. */
 int gh_op_copy_kv_cache( gh_attn_t h, void* const* token_rows, const void* state_kv, uint64_t batch, void* stream );
@@ -255,6 +277,18 @@ int gh_op_apply_rope( gh_attn_t h,
                       void* state_q,
                       void* const* token_rows,
                       void* stream );
+/* copy_kv_cache followed by apply_rope on the same token rows, as Llama2::pre_attention_ops and attention_ops issue
+ * them back to back (src/models/llama2/model.hh:345-364), in one kernel launch: row i of state_kv goes to
+ * token_rows[i] with K rotated on the way, state_q is rotated in place.  Same result as the two calls above. */
+int gh_op_copy_kv_cache_apply_rope( gh_attn_t h,
+                                    uint64_t batch,
+                                    const uint32_t* pos,
+                                    const void* freq_cis_real,
+                                    const void* freq_cis_imag,
+                                    void* state_q,
+                                    void* const* token_rows,
+                                    const void* state_kv,
+                                    void* stream );
 /* attention_0_gemm( query, layer_contexts[], att, batch, token_positions ) — ops.cuh:272-324. */
 int gh_op_attention_0_gemm( gh_attn_t h,
                             const void* query,
@@ -329,6 +363,10 @@ int gh_plan_projection( uint32_t n_heads,
  * contexts with uniform noise, src/profile/profiler.hh:79-93). */
 int gh_fill_normal( gh_attn_t h, void* dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t offset, void* stream );
 
+/* Host-side fault injection for tests of the error path: ORs `bits` into the kernels' error word as if a bounded
+ * wait had run out.  Nothing on the GPU is made to wait or fail.  No reference counterpart. */
+int gh_attn_inject_device_error( gh_attn_t h, uint32_t bits );
+
 /* ---- decode attention without any allocation ------------------------------------------------------ */
 
 /* Limits of gh_decode_noalloc; requests beyond them are refused. */
@@ -359,7 +397,8 @@ typedef struct gh_noalloc_shape
  * `layer_bases` is a host array of device pointers to the first token row of each context's layer (null = skip),
  * `pos` a host array, q and xb device pointers, exactly as for gh_op_attention_fused; the current CUDA device is
  * used.  The first call on a device resolves the array's device address; make it before any stream capture on
- * that device.  Every call reuses the same array (nothing in it needs clearing: all that a call reads it has written
+ * that device.  Do not call this entry point while a stream capture is in progress (it returns GH_ERR_STATE then):
+ * each call uploads its batch description from the caller's stack.  Every call reuses the same array (nothing in it needs clearing: all that a call reads it has written
  * first), so calls whose kernels could run concurrently on one GPU race with each other and must be ordered by the
  * caller.
  * Returns GH_ERR_INVALID when a limit above is exceeded; gh_decode_noalloc_error() then names the limit. */

@@ -17,9 +17,13 @@ Two things stand between GCC 13 and the reference headers, and both are handled 
    template head is written to a scratch directory outside the repository and put first on the include path.
 
 Flavours: ``native`` uses the reference's own flags (``etc/cflags.cmake``: -O3 -march=native -ffast-math
--fsingle-precision-constant, plus OpenMP); ``v3`` swaps -march=native for -march=x86-64-v3 so that the
-library still loads on a host whose CPU lacks the build host's extensions.  ``load_ref()`` picks ``native``
-only when the running CPU advertises every flag the build host had.
+-fsingle-precision-constant, plus OpenMP); ``v4`` and ``v3`` swap -march=native for -march=x86-64-v4 (AVX-512) and
+-march=x86-64-v3 (AVX2) so that a library still loads on a host whose CPU lacks the build host's extensions.
+``load_ref()`` picks ``native`` only when the running CPU advertises every flag the build host had, else the
+widest of the other two that the CPU can run.
+
+The reference tree is looked for where the environment variable GLINTHAWK_REFERENCE points, else in a directory
+named ``reference`` beside the repository; when neither exists nothing is built and prebuilt libraries are used.
 """
 from __future__ import annotations
 
@@ -33,13 +37,15 @@ import tempfile
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REF_ROOT = Path(os.environ.get("GLINTHAWK_REFERENCE", "/root/reference"))
+REF_ROOT = Path(os.environ.get("GLINTHAWK_REFERENCE") or HERE.parent.parent / "reference")
 REF_OUT = HERE / "_ref"
 ORACLE_SO = HERE / "libattn_oracle.so"
 
 _REF_FLAGS = ["-std=c++20", "-O3", "-DNDEBUG", "-ffast-math", "-fsingle-precision-constant", "-fopenmp",
               "-DTARGET_PLATFORM_AMD64", "-shared", "-fPIC", "-w"]
 _TEMPLATE_HEAD = "template<typename Config, typename DType, typename ContextType>"
+_MARCH = {"native": "-march=native", "v4": "-march=x86-64-v4", "v3": "-march=x86-64-v3"}
+_V4_FLAGS = {"avx512f", "avx512bw", "avx512cd", "avx512dq", "avx512vl"}
 
 
 def _cpu_flags() -> list[str]:
@@ -123,7 +129,7 @@ def build_ref(force: bool = False) -> list[Path]:
         return sorted(REF_OUT.glob("libghref_*.so"))
     REF_OUT.mkdir(exist_ok=True)
     harness = HERE / "ref_harness.cc"
-    outs = {"native": REF_OUT / "libghref_native.so", "v3": REF_OUT / "libghref_v3.so"}
+    outs = {f: REF_OUT / f"libghref_{f}.so" for f in _MARCH}
     if not force and all(_newer(o, harness, HERE / "shim" / "glog" / "logging.h") for o in outs.values()):
         return list(outs.values())
     scratch = Path(tempfile.mkdtemp(prefix="ghref_build_"))
@@ -131,8 +137,7 @@ def build_ref(force: bool = False) -> list[Path]:
         inc = _patched_include_dir(scratch)
         extra_srcs = [str(REF_ROOT / "src" / "util" / "demangle.cc")]
         for flavour, out in outs.items():
-            march = "-march=native" if flavour == "native" else "-march=x86-64-v3"
-            cmd = ["g++", *_REF_FLAGS, march, f"-I{HERE / 'shim'}", f"-I{inc}", f"-I{REF_ROOT / 'src'}",
+            cmd = ["g++", *_REF_FLAGS, _MARCH[flavour], f"-I{HERE / 'shim'}", f"-I{inc}", f"-I{REF_ROOT / 'src'}",
                    str(harness), *extra_srcs, "-o", str(out)]
             subprocess.run(cmd, check=True)
         (REF_OUT / "BUILD_INFO.json").write_text(json.dumps({
@@ -206,12 +211,15 @@ def load_oracle() -> ctypes.CDLL:
 
 def ref_flavour() -> str | None:
     """Which prebuilt reference library this host can run, or None when there is none."""
-    native, v3 = REF_OUT / "libghref_native.so", REF_OUT / "libghref_v3.so"
+    native, v4, v3 = (REF_OUT / f"libghref_{f}.so" for f in ("native", "v4", "v3"))
     info = REF_OUT / "BUILD_INFO.json"
+    have = set(_cpu_flags())
     if native.exists() and info.exists():
         need = set(json.loads(info.read_text()).get("native_cpu_flags", []))
-        if need and need <= set(_cpu_flags()):
+        if need and need <= have:
             return "native"
+    if v4.exists() and _V4_FLAGS <= have:
+        return "v4"
     if v3.exists():
         return "v3"
     return None

@@ -164,6 +164,24 @@ class Oracle:
         rows = [c[int(p)].copy() if a else None for c, p, a in zip(cache, case.pos, case.active)]
         return StepResult(rows, q, xb, att if keep_att else None)
 
+    def timed_layer_step(self, case: Case):
+        """As Reference.timed_layer_step, for the C restatement."""
+        sh, B = case.shape, case.B
+        cache = [c.copy() for c in case.cache]
+        q, xb = case.q.copy(), np.zeros_like(case.q)
+        att = np.zeros((B, sh.n_heads, sh.seq_len), dtype=case.q.dtype)
+        bases = (C.c_void_p * B)(*[c.ctypes.data if a else 0 for c, a in zip(cache, case.active)])
+        args = (case.dtype, C.c_uint64(B), _vp(case.pos), bases, _vp(case.fcr), _vp(case.fci), _vp(q), _vp(case.kv_new),
+                _vp(att), _vp(xb), C.c_uint64(sh.n_kv_heads), C.c_uint64(sh.gqa_size), C.c_uint64(sh.head_size),
+                C.c_uint64(sh.seq_len))
+        keep = (cache, q, xb, att, case)
+
+        def run():
+            assert self.lib.gho_layer_step(*args) == 0
+            return keep is not None
+
+        return run
+
     def _rotate_and_append(self, case: "ProjCase", q: np.ndarray, kv: np.ndarray):
         """copy_kv_cache + apply_rope on one-row slots: what the reference does with the projections next
         (src/models/llama2/model.hh:345-360)."""
@@ -196,18 +214,39 @@ class Oracle:
 class Reference:
     """ctypes view of ``oracle/_ref/libghref_*.so`` (see ``oracle/ref_harness.cc``)."""
 
-    def __init__(self, lib):
+    def __init__(self, lib, flavour: str = ""):
         self.lib = lib
+        self.flavour = flavour  # which build of the reference this is: native, v4 (AVX-512) or v3 (AVX2)
         lib.ghref_shape_name.restype = C.c_char_p
         self.names = [lib.ghref_shape_name(i).decode() for i in range(lib.ghref_shape_count())]
 
     @classmethod
     def try_load(cls):
         lib = oracle_build.load_ref()
-        return cls(lib) if lib is not None else None
+        return cls(lib, oracle_build.ref_flavour() or "") if lib is not None else None
 
     def threads(self) -> int:
         return self.lib.ghref_threads()
+
+    def timed_layer_step(self, case: Case):
+        """A closure that runs the reference's five operations on the case and nothing else: buffers are set up here,
+        outside whatever the caller times.  Every call appends the same rows again and rotates q once more."""
+        assert case.dtype in (F16, F32), "the reference's amd64 backend has no bf16"
+        sh, B = case.shape, case.B
+        idx = self.names.index(sh.name)
+        cache = [c.copy() for c in case.cache]
+        q, xb = case.q.copy(), np.zeros_like(case.q)
+        att = np.zeros((B, sh.n_heads, sh.seq_len), dtype=case.q.dtype)
+        bases = (C.c_void_p * B)(*[c.ctypes.data if a else 0 for c, a in zip(cache, case.active)])
+        args = (idx, case.dtype, C.c_uint64(B), _vp(case.pos), bases, _vp(case.fcr), _vp(case.fci), _vp(q),
+                _vp(case.kv_new), _vp(att), _vp(xb))
+        keep = (cache, q, xb, att, case)  # noqa: F841  (the closure keeps the buffers alive)
+
+        def run():
+            assert self.lib.ghref_layer_step(*args) == 0
+            return keep is not None
+
+        return run
 
     def layer_step(self, case: Case, keep_att: bool = False) -> StepResult:
         assert case.dtype in (F16, F32), "the reference's amd64 backend has no bf16"

@@ -1,4 +1,4 @@
-"""Drop-in at model level (BASELINE configuration 1): the reference's own `Llama2` model class on a tiny Llama-2
+"""Drop-in at model level: the reference's own `Llama2` model class on a tiny Llama-2
 shape (stories15M: dim 288, 6 layers, 6 heads of 48, vocabulary 32000, 256-token slots, fp32, N(0, 0.02) weights),
 batch of 4 prompts of 1-32 random tokens fed one token per pass, then 64 greedy steps — once with the reference's
 amd64 backend, once with the attention stage replaced by this library through the C++ adapter and the C ABI.

@@ -112,9 +112,11 @@ def test_the_operation_level_entry_point_takes_the_reference_arguments(oracle):
     rows_d = torch.full((B, 2 * sh.kv_dim), float("nan"), device="cuda", dtype=torch.float16)
     ptrs = [rows_d[i].data_ptr() for i in range(B)]
     ptrs[2] = 0  # inactive
+    pos = case.pos.copy()
+    pos[2] = 0xFFFFFFFF  # ... and its position is a value that must never index the tables
     q_out = torch.zeros((B, sh.dim), device="cuda", dtype=torch.float16)
     st.pre_attention_rope_append(B, gpu_util.to_dev(case.x, dt), gpu_util.to_dev(case.rms_w, dt), gpu_util.to_dev(case.wq, dt),
-                                 gpu_util.to_dev(case.wkv, dt), q_out, case.pos, gpu_util.to_dev(case.fcr, dt),
+                                 gpu_util.to_dev(case.wkv, dt), q_out, pos, gpu_util.to_dev(case.fcr, dt),
                                  gpu_util.to_dev(case.fci, dt), ptrs)
     torch.cuda.synchronize()
     assert st.stats().device_error == 0

@@ -109,6 +109,52 @@ def _handoff_worker(rank: int, world: int, port: int, out):
         dist.destroy_process_group()
 
 
+def _layer_link_worker(rank: int, world: int, port: int, out):
+    import torch
+
+    from glinthawk_b200.handoff import LayerLink, attention_side_step, dense_side_step
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        link = LayerLink(1 - rank, dist.new_group([0, 1]), dist.new_group([0, 1]))
+        n_layers, B = 7, 5
+        gen = torch.Generator().manual_seed(11)
+        q_src, kv_src = torch.randn(n_layers, B, 64, generator=gen), torch.randn(n_layers, B, 32, generator=gen)
+        for step in range(2):
+            if rank == 0:
+                xb_rx = torch.zeros(n_layers, B, 64)
+                dense_side_step(link, n_layers, q_src + step, kv_src, xb_rx)
+                want = (q_src + step) * 2 + kv_src.sum(dim=2, keepdim=True) + torch.arange(n_layers).view(-1, 1, 1)
+                out.put(("dense", step, bool(torch.allclose(xb_rx, want))))
+            else:
+                q, kv, xb = torch.zeros(n_layers, B, 64), torch.zeros(n_layers, B, 32), torch.zeros(n_layers, B, 64)
+
+                def step_layer(l):
+                    xb[l] = q[l] * 2 + kv[l].sum(dim=1, keepdim=True) + l
+
+                attention_side_step(link, n_layers, q, kv, xb, step_layer)
+                out.put(("attention", step, True))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_layer_by_layer_handoff_with_one_group_per_direction():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_layer_link_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in range(4)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, _, ok in results) and {(s, st) for s, st, _ in results} == {
+        ("dense", 0), ("dense", 1), ("attention", 0), ("attention", 1)}
+
+
 def test_stage_handoff_protocol_between_two_ranks():
     world, port = 2, _free_port()
     ctx = mp.get_context("spawn")

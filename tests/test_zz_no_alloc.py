@@ -4,8 +4,9 @@ Some users of this library run where cudaMalloc is not an option: a worker that 
 weights and context slots at start-up (and treats a failed allocation as fatal), or a serving loop that must not
 take the device-wide synchronisation an allocation implies.  For them the library carries its split-K scratch as
 a fixed array inside its own image.  This file checks that entry point, through the C ABI, against the regular
-fused entry point (gh_op_attention_fused) on the same inputs — twice in a row with different batches, because the
-second call finds the array as the first one left it.  It is named so that pytest collects it last.
+fused entry point (gh_op_attention_fused) on the same inputs and against the CPU oracle's layer-step on them —
+twice in a row with different batches, because the second call finds the array as the first one left it.  It is
+named so that pytest collects it last.
 """
 import numpy as np
 import pytest
@@ -18,11 +19,20 @@ from tests import cases, gpu_util
 pytestmark = pytest.mark.gpu
 
 
-def _both_ways(shape_name, dtype, pos, seed, inactive=()):
+def _both_ways(oracle, shape_name, dtype, pos, seed, inactive=()):
     case = cases.make_case("noalloc", shape_name, dtype, pos, seed, inactive=inactive)
-    caches = [gpu_util.to_dev(c, dtype) for c in case.cache]  # ordinary device buffers: nothing from a slot pool
+    # The oracle's layer-step appends and rotates first; the attention part of it is what the entry point computes,
+    # so the device gets the caches with the oracle's appended rows in place and the oracle's rotated q.
+    oracle_step = oracle.layer_step(case)
+    host_caches = []
+    for c, p, row in zip(case.cache, case.pos, oracle_step.rows):
+        c = c.copy()
+        if row is not None:
+            c[int(p)] = row
+        host_caches.append(c)
+    caches = [gpu_util.to_dev(c, dtype) for c in host_caches]  # ordinary device buffers: nothing from a slot pool
     bases = [c.data_ptr() if a else 0 for c, a in zip(caches, case.active)]
-    q = gpu_util.to_dev(case.q, dtype)
+    q = gpu_util.to_dev(oracle_step.q, dtype)
 
     stage = gpu_util.make_stage(case)  # the existing entry point needs a handle; the new one does not
     want = torch.zeros_like(q)
@@ -33,23 +43,25 @@ def _both_ways(shape_name, dtype, pos, seed, inactive=()):
     got = torch.zeros_like(q)
     decode_noalloc(case.shape, gpu_util.TORCH_DT[dtype], bases, case.pos, q, got)
     torch.cuda.synchronize()
-    return case, got, want
+    return case, got, want, cases.as_f32(oracle_step.xb, dtype)
 
 
 @pytest.mark.parametrize("shape_name,dtype", [("mini_g8", cases.F16), ("tiny15m", cases.F32), ("mini_g4", cases.BF16)])
-def test_noalloc_matches_existing_entry_point_twice_in_a_row(shape_name, dtype):
+def test_noalloc_matches_existing_entry_point_twice_in_a_row(oracle, shape_name, dtype):
     S = cases.SHAPES[shape_name].seq_len
     # first call: long contexts, so several are cut into work items and leave partial records and counters behind
     first = [S - 1, S - 2, 300 % S, 0, S // 2]
     # second call: a different batch size and different lengths on top of the stale scratch
     second = [5, S - 1, 64, 63, 129 % S, S - 3, 1]
     for pos, seed, inactive in ((first, 1, ()), (second, 2, (2,))):
-        case, got, want = _both_ways(shape_name, dtype, pos, seed, inactive)
+        case, got, want, oracle_xb = _both_ways(oracle, shape_name, dtype, pos, seed, inactive)
         tol = cases.TOL_XB[dtype]
         for i in range(case.B):
             if case.active[i]:
                 np.testing.assert_allclose(got[i].float().cpu().numpy(), want[i].float().cpu().numpy(), rtol=0,
-                                           atol=tol, err_msg=f"context {i}")
+                                           atol=tol, err_msg=f"context {i} against gh_op_attention_fused")
+                np.testing.assert_allclose(got[i].float().cpu().numpy(), oracle_xb[i], rtol=0,
+                                           atol=tol, err_msg=f"context {i} against the oracle")
             else:
                 assert torch.count_nonzero(got[i]) == 0  # inactive prompts are skipped
 
