@@ -445,7 +445,7 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
     n_pf, t_pf = wl.prefill_contexts, wl.prefill_tokens
     plain = not n_pf and not args.producer
     do_via_ops = extras and plain
-    do_strong = extras and plain and (world > 1 or bool(args.strong_share))
+    do_strong = plain and (bool(args.strong_share) or (extras and world > 1))
     do_handoff = extras and plain and world > 1 and world % 2 == 0
     do_parity = extras and plain and rank == 0
     do_producer_extra = extras and plain and world == 1 and wl.dtype != "f32"
@@ -919,10 +919,11 @@ def handoff_region(stage, env, n_layers, batch, slots, pos, q_all, kv_all, xb_al
     # what arrived on the dense side against the attention side's own buffer, sent once more after the timed region
     same = torch.ones(1, device=dev)
     if attention_side:
-        dist.send(xb_all, peer, group=g_out)
+        handoff.wait_all(dist.batch_isend_irecv([dist.P2POp(dist.isend, xb_all, peer, group=g_out)]))
     else:
         again = torch.empty_like(xb_rx)
-        dist.recv(again, peer, group=g_out)
+        handoff.wait_all(dist.batch_isend_irecv([dist.P2POp(dist.irecv, again, peer, group=g_out)]))
+        torch.cuda.synchronize()
         same = torch.tensor([1.0 if torch.equal(again, xb_rx) else 0.0], device=dev)
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
     per_layer = (batch * q_all.shape[2] * 2 + batch * kv_all.shape[2]) * q_all.element_size()

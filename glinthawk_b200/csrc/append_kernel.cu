@@ -108,6 +108,11 @@ __global__ void __launch_bounds__( 256, 6 ) append_ordered_kernel( const AppendA
   const int i = blockIdx.x / blocks_per_ctx;                 // context
   const int tk0 = ( blockIdx.x - i * blocks_per_ctx ) * TB;  // first token of the chunk this block handles
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
+  // Launched as a programmatic dependent of the kernel before it in the stream (normally the previous layer-step's
+  // decode kernel), so that this kernel's launch latency hides behind that kernel's tail.  Unless the caller declared
+  // consecutive calls independent, nothing is read or written before that kernel has completed.
+  if ( a.dependent_launch == 1 )
+    asm volatile( "griddepcontrol.wait;" ::: "memory" );
   const CtxMeta c = a.ctx[i];
   if ( c.kv_off == kInactive )
     return;
@@ -194,8 +199,9 @@ cudaError_t launch_append( const AppendArgs& args, cudaStream_t st, uint64_t* la
     const unsigned tb = tokens >= 2 ? 2 : 1;
     const dim3 cgrid( a.batch * ( ( tokens + tb - 1 ) / tb ), ( cunits + 255 ) / 256 );
     if ( a.dependent_launch != 0 && tb == 1 ) {
-      // The caller declared consecutive steps independent: this launch may begin while the decode kernel before it
-      // in the stream is still running (that kernel releases its dependents at once in this mode).
+      // A programmatic dependent of the kernel before it in the stream: its blocks are placed while that kernel's
+      // last blocks still run (the decode kernel releases its dependents as soon as its last block has started).
+      // dependent_launch == 1: the kernel then waits for that kernel to complete; == 2: it goes ahead.
       cudaLaunchConfig_t cfg {};
       cfg.gridDim = cgrid;
       cfg.blockDim = dim3( 256 );

@@ -60,6 +60,7 @@ struct ScratchSet
 {
   float* part_o = nullptr;
   float* part_ml = nullptr;
+  uint32_t* arrivals = nullptr; // [max_batch][n_kv_heads], zero whenever no launch of the set is in flight
   cudaEvent_t done = nullptr;
   cudaStream_t stream = nullptr;
   bool used = false;
@@ -333,8 +334,8 @@ DecodeArgs decode_args( gh_attn* h, int entry, uint32_t n_items, uint32_t n_spli
   a.xb = xb;
   a.dev_error = h->dev_error;
   a.sm_count = h->sm_count;
-  // (a merge launch behind the decode kernel has to wait for all of it, so nothing could start early anyway)
-  a.trigger_early = ( h->cfg.pipeline_steps != 0 && n_split == 0 ) ? 1u : 0u;
+  // (the CUDA-core kernel is followed by a merge launch when contexts are cut, which has to wait for all of it)
+  a.trigger_early = ( h->use_mma || n_split == 0 ) ? 1u : 0u;
   return a;
 }
 
@@ -345,6 +346,7 @@ int run_decode( gh_attn* h, DecodeArgs a, bool allow_mma, cudaStream_t st )
     return rc;
   a.part_o = set->part_o;
   a.part_ml = set->part_ml;
+  a.arrivals = set->arrivals;
   cudaError_t e;
   if ( h->use_mma && allow_mma ) {
     e = launch_decode_mma( a, &h->kv_map, st, &h->stats.kernel_launches );
@@ -507,6 +509,9 @@ int gh_attn_create( const gh_attn_config* cfg, gh_attn_t* out )
   for ( auto& set : h->scratch ) {
     GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_o ), recs * sh.head_size * sizeof( float ) ) );
     GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.part_ml ), recs * 2 * sizeof( float ) ) );
+    const size_t counts = static_cast<size_t>( cfg->max_batch ) * sh.n_kv_heads * sizeof( uint32_t );
+    GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &set.arrivals ), counts ) );
+    GH_CUDA( h.get(), cudaMemset( set.arrivals, 0, counts ) );
     GH_CUDA( h.get(), cudaEventCreateWithFlags( &set.done, cudaEventDisableTiming ) );
   }
   GH_CUDA( h.get(), cudaMalloc( reinterpret_cast<void**>( &h->dev_error ), sizeof( uint32_t ) ) );
@@ -569,6 +574,7 @@ int gh_attn_destroy( gh_attn_t h )
   for ( auto& set : h->scratch ) {
     cudaFree( set.part_o );
     cudaFree( set.part_ml );
+    cudaFree( set.arrivals );
     if ( set.done )
       cudaEventDestroy( set.done );
   }
@@ -640,6 +646,8 @@ int gh_attn_clear_device_error( gh_attn_t h )
   DeviceGuard guard( h->device );
   GH_CUDA( h, cudaDeviceSynchronize() );
   GH_CUDA( h, cudaMemset( h->dev_error, 0, sizeof( uint32_t ) ) );
+  for ( auto& set : h->scratch ) // a launch that gave up may have left arrival counts behind
+    GH_CUDA( h, cudaMemset( set.arrivals, 0, static_cast<size_t>( h->cfg.max_batch ) * h->sh.n_kv_heads * sizeof( uint32_t ) ) );
   h->stats.device_error = 0;
   h->device_error_seen = false;
   return GH_OK;
@@ -810,7 +818,7 @@ int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_n
   a.kv_new = kv_new;
   a.rope_cos = h->rope_cos;
   a.rope_sin = h->rope_sin;
-  a.dependent_launch = h->cfg.pipeline_steps != 0 ? 1u : 0u;
+  a.dependent_launch = h->cfg.pipeline_steps != 0 ? 2u : 1u;
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
   if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
     return cuda_fail( h, "append kernel launch", e );
@@ -1231,7 +1239,7 @@ bool resolve_own_rows( gh_attn* h, uint64_t batch, const void* const* ptrs, cons
   for ( uint64_t i = 0; i < batch; i++ ) {
     if ( ptrs[i] == nullptr ) {
       h->op_slots_tmp[i] = -1;
-      h->op_pos_tmp[i] = pos != nullptr ? pos[i] : 0;
+      h->op_pos_tmp[i] = 0; // an inactive prompt's position means nothing (copy_kv_cache does not even receive it)
       continue;
     }
     const char* p = static_cast<const char*>( ptrs[i] );
@@ -1297,7 +1305,7 @@ int append_own_rows( gh_attn* h, uint64_t batch, uint32_t layer, void* q, const 
   a.kv_new = kv_new;
   a.rope_cos = rope_cos;
   a.rope_sin = rope_sin;
-  a.dependent_launch = h->cfg.pipeline_steps != 0 ? 1u : 0u;
+  a.dependent_launch = h->cfg.pipeline_steps != 0 ? 2u : 1u;
   if ( const cudaError_t e = launch_append( a, st, &h->stats.kernel_launches ); e != cudaSuccess )
     return cuda_fail( h, "append kernel launch", e );
   return ring_touch( h, h->op_entry, st );
@@ -1674,6 +1682,7 @@ int gh_plan_batch( uint32_t blocks_per_item,
   pp.tile = tile;
   pp.fixed_chunk = fixed_chunk;
   pp.max_items = max_items;
+  pp.blocks_per_sm = 4; // what the tensor-core decode kernel keeps resident
   Plan plan;
   if ( !plan_batch( pp, ctx, plan ) )
     return GH_ERR_INVALID;

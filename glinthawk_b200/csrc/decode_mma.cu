@@ -1,5 +1,6 @@
 // Fused ragged-batch decode attention for 16-bit KV with head size 128: TMA-staged K/V tiles, warp-level
-// tensor-core products with fp32 accumulation, online softmax, GQA sharing, split-K with a warp-level merge inside a block and a tiny merge kernel across blocks.
+// tensor-core products with fp32 accumulation, online softmax, GQA sharing, split-K with a warp-level merge inside a
+// block and, across the blocks of a cut context, a merge by whichever of them finishes last.
 //
 // One launch per layer-step replaces, for the whole batch, the reference's per-context cuBLAS QK^T call, four
 // softmax kernels and cuBLAS AV call (src/arch/cuda/llama2/ops.cuh:272-411) and the `att` score matrix between
@@ -16,8 +17,8 @@
 //   * Consumer warp w owns tokens 16w..16w+15 of every tile: S = Q K^T with mma.m16n8k16 (query heads of the group
 //     are the M rows, padded to 16), online softmax in the log2 domain with quad shuffles, O += P V with the
 //     probabilities re-used from registers.  The warps keep independent (m, l, O) states that are combined
-//     through shared memory at the end ("warp-level merge"); contexts cut into several items are then combined by
-//     a small second kernel (gh_merge.cuh).
+//     through shared memory at the end ("warp-level merge"); the blocks of a context cut into several items leave
+//     partial records and count their arrivals, and the last one to arrive combines the records (gh_merge.cuh).
 // The path is HBM-bound: 512 B of K+V per (token, kv head) against 2 x 16 x 128 x 2 tensor flops.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a sticky error word and leaves.
@@ -169,7 +170,10 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   constexpr bool ROWS16 = G16 || CHUNK;
   constexpr int kTile = G::kTile, kConsumerWarps = G::kConsumerWarps, kConsumers = G::kConsumers;
   constexpr int kBoxBytes = G::kBoxBytes, kStageBytes = G::kStageBytes, kStages = G::kStages;
-  if ( a.trigger_early ) // the caller declared the next step independent of this one: let its append launch begin
+  // The kernel behind this one in the stream may be placed on the SMs once every block of this launch has started
+  // (so it never takes a block slot from this launch); if it is one of this library's kernels it waits there for this
+  // launch to complete, unless the caller declared the two independent.
+  if ( a.trigger_early )
     asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kStages];
@@ -458,6 +462,29 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   } else {
     store_item<T>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
                    threadIdx.x, kConsumers );
+#ifndef GH_DECODE_MERGE_KERNEL // (defined only in comparison builds: the records then go to merge_partials_kernel)
+    if ( c.nsplits > 1 ) {
+      // This block left a partial record.  Count it; whichever block of the (context, kv head) arrives last finds
+      // every record of the context in memory and combines them.  No block waits for another.
+      __threadfence();
+      asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
+      int* sm_last = reinterpret_cast<int*>( &sm_wm[0][0] ); // (the warps' states were consumed above)
+      if ( threadIdx.x == 0 ) {
+        uint32_t* count = a.arrivals + (size_t)it.ctx * sh.n_kv_heads + kvh;
+        const bool last = atomicAdd( count, 1u ) + 1u == (uint32_t)c.nsplits;
+        if ( last )
+          *count = 0; // nobody else touches it in this launch: it is zero again for the next one
+        *sm_last = last ? 1 : 0;
+      }
+      asm volatile( "bar.sync 1, %0;" ::"n"( kConsumers ) : "memory" );
+      if ( *sm_last != 0 ) {
+        __threadfence();
+        static_assert( 16 * ( 2 * kMaxSplits + 1 ) * 4 <= kStages * kStageBytes, "combine scratch must fit the ring" );
+        combine_records<T>( sh, c, it.ctx, kvh * group, group, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
+                            reinterpret_cast<float*>( ring ), threadIdx.x, kConsumers );
+      }
+    }
+#endif
   }
 }
 
@@ -478,8 +505,10 @@ cudaError_t launch_g( const DecodeArgs& a, const CUtensorMap* map, cudaStream_t 
     return cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G, true>, a, *map );
   cudaError_t e = a.sh.group > 8 ? cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, true, G, false>, a, *map )
                                  : cudaLaunchKernelEx( &cfg, decode_mma_kernel<T, false, G, false>, a, *map );
+#ifdef GH_DECODE_MERGE_KERNEL
   if ( e == cudaSuccess && a.n_split_ctx > 0 )
     e = launch_merge_partials<T>( a.sh, a.ctx, a.split_ctx, a.n_split_ctx, a.part_o, a.part_ml, static_cast<T*>( a.xb ), st );
+#endif
   return e;
 }
 
@@ -556,7 +585,7 @@ cudaError_t launch_decode_mma( const DecodeArgs& a, const CUtensorMap* kv_map, c
     case DT_BF16: e = launch_t<__nv_bfloat16>( a, kv_map, st ); break;
     default: return cudaErrorInvalidValue;
   }
-  *launches += a.n_split_ctx > 0 ? 2 : 1;
+  *launches += 1;
   return e;
 }
 

@@ -24,7 +24,9 @@ struct AppendArgs
   const void* kv_new;   // [batch][2 * kv_dim]; nullptr = rotate the row already in the slot (apply_rope alone)
   const void* rope_cos; // [seq_len][head_size / 2]; nullptr = copy without rotation (copy_kv_cache alone)
   const void* rope_sin;
-  uint32_t dependent_launch; // 1 = launch as a programmatic dependent of the kernel before it (pipeline_steps)
+  uint32_t dependent_launch; // 0 = ordinary launch; 1 = programmatic dependent of the kernel before it in the stream that
+                             // waits for that kernel to complete before it touches anything; 2 = the same without the
+                             // wait (gh_attn_config.pipeline_steps: the caller declared consecutive calls independent)
 };
 
 struct DecodeArgs
@@ -40,12 +42,14 @@ struct DecodeArgs
   void* xb;
   float* part_o;
   float* part_ml;
+  uint32_t* arrivals;       // [batch][n_kv_heads] arrival counts of the blocks of cut contexts, all zero between
+                            // launches (tensor-core kernel: the last block to arrive combines the records itself)
   const int32_t* split_ctx; // batch indices of the contexts that were cut into several items
   uint32_t n_split_ctx;
   uint32_t* dev_error;
   uint32_t sm_count;
   uint32_t chunk_tokens; // 0 = decode step; T = prefill chunk of T tokens per context (tensor-core kernel only)
-  uint32_t trigger_early; // 1 = release the next programmatic dependent launch at once (gh_attn_config.pipeline_steps)
+  uint32_t trigger_early; // 1 = release the next programmatic dependent launch as soon as every block has started
 };
 
 struct ScoreArgs // the reference's three unfused operations

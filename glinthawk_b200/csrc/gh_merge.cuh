@@ -1,10 +1,11 @@
-// Epilogue shared by the decode kernels, and the kernel that combines the pieces of contexts that were cut.
+// Epilogue shared by the decode kernels, and the two ways the pieces of contexts that were cut are combined.
 //
 // A context that fits one work item is finished by the block that processed it.  A context cut into several items
-// leaves one partial record per (item, query head); a second, tiny, massively parallel kernel then combines the
-// records of each such context.  It is launched only when the batch has cut contexts, as a programmatic dependent
-// of the decode kernel, so its launch latency hides behind the decode kernel's tail.  Nothing waits on another
-// block anywhere: no flags, no counters, no spinning.
+// leaves one partial record per (item, query head).  The CUDA-core kernels leave the records to a second, tiny,
+// massively parallel kernel, launched only when the batch has cut contexts, as a programmatic dependent of the decode
+// kernel.  The tensor-core kernel counts the arrivals of a context's blocks and lets the block that arrives last
+// combine the records (combine_records below): with few contexts per GPU, where contexts are cut to fill the SMs,
+// the extra launch cost a fifth of the layer-step.  Nothing waits on another block either way: no spinning.
 #pragma once
 
 #include "gh_common.cuh"
@@ -47,6 +48,81 @@ __device__ __forceinline__ void store_item( const Shape& sh,
   for ( int r = tid; r < nrows; r += nthreads ) {
     part_ml[( rec0 + r ) * 2 + 0] = sm_m[r];
     part_ml[( rec0 + r ) * 2 + 1] = sm_l[r];
+  }
+}
+
+// For the block of a cut context that arrived last (every record of the context is visible to it): combines the
+// records of query heads head0 .. head0+nrows-1 and writes xb.  `scratch` is shared memory for
+// nrows * (2 * nsplits + 1) floats; barrier `bar_id` is met by all `nthreads` calling threads.
+template<typename T>
+__device__ __forceinline__ void combine_records( const Shape& sh,
+                                                 const CtxMeta& c,
+                                                 const int ctx_index,
+                                                 const int head0,
+                                                 const int nrows,
+                                                 T* __restrict__ xb,
+                                                 const float* part_o,
+                                                 const float* part_ml,
+                                                 float* scratch,
+                                                 const int tid,
+                                                 const int nthreads )
+{
+  const int hs = sh.head_size, ns = c.nsplits;
+  float* sm_ml = scratch;                 // [nrows][ns][2], then the weights in place of m
+  float* sm_L = scratch + nrows * ns * 2; // [nrows]
+  const size_t rec0 = (size_t)c.partial_base * sh.n_heads + head0;
+  for ( int i = tid; i < nrows * ns; i += nthreads ) {
+    const int r = i / ns, sp = i - r * ns;
+    const float2 ml = __ldcg( reinterpret_cast<const float2*>( part_ml + ( rec0 + (size_t)sp * sh.n_heads + r ) * 2 ) );
+    sm_ml[i * 2] = ml.x;
+    sm_ml[i * 2 + 1] = ml.y;
+  }
+  asm volatile( "bar.sync 1, %0;" ::"r"( nthreads ) : "memory" );
+  for ( int r = tid; r < nrows; r += nthreads ) {
+    float M = -INFINITY;
+    for ( int sp = 0; sp < ns; sp++ )
+      M = fmaxf( M, sm_ml[( r * ns + sp ) * 2] );
+    float L = 0.f;
+    for ( int sp = 0; sp < ns; sp++ ) {
+      const float w = exp2f( sm_ml[( r * ns + sp ) * 2] - M );
+      L += w * sm_ml[( r * ns + sp ) * 2 + 1];
+      sm_ml[( r * ns + sp ) * 2] = w;
+    }
+    sm_L[r] = L;
+  }
+  asm volatile( "bar.sync 1, %0;" ::"r"( nthreads ) : "memory" );
+  // Each thread finishes kU outputs at a time, so that kU loads per record are in flight together: the combining
+  // block sits at the tail of the launch, and its latency is what the launch pays.
+  constexpr int kU = 8;
+  T* out = xb + (size_t)ctx_index * sh.n_heads * hs + (size_t)head0 * hs;
+  const int n_out = nrows * hs;
+  const size_t rec_stride = (size_t)sh.n_heads * hs;
+  for ( int e0 = tid; e0 < n_out; e0 += nthreads * kU ) {
+    float O[kU];
+    int row[kU];
+#pragma unroll
+    for ( int u = 0; u < kU; u++ ) {
+      O[u] = 0.f;
+      row[u] = min( e0 + u * nthreads, n_out - 1 ) / hs;
+    }
+#pragma unroll 2
+    for ( int sp = 0; sp < ns; sp++ ) {
+      float v[kU];
+#pragma unroll
+      for ( int u = 0; u < kU; u++ ) {
+        const int e = e0 + u * nthreads;
+        v[u] = e < n_out ? __ldcg( part_o + rec0 * hs + (size_t)sp * rec_stride + e ) : 0.f;
+      }
+#pragma unroll
+      for ( int u = 0; u < kU; u++ )
+        O[u] += sm_ml[( row[u] * ns + sp ) * 2] * v[u];
+    }
+#pragma unroll
+    for ( int u = 0; u < kU; u++ ) {
+      const int e = e0 + u * nthreads;
+      if ( e < n_out )
+        out[e] = Conv<T>::from_f32( O[u] / sm_L[row[u]] );
+    }
   }
 }
 

@@ -2,10 +2,15 @@
 //
 // A batch is ragged: context i attends over pos[i] + 1 tokens.  Work items are ordered longest-first so that the
 // hardware block scheduler approximates longest-processing-time-first, and long contexts are cut along the token
-// axis only as far as that pays: every extra item costs a pipeline fill and drain (about 2 us on B200, against
-// roughly 23-45 ns per token per block slot), and an item of a cut context also writes a partial record that the
-// merge kernel reads back.  The split length is therefore chosen by simulating the launch for a few candidate
-// lengths and keeping the one with the shortest makespan.  The
+// axis only as far as that pays: every extra item costs a pipeline fill and drain (about 2 us on B200), and an item
+// of a cut context also writes a partial record that is read back when the records are combined.  The blocks that
+// run at the same time share the HBM bandwidth equally: with every block slot of the GPU busy a block takes about
+// 40 ns per token (one "token-time"), with fewer blocks running each gets more, down to about 20 ns per token, where
+// a block is bound by the latency of its own loads.  So a long context is the critical path of a launch even when
+// the GPU is saturated, and how far cutting pays depends on how many other contexts there are to fill the slots.
+// The split length is chosen by simulating this sharing for a dozen candidate lengths (an event-driven simulation,
+// one event per work item) and keeping the shortest launch; the model's constants were fitted to launch times
+// measured on B200 for 32 to 256 contexts per GPU and reproduce them to within 3 %.  The
 // reference has no counterpart: it loops over the batch on the host and launches per context
 // (src/arch/cuda/llama2/ops.cuh:272-453).
 #pragma once
@@ -30,8 +35,10 @@ struct PlanParams
   uint32_t max_items = 0;       // capacity of the item and partial-record buffers
   uint32_t blocks_per_sm = 2;       // thread blocks resident per SM
   uint32_t min_chunk = 256;
-  uint32_t whole_overhead = 90;     // cost of an uncut context's item beyond its tokens, in token-times
-  uint32_t piece_overhead = 200;    // the same for an item of a cut context (partial record + its share of the merge)
+  uint32_t whole_overhead = 100;    // cost of an uncut context's item beyond its tokens, in token-times
+  uint32_t piece_overhead = 250;    // the same for an item of a cut context (partial record, arrival count, combining)
+  uint32_t alone_rate_pct = 50;     // time per token of a block that runs latency-bound, in percent of a token-time
+                                    // (a token-time = time per token of a block when all block slots stream together)
 };
 
 struct Plan
@@ -84,9 +91,13 @@ inline bool plan_batch( const PlanParams& p, std::vector<CtxMeta>& ctx, Plan& ou
     return n;
   };
 
-  // Predicted makespan, in token-times, of the launch with split length `chunk`: items (each fanning out to
-  // n_kv_heads blocks at once) are dealt longest-first onto the block slots of the GPU.
+  // Predicted duration, in token-times, of the launch with split length `chunk`.  Items (each fanning out to
+  // n_kv_heads blocks at once) start longest-first while item slots are free; the n items running at any moment each
+  // progress at min( 1 / alone_rate, slots / n ) tokens per token-time.  Because all running items progress at the
+  // same rate, progress is tracked in one shared coordinate: an item of length L that starts at progress v ends at
+  // v + L, and the elapsed time between two ends is the progress made divided by the rate in force.
   const uint32_t machines = std::max<uint32_t>( 1, p.sm_count * p.blocks_per_sm / std::max<uint32_t>( 1, p.n_kv_heads ) );
+  const double top_rate = 100.0 / std::max<uint32_t>( 1, p.alone_rate_pct );
   std::vector<uint32_t> costs;
   auto makespan = [&]( uint32_t chunk ) {
     costs.clear();
@@ -96,23 +107,26 @@ inline bool plan_batch( const PlanParams& p, std::vector<CtxMeta>& ctx, Plan& ou
       const uint32_t len = c.pos + 1;
       const uint32_t n = ( len + chunk - 1 ) / chunk;
       const uint32_t step = round_up_u32( ( len + n - 1 ) / n, p.tile );
+      const uint32_t overhead = n > 1 ? p.piece_overhead : p.whole_overhead;
       for ( uint32_t b = 0; b < len; b += step )
-        costs.push_back( std::min( step, len - b ) + ( n > 1 ? p.piece_overhead : p.whole_overhead ) );
+        costs.push_back( std::min( step, len - b ) + overhead );
     }
     std::sort( costs.begin(), costs.end(), std::greater<uint32_t>() );
-    if ( costs.size() <= machines )
-      return static_cast<uint64_t>( costs.front() );
-    std::priority_queue<uint64_t, std::vector<uint64_t>, std::greater<uint64_t>> load;
-    for ( uint32_t m = 0; m < machines; m++ )
-      load.push( costs[m] );
-    uint64_t longest = costs.front();
-    for ( size_t i = machines; i < costs.size(); i++ ) {
-      const uint64_t l = load.top() + costs[i];
-      load.pop();
-      load.push( l );
-      longest = std::max( longest, l );
+    std::priority_queue<double, std::vector<double>, std::greater<double>> ends; // progress at which running items end
+    size_t next = 0;
+    double progress = 0.0, elapsed = 0.0;
+    while ( next < costs.size() && ends.size() < machines )
+      ends.push( progress + costs[next++] );
+    while ( !ends.empty() ) {
+      const double rate = std::min( top_rate, static_cast<double>( machines ) / static_cast<double>( ends.size() ) );
+      const double end = ends.top();
+      ends.pop();
+      elapsed += ( end - progress ) / rate;
+      progress = end;
+      if ( next < costs.size() )
+        ends.push( progress + costs[next++] );
     }
-    return longest;
+    return static_cast<uint64_t>( elapsed + 0.5 );
   };
 
   uint32_t chunk = p.fixed_chunk;
@@ -121,19 +135,25 @@ inline bool plan_batch( const PlanParams& p, std::vector<CtxMeta>& ctx, Plan& ou
     while ( item_count( chunk ) > p.max_items )
       chunk *= 2;
   } else {
-    // candidates: no cut at all, then halvings down to the minimum split length
+    // candidates: no cut at all, then three quarters and halves of that, and so on down to the minimum split
+    // length; of equally good ones the longest wins (fewest items)
     const uint32_t top = round_up_u32( max_len, p.tile );
+    const uint32_t floor_len = std::max( p.min_chunk, p.tile );
     uint64_t best = ~0ull;
-    for ( uint32_t cand = top;; cand = round_up_u32( cand / 2, p.tile ) ) {
-      if ( item_count( cand ) <= p.max_items ) {
-        const uint64_t ms = makespan( cand );
-        if ( ms < best ) {
-          best = ms;
-          chunk = cand;
-        }
+    auto consider = [&]( uint32_t cand ) {
+      if ( ( cand < floor_len && cand != top ) || item_count( cand ) > p.max_items )
+        return;
+      const uint64_t ms = makespan( cand );
+      if ( ms < best ) {
+        best = ms;
+        chunk = cand;
       }
-      if ( cand <= std::max( p.min_chunk, p.tile ) )
+    };
+    for ( uint32_t cand = top;; cand = round_up_u32( cand / 2, p.tile ) ) {
+      consider( cand );
+      if ( cand <= floor_len )
         break;
+      consider( round_up_u32( static_cast<uint64_t>( cand ) * 3 / 4, p.tile ) );
     }
     if ( chunk == 0 )
       return false;

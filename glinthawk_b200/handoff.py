@@ -65,32 +65,38 @@ class LayerLink:
     outputs: object
 
 
-def attention_side_step(link: LayerLink, n_layers: int, q_all, kv_all, xb_all, step_layer) -> None:
-    """Attention side of one decode step over all layers.  The receives of every layer's q / K,V rows are posted up
-    front, in layer order (the order the dense side sends them in); layer l's kernels are enqueued once its inputs
-    are in (`step_layer(l)` reads q_all[l], kv_all[l] and writes xb_all[l] on the current stream), and xb_all[l] goes
-    back while layer l+1 computes.  On NCCL a wait only orders streams; the host runs ahead."""
-    recvs = [dist.batch_isend_irecv([dist.P2POp(dist.irecv, q_all[l], link.peer, group=link.inputs),
-                                     dist.P2POp(dist.irecv, kv_all[l], link.peer, group=link.inputs)])
-             for l in range(n_layers)]
+def attention_side_step(link: LayerLink, n_layers: int, q_all, kv_all, xb_all, step_layer, ahead: int = 8) -> None:
+    """Attention side of one decode step over all layers.  The receives of q / K,V rows run `ahead` layers in front of
+    the compute, in layer order (the order the dense side sends them in); layer l's kernels are enqueued once its
+    inputs are in (`step_layer(l)` reads q_all[l], kv_all[l] and writes xb_all[l] on the current stream), and
+    xb_all[l] goes back while layer l+1 computes.  On NCCL a wait only orders streams; the host runs ahead, and it
+    posts only a few receives before the first layer's kernels so that the GPU does not sit idle behind it."""
+    def post(l):
+        return dist.batch_isend_irecv([dist.P2POp(dist.irecv, q_all[l], link.peer, group=link.inputs),
+                                       dist.P2POp(dist.irecv, kv_all[l], link.peer, group=link.inputs)])
+
+    recvs = {l: post(l) for l in range(min(ahead, n_layers))}
     sends = []
     for l in range(n_layers):
-        wait_all(recvs[l])
+        wait_all(recvs.pop(l))
         step_layer(l)
-        sends.append(dist.isend(xb_all[l], link.peer, group=link.outputs))
-    wait_all(sends)
+        sends.append(dist.batch_isend_irecv([dist.P2POp(dist.isend, xb_all[l], link.peer, group=link.outputs)]))
+        if l + ahead < n_layers:
+            recvs[l + ahead] = post(l + ahead)
+    for s_ in sends:
+        wait_all(s_)
 
 
 def dense_side_step(link: LayerLink, n_layers: int, q_all, kv_all, xb_rx) -> None:
     """Dense-stage side, mirroring attention_side_step: every layer's inputs go out in layer order, every layer's xb
     is received into xb_rx[l] in layer order."""
-    sends = [dist.batch_isend_irecv([dist.P2POp(dist.isend, q_all[l], link.peer, group=link.inputs),
-                                     dist.P2POp(dist.isend, kv_all[l], link.peer, group=link.inputs)])
-             for l in range(n_layers)]
-    recvs = [dist.irecv(xb_rx[l], link.peer, group=link.outputs) for l in range(n_layers)]
-    for s_ in sends:
-        wait_all(s_)
-    wait_all(recvs)
+    works = []
+    for l in range(n_layers):
+        works.append(dist.batch_isend_irecv([dist.P2POp(dist.isend, q_all[l], link.peer, group=link.inputs),
+                                             dist.P2POp(dist.isend, kv_all[l], link.peer, group=link.inputs)]))
+        works.append(dist.batch_isend_irecv([dist.P2POp(dist.irecv, xb_rx[l], link.peer, group=link.outputs)]))
+    for w in works:
+        wait_all(w)
 
 
 def wait_all(reqs) -> None:

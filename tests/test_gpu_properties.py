@@ -134,7 +134,9 @@ def test_batch_order_does_not_matter():
     st.decode(0, q, xb_i)
     torch.cuda.synchronize()
     keep = torch.from_numpy(s2 >= 0).cuda()
-    assert torch.equal(xb_i[keep], xb[keep]) and bool((xb_i[~keep] == 7.0).all())
+    # (with a third of the batch gone the planner may cut long contexts that it left whole before: same values up to
+    # the rounding of a different summation order, not the same bits)
+    assert float((xb_i[keep].float() - xb[keep].float()).abs().max()) <= 2e-3 and bool((xb_i[~keep] == 7.0).all())
     st.close()
 
 
