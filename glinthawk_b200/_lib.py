@@ -12,7 +12,7 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 LIB_PATH = Path(os.environ.get("GLINTHAWK_ATTN_LIB", PKG / "libglinthawk_attn.so"))  # override for A/B runs
-HEADER = PKG.parent / "include" / "glinthawk_attn.h"
+HEADERS = sorted((PKG.parent / "include").glob("*.h"))
 
 GH_OK, GH_ERR_INVALID, GH_ERR_CUDA, GH_ERR_NO_SLOT, GH_ERR_CAPACITY = 0, 1, 2, 3, 4
 GH_ERR_OOM, GH_ERR_UNSUPPORTED, GH_ERR_STATE, GH_ERR_NOT_FOUND = 5, 6, 7, 8
@@ -86,9 +86,12 @@ _PROTOS = {
 
 
 def declared_symbols() -> list[str]:
-    """Every function name the public header declares."""
-    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"\b(gh_[a-z0-9_]+)\s*\(", text)))
+    """Every function name the public headers declare."""
+    names: set[str] = set()
+    for header in HEADERS:
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names.update(re.findall(r"\b(gh_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def load() -> C.CDLL:

@@ -37,7 +37,7 @@ def _stale(obj: Path, src: Path, headers: list[Path]) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.hh")) + [PKG.parent / "include" / "glinthawk_attn.h"]
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.hh")) + sorted((PKG.parent / "include").glob("*.h"))
     objdir = PKG / "build"
     objdir.mkdir(exist_ok=True)
     nvcc = _nvcc()

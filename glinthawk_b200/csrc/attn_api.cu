@@ -1,5 +1,6 @@
 // C ABI of the attention stage (see include/glinthawk_attn.h for the contract of every entry point).
 #include "../../include/glinthawk_attn.h"
+#include "../../include/glinthawk_attn_aux.h"
 
 #include <algorithm>
 #include <cstdio>

@@ -302,9 +302,13 @@ __global__ void __launch_bounds__( kThreads, 2 )
       }
       float tmax = -INFINITY;
       if ( full_tile ) {
+        // four chains of eight three-input maxima each instead of one chain of 32: the row owners have only two
+        // warps per scheduler to hide a chain's latency behind
+        float t4[4] = { -INFINITY, -INFINITY, -INFINITY, -INFINITY };
 #pragma unroll
         for ( int j = 0; j < 32; j++ )
-          tmax = max3( tmax, sc[j], sc[32 + j] );
+          t4[j & 3] = max3( t4[j & 3], sc[j], sc[32 + j] );
+        tmax = fmaxf( max3( t4[0], t4[1], t4[2] ), t4[3] );
       } else {
 #pragma unroll
         for ( int j = 0; j < 32; j++ ) {

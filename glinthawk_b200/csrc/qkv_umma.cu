@@ -56,6 +56,9 @@ __global__ void __launch_bounds__( 256 ) rmsnorm_kernel( T* __restrict__ out, co
 {
   constexpr int N = Vec16<T>::N;
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
+  // launched as a programmatic dependent of the kernel before it in the stream (its launch latency hides behind
+  // that kernel's tail); x and the scratch row may still be in use until that kernel has completed
+  asm volatile( "griddepcontrol.wait;" ::: "memory" );
   const T* X = x + (size_t)blockIdx.x * dim;
   T* O = out + (size_t)blockIdx.x * dim;
   const uint32_t pieces = dim / N; // dim is a multiple of 128
@@ -166,8 +169,6 @@ __global__ void __launch_bounds__( kThreads, 1 )
   __syncthreads();
   asm volatile( "tcgen05.fence::after_thread_sync;" ::: "memory" );
   const uint32_t tmem_base = *tmem_base_p;
-  // xb was written by the rmsnorm kernel, the kernel before this one in the stream
-  asm volatile( "griddepcontrol.wait;" ::: "memory" );
 
   constexpr unsigned kFull = 0xffffffffu;
 
@@ -178,7 +179,31 @@ __global__ void __launch_bounds__( kThreads, 1 )
       uint32_t n = 0; // stages filled so far
       uint64_t stream_policy;
       asm volatile( "createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"( stream_policy ) );
-      for ( int u = u_begin; u < u_end && ok; ) {
+      // The weights do not depend on the kernel before this one in the stream (rmsnorm): the weight tiles of the first
+      // ring of stages are on their way before this lane waits for that kernel, the activation tiles follow after.
+      // Nothing else in the block touches anything that kernel or its predecessors write: the other roles only see
+      // what these loads bring.
+      const int first_units = min( n_stages, u_end - u_begin );
+      for ( int pass = 0; pass < 2; pass++ ) {
+        if ( pass == 1 )
+          asm volatile( "griddepcontrol.wait;" ::: "memory" );
+        for ( int i = 0; i < first_units; i++ ) {
+          const Piece p = piece_at( u_begin + i, u_end, kblocks, upc );
+          uint8_t* sA = smem + i * stage_bytes;
+          if ( pass == 0 ) {
+            const bool is_q = p.tile < (int)a.q_tiles;
+            asm volatile( "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"( smem_u32( &bar_full[i] ) ),
+                          "r"( (uint32_t)( kATile + nb * 128 ) )
+                          : "memory" );
+            tma_load_2d_hint( sA, is_q ? &wq_map : &wkv_map, p.k0 * kBK,
+                              ( is_q ? p.tile : p.tile - (int)a.q_tiles ) * kTileF, &bar_full[i], stream_policy );
+          } else {
+            tma_load_2d( sA + kATile, &xb_map, p.k0 * kBK, (int)a.batch0, &bar_full[i] );
+          }
+        }
+      }
+      n = static_cast<uint32_t>( first_units );
+      for ( int u = u_begin + first_units; u < u_end && ok; ) {
         const Piece p = piece_at( u, u_end, kblocks, upc );
         const bool is_q = p.tile < (int)a.q_tiles;
         const CUtensorMap* wmap = is_q ? &wq_map : &wkv_map;
@@ -445,24 +470,33 @@ cudaError_t launch_rmsnorm( void* out, const void* x, const void* weight, uint32
   const uint32_t per_piece = dtype == DT_F32 ? 4 : 8;
   if ( dim % per_piece != 0 || dim > 256u * kNormPieces * per_piece )
     return cudaErrorInvalidValue;
+  cudaLaunchConfig_t cfg {};
+  cfg.gridDim = dim3( rows );
+  cfg.blockDim = dim3( 256 );
+  cfg.stream = st;
+  cudaLaunchAttribute attr {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
   switch ( dtype ) {
     case DT_F32:
-      rmsnorm_kernel<float><<<rows, 256, 0, st>>>( static_cast<float*>( out ), static_cast<const float*>( x ),
-                                                   static_cast<const float*>( weight ), dim );
+      e = cudaLaunchKernelEx( &cfg, rmsnorm_kernel<float>, static_cast<float*>( out ), static_cast<const float*>( x ),
+                              static_cast<const float*>( weight ), dim );
       break;
     case DT_F16:
-      rmsnorm_kernel<__half><<<rows, 256, 0, st>>>( static_cast<__half*>( out ), static_cast<const __half*>( x ),
-                                                    static_cast<const __half*>( weight ), dim );
+      e = cudaLaunchKernelEx( &cfg, rmsnorm_kernel<__half>, static_cast<__half*>( out ), static_cast<const __half*>( x ),
+                              static_cast<const __half*>( weight ), dim );
       break;
     case DT_BF16:
-      rmsnorm_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>( static_cast<__nv_bfloat16*>( out ),
-                                                           static_cast<const __nv_bfloat16*>( x ),
-                                                           static_cast<const __nv_bfloat16*>( weight ), dim );
+      e = cudaLaunchKernelEx( &cfg, rmsnorm_kernel<__nv_bfloat16>, static_cast<__nv_bfloat16*>( out ),
+                              static_cast<const __nv_bfloat16*>( x ), static_cast<const __nv_bfloat16*>( weight ), dim );
       break;
     default: return cudaErrorInvalidValue;
   }
   ( *launches )++;
-  return cudaGetLastError();
+  return e;
 }
 
 cudaError_t launch_project( const ProjectArgs& a, uint32_t grid, const CUtensorMap* wq_map, const CUtensorMap* wkv_map,

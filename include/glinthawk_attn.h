@@ -342,31 +342,6 @@ int gh_op_project_append( gh_attn_t h,
                           void* const* token_rows,
                           void* stream );
 
-/* Host-only (touches no device): how gh_attn_project_append deals its work to the SMs.  plan_out receives
- * {CTAs, work units per CTA, most pieces a tile is cut into, feature tiles, k-blocks per tile}; pieces_out receives
- * one record {CTA, tile, first k-block, end k-block, index of the piece within its tile, pieces of that tile} per
- * piece, CTA by CTA in processing order.  No reference counterpart (the reference calls cuBLAS,
- * src/arch/cuda/common/ops.cuh:616-693). */
-int gh_plan_projection( uint32_t n_heads,
-                        uint32_t head_size,
-                        uint32_t kv_dim,
-                        uint32_t sm_count,
-                        uint32_t* plan_out,
-                        int32_t* pieces_out,
-                        uint32_t max_pieces,
-                        uint32_t* n_pieces );
-
-/* ---- helpers for benchmarks and tests ------------------------------------------------------------- */
-
-/* Fills n elements of `dtype` at device pointer `dst` with N(0,1) values from a counter-based generator
- * keyed by (seed, element index + offset).  No reference counterpart (the reference's profiler fills its
- * contexts with uniform noise, src/profile/profiler.hh:79-93). */
-int gh_fill_normal( gh_attn_t h, void* dst, uint64_t n, uint32_t dtype, uint64_t seed, uint64_t offset, void* stream );
-
-/* Host-side fault injection for tests of the error path: ORs `bits` into the kernels' error word as if a bounded
- * wait had run out.  Nothing on the GPU is made to wait or fail.  No reference counterpart. */
-int gh_attn_inject_device_error( gh_attn_t h, uint32_t bits );
-
 /* ---- decode attention without any allocation ------------------------------------------------------ */
 
 /* Limits of gh_decode_noalloc; requests beyond them are refused. */
@@ -398,9 +373,9 @@ typedef struct gh_noalloc_shape
  * `pos` a host array, q and xb device pointers, exactly as for gh_op_attention_fused; the current CUDA device is
  * used.  The first call on a device resolves the array's device address; make it before any stream capture on
  * that device.  Do not call this entry point while a stream capture is in progress (it returns GH_ERR_STATE then):
- * each call uploads its batch description from the caller's stack.  Every call reuses the same array (nothing in it needs clearing: all that a call reads it has written
- * first), so calls whose kernels could run concurrently on one GPU race with each other and must be ordered by the
- * caller.
+ * each call uploads its batch description from the caller's stack.  Every call reuses the same array (nothing in
+ * it needs clearing: all that a call reads it has written first), so calls whose kernels could run concurrently on
+ * one GPU race with each other and must be ordered by the caller.
  * Returns GH_ERR_INVALID when a limit above is exceeded; gh_decode_noalloc_error() then names the limit. */
 int gh_decode_noalloc( const gh_noalloc_shape* shape,
                        uint64_t batch,
@@ -411,22 +386,6 @@ int gh_decode_noalloc( const gh_noalloc_shape* shape,
                        void* stream );
 /* Message of the calling thread's most recent gh_decode_noalloc failure ("" after a success). */
 const char* gh_decode_noalloc_error( void );
-
-/* Host-only (touches no device): the split plan gh_attn_batch_begin makes for token positions `pos`
- * (UINT32_MAX marks an inactive prompt).  `blocks_per_item` is the number of thread blocks a work item fans out
- * to (kv heads for the tensor-core kernel).  Writes n_items records {context, t_begin, t_end, split} to
- * items_out (room for max_items) and the split length to *chunk.  No reference counterpart: the reference
- * loops over the batch on the host and launches per context (src/arch/cuda/llama2/ops.cuh:272-453). */
-int gh_plan_batch( uint32_t blocks_per_item,
-                   uint32_t sm_count,
-                   uint32_t tile,
-                   uint32_t fixed_chunk,
-                   uint32_t max_items,
-                   uint64_t batch,
-                   const uint32_t* pos,
-                   int32_t* items_out,
-                   uint32_t* n_items,
-                   uint32_t* chunk );
 
 #ifdef __cplusplus
 }
