@@ -269,3 +269,48 @@ def test_reference_operations_on_own_slots_share_one_description(oracle, paged):
                          rng.standard_normal(cur.q.shape).astype(cur.q.dtype),
                          rng.standard_normal(cur.kv_new.shape).astype(cur.kv_new.dtype), cur.fcr, cur.fci)
     st.close()
+
+
+def test_consecutive_calls_execute_in_order_although_launches_overlap():
+    """Every kernel of the path is launched as a programmatic dependent of the one before it, so that its blocks are
+    placed while the last blocks of the previous kernel still run.  Calls must still execute strictly one after the
+    other: here layer 1 takes layer 0's OUTPUT buffer as its q (rotated in place by layer 1's append) and writes its
+    own output over layer 0's q, on the full 256-context batch; the result must be what the same calls give with the
+    device drained between them."""
+    wl = WORKLOADS["llama2_70b_gqa"]
+    sh = wl.shape
+    lens = wl.lengths(20240, headroom=4).astype(np.uint32)
+    B = len(lens)
+
+    def run(drain: bool):
+        st = AttentionStage(sh, torch.float16, n_layers_hosted=2, max_batch=B, max_contexts=B, paged=True)
+        cos, sin = rope_tables(sh.head_size, sh.seq_len, sh.rope_theta)
+        st.set_rope_tables(torch.from_numpy(cos).cuda().half(), torch.from_numpy(sin).cuda().half())
+        slots = st.get_contexts(np.arange(1, B + 1, dtype=np.uint32))
+        row = 2 * sh.kv_dim
+        for i in range(B):
+            for l in range(2):
+                st.prepare(int(slots[i]), l, int(lens[i]))
+                st.fill_normal(st.layer_ptr(int(slots[i]), l), int(lens[i]) * row, torch.float16, 3,
+                               offset=(2 * i + l) * sh.seq_len * row)
+        a = torch.empty((B, sh.dim), dtype=torch.float16, device="cuda")
+        b = torch.zeros_like(a)
+        kv = torch.empty((B, row), dtype=torch.float16, device="cuda")
+        st.fill_normal(a, a.numel(), torch.float16, 4)
+        st.fill_normal(kv, kv.numel(), torch.float16, 5)
+        torch.cuda.synchronize()
+        st.batch_begin(slots, lens)
+        st.step(0, a, kv, b)      # q = a, output -> b
+        if drain:
+            torch.cuda.synchronize()
+        st.step(1, b, kv, a)      # q = layer 0's output, output -> over layer 0's q
+        torch.cuda.synchronize()
+        assert st.stats().device_error == 0
+        out = (a.clone(), b.clone())
+        st.close()
+        return out
+
+    a0, b0 = run(drain=True)
+    a1, b1 = run(drain=False)
+    assert torch.equal(a0, a1) and torch.equal(b0, b1)
+    assert torch.isfinite(a0.float()).all() and float(a0.float().abs().max()) > 0
