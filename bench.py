@@ -24,8 +24,9 @@ Printed (rank 0, one JSON line):
   parity    the CUDA path against the CPU checker on the bench's own configuration, untimed
   cpu_baseline  the reference's own amd64/OpenMP operations (or the C restatement when that library is absent)
             timed on this host's cores on one layer-step of the same workload
-  producer, prefill   short extra regions (N = 1): the stage's fused producer on this workload, and the prompt-chunk
-            kernel on the Llama3-8B mixed configuration
+  producer, prefill, other_configs   short extra regions (N = 1): the stage's fused producer on this workload, the
+            prompt-chunk kernel on the Llama3-8B mixed configuration, and one layer-step each of the Llama2-7B,
+            Llama2-13B and Llama3-8B decode configurations
 
 `--impl reference` times only the CPU path, as a separate run with the same metric and configuration.
 """
@@ -422,6 +423,17 @@ def main():
         out["prefill"] = {"workload": pf_wl.name, "ms_per_step": pf["ms_per_step"], "tokens_s": pf["value"],
                           "dtype": pf_wl.dtype + " (checked against the C restatement with bf16 storage: the reference's "
                                                  "amd64 backend has no bf16)", **pf["prefill"]}
+        # ---- and one layer each of the other benchmark configurations (the decode kernel on their shapes) ----
+        others = {}
+        for name in ("llama2_7b_layer", "llama2_13b", "llama3_8b_decode"):
+            o_wl = WORKLOADS[name]
+            o = run_workload(pf_args, o_wl, 1, o_wl.batch, env, main_line=False, extras=False)
+            others[name] = {"contexts": o_wl.batch, "layers_run": 1, "layers_of_the_configuration": o_wl.n_layers,
+                            "dtype": o_wl.dtype, "ms_per_layer_step": o["ms_per_step"],
+                            "kv_streamed_gb": o["run"]["kv_streamed_per_layer_step_gb"],
+                            "decode_kernel": o["roofline"]["kernel"], "decode_gbs": o["roofline"]["achieved"],
+                            "decode_frac_of_measured_hbm": o["roofline"]["frac"]}
+        out["other_configs"] = others
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
