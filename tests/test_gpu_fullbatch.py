@@ -314,3 +314,28 @@ def test_consecutive_calls_execute_in_order_although_launches_overlap():
     a1, b1 = run(drain=False)
     assert torch.equal(a0, a1) and torch.equal(b0, b1)
     assert torch.isfinite(a0.float()).all() and float(a0.float().abs().max()) > 0
+
+
+def test_copy_and_rope_in_one_call_on_foreign_rows(oracle):
+    """gh_op_copy_kv_cache_apply_rope with token rows that are NOT in the stage's slots (plain device buffers): the
+    pointer array travels to the device with the call, the result is that of the two operations."""
+    case = cases.make_case("foreign_rows", "mini_g4", cases.BF16, [3, 200, 77, 510], seed=12, inactive=[1])
+    want = oracle.layer_step(case)
+    st = gpu_util.make_stage(case)
+    rows_d = torch.full((case.B, 2 * case.shape.kv_dim), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ptrs = [rows_d[i].data_ptr() if case.active[i] else 0 for i in range(case.B)]
+    q = gpu_util.to_dev(case.q, case.dtype)
+    q_before = q.clone()
+    st.copy_kv_cache_apply_rope(case.B, case.pos, gpu_util.to_dev(case.fcr, case.dtype), gpu_util.to_dev(case.fci, case.dtype),
+                                q, ptrs, gpu_util.to_dev(case.kv_new, case.dtype))
+    torch.cuda.synchronize()
+    got_rows, got_q = gpu_util.to_host(rows_d, case.dtype), gpu_util.to_host(q, case.dtype)
+    kvd = case.shape.kv_dim
+    for i in range(case.B):
+        if not case.active[i]:
+            assert torch.isnan(rows_d[i].float()).all() and torch.equal(q[i], q_before[i]), "inactive prompt untouched"
+            continue
+        assert np.array_equal(got_rows[i][kvd:], want.rows[i][kvd:]), "V bit-exact"
+        gpu_util.assert_rotation_close(got_rows[i][:kvd], want.rows[i][:kvd], case.kv_new[i][:kvd], case.dtype, f"K {i}")
+        gpu_util.assert_rotation_close(got_q[i], want.q[i], case.q[i], case.dtype, f"q {i}")
+    st.close()
