@@ -799,8 +799,8 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
                   "contexts_cut": s_stats.last_split_contexts,
                   "decode_ms_per_launch": d_ms, "decode_gbs": d_bytes / (d_ms / 1e3) / 1e9,
                   "decode_frac_of_measured_hbm": d_bytes / (d_ms / 1e3) / 1e9 / peak,
-                  "note": "rank 0's figures for work items, cuts and the decode launch (which includes the merge launch "
-                          "when contexts are cut); efficiency = (N=1 step time / N) / this step time"}
+                  "note": "rank 0's figures for work items, cuts and the decode launch (the blocks of a cut context "
+                          "combine their records inside it); efficiency = (N=1 step time / N) / this step time"}
         if args.strong_share:
             strong["note"] += "; emulated on one GPU: this rank's share only"
 
