@@ -104,6 +104,7 @@ struct gh_attn
   // The batch the gh_op_* calls were last made for, when their pointer arrays named rows of this handle's own slots
   // (every layer of a step names the same slots and positions): its uploaded description is reused.
   int op_entry = -1;
+  cudaStream_t op_stream = nullptr; // the stream its upload was issued on: only calls on that stream are ordered behind it
   uint32_t op_items = 0, op_split = 0;
   std::vector<int32_t> op_slots, op_slots_tmp;
   std::vector<uint32_t> op_pos, op_pos_tmp;
@@ -1270,7 +1271,7 @@ bool resolve_own_rows( gh_attn* h, uint64_t batch, const void* const* ptrs, cons
 // call's, else a fresh plan and upload.
 int op_batch_entry( gh_attn* h, uint64_t batch, cudaStream_t st )
 {
-  if ( h->op_entry >= 0 && h->op_slots == h->op_slots_tmp && h->op_pos == h->op_pos_tmp )
+  if ( h->op_entry >= 0 && h->op_stream == st && h->op_slots == h->op_slots_tmp && h->op_pos == h->op_pos_tmp )
     return GH_OK;
   h->op_entry = -1;
   std::vector<CtxMeta> ctx( batch );
@@ -1283,6 +1284,7 @@ int op_batch_entry( gh_attn* h, uint64_t batch, cudaStream_t st )
   if ( const int rc = plan_and_upload( h, ctx, st, &entry, &h->op_items, &h->op_split, RING_OP ); rc != GH_OK )
     return rc;
   h->op_entry = entry;
+  h->op_stream = st;
   h->op_slots.swap( h->op_slots_tmp );
   h->op_pos.swap( h->op_pos_tmp );
   return GH_OK;

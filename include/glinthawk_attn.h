@@ -182,7 +182,8 @@ size_t gh_slot_bytes( gh_attn_t h );
  * (src/models/llama2/model.hh:446-477, 611-628): records slot and token position of every prompt of the
  * batch (host arrays, as the reference's ScratchPad keeps them, src/models/llama2/base.hh:197-202), plans
  * the splits of long contexts and uploads the batch description on `stream`.  slot -1 = inactive prompt.
- * The per-layer calls below refer to the batch set up last. */
+ * The per-layer calls below refer to the batch set up last; a per-layer call on another stream than `stream` must
+ * be ordered behind the upload by the caller (an event recorded on `stream` after this call). */
 int gh_attn_batch_begin( gh_attn_t h, uint64_t batch, const int32_t* slots, const uint32_t* pos, void* stream );
 
 /* copy_kv_cache + apply_rope in one kernel (src/arch/amd64/llama2/ops.hh:335-352 and :300-333; order of

@@ -19,8 +19,9 @@ Two things stand between GCC 13 and the reference headers, and both are handled 
 Flavours: ``native`` uses the reference's own flags (``etc/cflags.cmake``: -O3 -march=native -ffast-math
 -fsingle-precision-constant, plus OpenMP); ``v4`` and ``v3`` swap -march=native for -march=x86-64-v4 (AVX-512) and
 -march=x86-64-v3 (AVX2) so that a library still loads on a host whose CPU lacks the build host's extensions.
-``load_ref()`` picks ``native`` only when the running CPU advertises every flag the build host had, else the
-widest of the other two that the CPU can run.
+``load_ref()`` picks ``native`` only when the running CPU advertises every instruction-set extension the build host
+had (flags that do not stand for compiler-generated instructions are not compared), else the widest of the other
+two that the CPU can run.
 
 The reference tree is looked for where the environment variable GLINTHAWK_REFERENCE points, else in a directory
 named ``reference`` beside the repository; when neither exists nothing is built and prebuilt libraries are used.
@@ -46,6 +47,14 @@ _REF_FLAGS = ["-std=c++20", "-O3", "-DNDEBUG", "-ffast-math", "-fsingle-precisio
 _TEMPLATE_HEAD = "template<typename Config, typename DType, typename ContextType>"
 _MARCH = {"native": "-march=native", "v4": "-march=x86-64-v4", "v3": "-march=x86-64-v3"}
 _V4_FLAGS = {"avx512f", "avx512bw", "avx512cd", "avx512dq", "avx512vl"}
+# /proc/cpuinfo flags that stand for instructions a compiler emits on its own under -march=native (vector, bit
+# manipulation and conversion extensions).  The rest of the list (rtm, pku, hypervisor and mitigation flags, ...) says
+# nothing about whether code built on one host runs on another.
+_CODEGEN_FLAGS = {"pni", "ssse3", "sse4_1", "sse4_2", "popcnt", "abm", "movbe", "bmi1", "bmi2", "adx", "avx", "avx2", "fma",
+                  "f16c", "avx_vnni", "avx512f", "avx512dq", "avx512cd", "avx512bw", "avx512vl", "avx512ifma",
+                  "avx512vbmi", "avx512_vbmi2", "avx512_vnni", "avx512_bitalg", "avx512_vpopcntdq", "avx512_bf16",
+                  "avx512_fp16", "gfni", "vaes", "vpclmulqdq", "pclmulqdq", "aes", "sha_ni", "lahf_lm", "cx16",
+                  "amx_tile", "amx_int8", "amx_bf16"}
 
 
 def _cpu_flags() -> list[str]:
@@ -215,7 +224,7 @@ def ref_flavour() -> str | None:
     info = REF_OUT / "BUILD_INFO.json"
     have = set(_cpu_flags())
     if native.exists() and info.exists():
-        need = set(json.loads(info.read_text()).get("native_cpu_flags", []))
+        need = set(json.loads(info.read_text()).get("native_cpu_flags", [])) & _CODEGEN_FLAGS
         if need and need <= have:
             return "native"
     if v4.exists() and _V4_FLAGS <= have:
