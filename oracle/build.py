@@ -234,8 +234,24 @@ def ref_flavour() -> str | None:
     return None
 
 
-def load_ref() -> ctypes.CDLL | None:
-    fl = ref_flavour()
+def runnable_flavours() -> list[str]:
+    """Every prebuilt reference library this host's CPU can run, widest instruction set first."""
+    have = set(_cpu_flags())
+    out = []
+    info = REF_OUT / "BUILD_INFO.json"
+    if (REF_OUT / "libghref_native.so").exists() and info.exists():
+        need = set(json.loads(info.read_text()).get("native_cpu_flags", [])) & _CODEGEN_FLAGS
+        if need and need <= have:
+            out.append("native")
+    if (REF_OUT / "libghref_v4.so").exists() and _V4_FLAGS <= have:
+        out.append("v4")
+    if (REF_OUT / "libghref_v3.so").exists():
+        out.append("v3")
+    return out
+
+
+def load_ref(flavour: str | None = None) -> ctypes.CDLL | None:
+    fl = flavour or ref_flavour()
     return ctypes.CDLL(str(REF_OUT / f"libghref_{fl}.so")) if fl else None
 
 

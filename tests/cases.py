@@ -221,9 +221,9 @@ class Reference:
         self.names = [lib.ghref_shape_name(i).decode() for i in range(lib.ghref_shape_count())]
 
     @classmethod
-    def try_load(cls):
-        lib = oracle_build.load_ref()
-        return cls(lib, oracle_build.ref_flavour() or "") if lib is not None else None
+    def try_load(cls, flavour: str | None = None):
+        lib = oracle_build.load_ref(flavour)
+        return cls(lib, flavour or oracle_build.ref_flavour() or "") if lib is not None else None
 
     def threads(self) -> int:
         return self.lib.ghref_threads()
