@@ -70,6 +70,7 @@ _PROTOS = {
     "gh_plan_projection": (C.c_int, [_U32, _U32, _U32, _U32, _P, _P, _U32, _P]),
     "gh_op_project_append": (C.c_int, [_P, _U64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "gh_attn_forward_attention_host": (C.c_int, [_P, _U32, _U32, _P, _P, _P, _P]),
+    "gh_attn_forward_attention_state": (C.c_int, [_P, _U32, _P, C.c_size_t, _P]),
     "gh_op_copy_kv_cache": (C.c_int, [_P, _P, _P, _U64, _P]),
     "gh_op_apply_rope": (C.c_int, [_P, _U64, _P, _P, _P, _P, _P, _P]),
     "gh_op_copy_kv_cache_apply_rope": (C.c_int, [_P, _U64, _P, _P, _P, _P, _P, _P, _P]),

@@ -1199,6 +1199,67 @@ int gh_attn_forward_attention_host( gh_attn_t h,
   return GH_OK;
 }
 
+static_assert( sizeof( gh_wire_metadata ) == 32 && sizeof( gh_wire_prompt ) == 57, "wire structs must stay packed" );
+
+int gh_attn_forward_attention_state( gh_attn_t h, uint32_t first_layer_hosted, void* state, size_t state_bytes, void* stream )
+{
+  if ( h == nullptr || state == nullptr || state_bytes < sizeof( gh_wire_metadata ) )
+    return fail( h, GH_ERR_INVALID, "no state, or too short for its metadata" );
+  char* bytes = static_cast<char*>( state );
+  gh_wire_metadata md;
+  std::memcpy( &md, bytes, sizeof( md ) );
+  if ( md.batch_size == 0 || md.batch_size > h->cfg.max_batch || !dtype_ok( md.dtype ) )
+    return fail( h, GH_ERR_INVALID, "state with a batch size or dtype this stage does not take" );
+  if ( md.next_stage != GH_STAGE_ATTENTION )
+    return fail( h, GH_ERR_STATE, "the state's next stage is not attention" );
+  if ( md.has_queries == 0 || md.has_kvs == 0 )
+    return fail( h, GH_ERR_UNSUPPORTED, "the state carries no queries or no key-values" );
+  if ( md.next_layer < first_layer_hosted || md.next_layer - first_layer_hosted >= h->sh.n_layers )
+    return fail( h, GH_ERR_INVALID, "layer " + std::to_string( md.next_layer ) + " is not hosted" );
+  const uint32_t layer = md.next_layer - first_layer_hosted;
+  const size_t B = md.batch_size, sz = dtype_size( md.dtype );
+  const size_t dim = static_cast<size_t>( h->sh.n_heads ) * h->sh.head_size;
+  const size_t off_prompts = sizeof( gh_wire_metadata );
+  const size_t off_act = off_prompts + B * sizeof( gh_wire_prompt );
+  const size_t off_q = off_act + ( md.has_activations != 0 ? B * dim * sz : 0 );
+  const size_t off_kv = off_q + B * dim * sz;
+  if ( off_kv + B * h->sh.row_elems * sz != state_bytes )
+    return fail( h, GH_ERR_INVALID, "state of " + std::to_string( state_bytes ) + " bytes, its metadata describes "
+                                      + std::to_string( off_kv + B * h->sh.row_elems * sz ) );
+
+  // get_contexts: every active prompt's slot, all or nothing (contextman.hh:127-171)
+  std::vector<uint32_t> ids( B ), pos( B );
+  std::vector<int32_t> slots( B );
+  for ( size_t i = 0; i < B; i++ ) {
+    gh_wire_prompt pr;
+    std::memcpy( &pr, bytes + off_prompts + i * sizeof( gh_wire_prompt ), sizeof( pr ) );
+    ids[i] = pr.active != 0 ? pr.context_id : 0u;
+    pos[i] = pr.token_pos;
+  }
+  if ( const int rc = h->pool.acquire_batch( B, ids.data(), slots.data() ); rc != GH_OK )
+    return fail( h, rc, "not enough free context slots for the state's prompts" );
+  DeviceGuard guard( h->device );
+  for ( size_t i = 0; i < B; i++ ) {
+    if ( slots[i] < 0 )
+      continue;
+    // Context::prepare( next_layer, token_pos, token_pos == 0 && first_layer_served == next_layer ), model.hh:617-621
+    const int rc = h->pool.prepare( slots[i], layer, pos[i], pos[i] == 0 && layer == 0, h->err );
+    if ( rc != GH_OK )
+      return rc == GH_ERR_CAPACITY ? fail( h, rc, "token position beyond slot capacity in the state" ) : rc;
+  }
+  if ( const int rc = gh_attn_batch_begin( h, B, slots.data(), pos.data(), stream ); rc != GH_OK )
+    return rc;
+  // q in, new [K,V] rows in, attention output back over the queries buffer (model.hh:697-722)
+  if ( const int rc = gh_attn_forward_attention_host( h, layer, md.dtype, bytes + off_q, bytes + off_kv, bytes + off_q, stream );
+       rc != GH_OK )
+    return rc;
+  if ( const int rc = gh_attn_synchronize( h, stream ); rc != GH_OK )
+    return rc;
+  md.next_stage = GH_STAGE_POST_ATTENTION;
+  std::memcpy( bytes, &md, sizeof( md ) );
+  return GH_OK;
+}
+
 // ---- the reference's operations, argument for argument -------------------------------------------------
 
 namespace {

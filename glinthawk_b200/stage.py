@@ -201,6 +201,11 @@ class AttentionStage:
         self._ck(lib.gh_attn_forward_attention_host(self._h, layer, dtype_code(io_dtype), _ptr(q_host), _ptr(kv_host),
                                                     _ptr(xb_host), _stream(stream)))
 
+    def forward_attention_state(self, state: np.ndarray, first_layer_hosted: int = 0, stream=None) -> None:
+        """Llama2::forward_attention on a serialized BatchedInferenceState (a writable uint8 array), in place."""
+        assert state.dtype == np.uint8 and state.flags.c_contiguous and state.flags.writeable
+        self._ck(lib.gh_attn_forward_attention_state(self._h, first_layer_hosted, _ptr(state), state.nbytes, _stream(stream)))
+
     # -- the reference's operations, argument for argument -------------------------------------------
     @staticmethod
     def _ptr_array(ptrs) -> np.ndarray:

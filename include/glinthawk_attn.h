@@ -256,6 +256,68 @@ int gh_attn_forward_attention_host( gh_attn_t h,
                                     void* xb_host,
                                     void* stream );
 
+/* ---- the wire format: a serialized BatchedInferenceState ------------------------------------------- */
+
+/* What travels between Glinthawk's workers: BatchedInferenceState::serialize() (src/models/common/state.hh:561-594)
+ * = StateMetadata, then batch_size x PromptData, then the activations, queries and key-values buffers that the
+ * metadata says are present, each [batch_size][row] of the state's dtype.  The two structs below restate the
+ * reference's packed structs field for field (state.hh:17-50; PromptID is a 32-byte SHA-256, src/util/digest.hh:15-18;
+ * stage codes are InferenceStage, src/models/types.hh:29-38). */
+#pragma pack( push, 1 )
+typedef struct gh_wire_metadata
+{
+  uint64_t id;
+  uint32_t batch_size;
+  uint8_t dtype; /* gh_dtype */
+  uint32_t route_id;
+  uint32_t model_id;
+  uint32_t next_layer;
+  uint8_t next_stage; /* gh_stage */
+  int8_t next_tier;
+  uint8_t next_rank;
+  uint8_t has_activations;
+  uint8_t has_queries;
+  uint8_t has_kvs;
+  uint8_t is_sharded;
+} gh_wire_metadata; /* 32 bytes */
+
+typedef struct gh_wire_prompt
+{
+  uint8_t active;
+  uint8_t prompt_id[32];
+  uint32_t context_id;
+  uint32_t token;
+  uint32_t token_pos;
+  uint8_t temperature;
+  uint32_t prompt_length;
+  uint32_t max_completion_length;
+  uint8_t finished;
+  int8_t kv_tier;
+  uint8_t kv_rank;
+} gh_wire_prompt; /* 57 bytes */
+#pragma pack( pop )
+
+typedef enum gh_stage
+{
+  GH_STAGE_PRE_ATTENTION = 0,
+  GH_STAGE_ATTENTION = 1,
+  GH_STAGE_POST_ATTENTION = 2,
+  GH_STAGE_CLASSIFICATION = 3
+} gh_stage;
+
+/* Llama2::forward_attention( states, contexts ) on the serialized state itself (src/models/llama2/model.hh:611-725,
+ * with the context look-up of PreallocatingContextManager::get_contexts, src/compute/contextman.hh:127-171, done
+ * here): `state` holds state_bytes of BatchedInferenceState::serialize() output with next_stage == Attention,
+ * queries and key-values present.  For every active prompt the slot bound to its context_id is looked up (bound on
+ * first use), prepared for token_pos (a prompt at position 0 of the first hosted layer starts its slot afresh,
+ * model.hh:617-621), its new [K,V] row is appended and the attention output computed; inactive prompts are skipped.
+ * The result is written where the reference writes it: over the queries buffer (model.hh:697-722), and next_stage
+ * becomes PostAttention; everything else in `state` is left as it is, so the bytes are again a valid serialized
+ * state.  `first_layer_hosted` is the model layer that hosted layer 0 stands for (next_layer is a model layer).
+ * Blocking, like the reference's (it copies with cudaMemcpy); replaces the batch set up by gh_attn_batch_begin.
+ * The state's dtype may differ from the handle's (the reference mixes fp16 pre-/post-attention with fp32 attention). */
+int gh_attn_forward_attention_state( gh_attn_t h, uint32_t first_layer_hosted, void* state, size_t state_bytes, void* stream );
+
 /* ---- the reference's five operations, argument for argument --------------------------------------- */
 /* `token_rows` / `layer_bases` are HOST arrays of device pointers (what TokenContext::key() and
  * LayerContext::token(0).key() return); a null entry means "inactive, skip" (ops.hh:195,250,314,344).

@@ -13,6 +13,7 @@
  * forward pass, the logits of every prompt and the chosen tokens, and at the end the KV cache of every context.
  * tests/test_gpu_model.py compares the two runs.
  */
+#include <cstddef>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -151,6 +152,21 @@ int run( const std::string& model_dir, const std::string& prompts_path, const in
   std::printf( "%u contexts, %u forward passes\n", B, steps );
   return 0;
 }
+
+// The wire format of gh_attn_forward_attention_state is the reference's own: the restated structs must match the
+// reference's packed structs byte for byte (src/models/common/state.hh:17-50).
+namespace wire = glinthawk::models;
+static_assert( sizeof( gh_wire_metadata ) == sizeof( wire::StateMetadata ) && sizeof( gh_wire_prompt ) == sizeof( wire::PromptData ) );
+static_assert( offsetof( gh_wire_metadata, dtype ) == offsetof( wire::StateMetadata, dtype )
+               && offsetof( gh_wire_metadata, next_layer ) == offsetof( wire::StateMetadata, next_layer )
+               && offsetof( gh_wire_metadata, next_stage ) == offsetof( wire::StateMetadata, next_stage )
+               && offsetof( gh_wire_metadata, has_queries ) == offsetof( wire::StateMetadata, has_queries )
+               && offsetof( gh_wire_metadata, is_sharded ) == offsetof( wire::StateMetadata, is_sharded ) );
+static_assert( offsetof( gh_wire_prompt, context_id ) == offsetof( wire::PromptData, context_id )
+               && offsetof( gh_wire_prompt, token_pos ) == offsetof( wire::PromptData, token_pos )
+               && offsetof( gh_wire_prompt, kv_rank ) == offsetof( wire::PromptData, kv_rank ) );
+static_assert( GH_STAGE_ATTENTION == static_cast<int>( wire::InferenceStage::Attention )
+               && GH_STAGE_POST_ATTENTION == static_cast<int>( wire::InferenceStage::PostAttention ) );
 
 int main( int argc, char** argv )
 {
