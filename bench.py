@@ -440,15 +440,22 @@ def main():
                                         "strong_share": "", "static": False, "decode_chunk": 0, "force_generic": False,
                                         "pipeline_steps": False, "overlap_prefill": False})
         pf_wl = WORKLOADS["llama3_8b_mixed"]
-        pf = run_workload(pf_args, pf_wl, pf_wl.n_layers, pf_wl.batch, env, main_line=False, extras=False)
-        out["prefill"] = {"workload": pf_wl.name, "ms_per_step": pf["ms_per_step"], "tokens_s": pf["value"],
-                          "dtype": pf_wl.dtype + " (checked against the C restatement with bf16 storage: the reference's "
-                                                 "amd64 backend has no bf16)", **pf["prefill"]}
+        try:
+            pf = run_workload(pf_args, pf_wl, pf_wl.n_layers, pf_wl.batch, env, main_line=False, extras=False)
+            out["prefill"] = {"workload": pf_wl.name, "ms_per_step": pf["ms_per_step"], "tokens_s": pf["value"],
+                              "dtype": pf_wl.dtype + " (checked against the C restatement with bf16 storage: the "
+                                                     "reference's amd64 backend has no bf16)", **pf["prefill"]}
+        except Exception as e:  # noqa: BLE001  (an extra region must not take the main figures down with it)
+            out["prefill"] = {"error": f"{type(e).__name__}: {e}"[:400]}
         # ---- and one layer each of the other benchmark configurations (the decode kernel on their shapes) ----
         others = {}
         for name in ("llama2_7b_layer", "llama2_13b", "llama3_8b_decode"):
             o_wl = WORKLOADS[name]
-            o = run_workload(pf_args, o_wl, 1, o_wl.batch, env, main_line=False, extras=False)
+            try:
+                o = run_workload(pf_args, o_wl, 1, o_wl.batch, env, main_line=False, extras=False)
+            except Exception as e:  # noqa: BLE001
+                others[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+                continue
             others[name] = {"contexts": o_wl.batch, "layers_run": 1, "layers_of_the_configuration": o_wl.n_layers,
                             "dtype": o_wl.dtype, "ms_per_layer_step": o["ms_per_step"],
                             "kv_streamed_gb": o["run"]["kv_streamed_per_layer_step_gb"],
@@ -637,6 +644,21 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
         mine = a.elapsed_time(b) / steps
         return dist_util.max_over_ranks(mine, dev), mine
 
+    def guarded(fn):
+        """A region behind the main one must not take the headline figures down with it.  With one rank a failure
+        becomes an {"error": ...} entry; with several ranks an exception cannot be contained (the other ranks would
+        wait in the next barrier), so it propagates."""
+        if world > 1:
+            return fn()
+        try:
+            return fn()
+        except Exception as e:  # noqa: BLE001
+            try:
+                torch.cuda.synchronize()
+            except Exception:  # noqa: BLE001
+                pass
+            return {"error": f"{type(e).__name__}: {e}"[:400]}
+
     def gather(value: float) -> list[float]:
         if world == 1:
             return [float(value)]
@@ -763,8 +785,7 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
         del q_h, kv_h, xb_h
 
     # ---- the reference's call sequence: host arrays of row pointers, operation by operation ----
-    via_ops = None
-    if do_via_ops:
+    def region_via_ops():
         row_bytes = row_elems * elem
         base_ptrs = [np.array([stage.layer_ptr(int(s), l) for s in slots], dtype=np.uint64) for l in range(n_layers)]
         cos_p, sin_p = C.c_void_p(cos_d.data_ptr()), C.c_void_p(sin_d.data_ptr())
@@ -781,13 +802,14 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
             pos[:] += 1
 
         ops_ms, _ = timed(ops_step, extra_steps)
-        via_ops = {"ms_per_step": ops_ms, "tokens_s": batch * world / (ops_ms / 1e3), "over_value": ops_ms / ms_per_step,
+        return {"ms_per_step": ops_ms, "tokens_s": batch * world / (ops_ms / 1e3), "over_value": ops_ms / ms_per_step,
                    "sequence": "per layer: gh_op_copy_kv_cache_apply_rope (the adapter holds copy_kv_cache back until "
                                "apply_rope names the same rows) + gh_op_attention_fused, host pointer arrays"}
 
+    via_ops = guarded(region_via_ops) if do_via_ops else None
+
     # ---- strong scaling: ONE set of requests divided among the ranks by cached tokens ----
-    strong = None
-    if do_strong:
+    def region_strong():
         n_div, r_div = world, rank
         if args.strong_share:
             r_div, n_div = (int(v) for v in args.strong_share.split("/"))
@@ -824,6 +846,9 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
                           "combine their records inside it); efficiency = (N=1 step time / N) / this step time"}
         if args.strong_share:
             strong["note"] += "; emulated on one GPU: this rank's share only"
+        return strong
+
+    strong = guarded(region_strong) if do_strong else None
 
     # ---- stage hand-off between GPUs: q and K/V rows in, xb out, over NCCL point-to-point ----
     handoff = None
@@ -832,23 +857,23 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
                                  ms_per_step, lambda l: ck(ghlib.gh_attn_step(handle, l, q_ptr[l], kv_ptr[l], xb_ptr[l], st_ptr)))
 
     # ---- short extra region: the stage's producer in front of every layer-step ----
+    def region_producer():
+        producer_events.clear()
+        rec = []
+        device_step(producer=True)
+        p_ms, _ = timed(lambda: device_step(rec, producer=True), extra_steps, warm=1)
+        res = producer_summary(producer_events, sh, row_elems, elem, batch, peak)
+        res["ms_per_step_with_producer"] = p_ms
+        res["weights_resident"] = f"{n_w} layers' matrices, cycled ({n_w * (sh.dim + row_elems) * sh.dim * elem / 1e9:.2f} GB)"
+        return res
+
     if do_producer_extra:
-        from glinthawk_b200.stage import GlinthawkAttnError
-        try:
-            producer_events.clear()
-            rec = []
-            device_step(producer=True)
-            p_ms, _ = timed(lambda: device_step(rec, producer=True), extra_steps, warm=1)
-            producer = producer_summary(producer_events, sh, row_elems, elem, batch, peak)
-            producer["ms_per_step_with_producer"] = p_ms
-            producer["weights_resident"] = (f"{n_w} layers' matrices, cycled "
-                                            f"({n_w * (sh.dim + row_elems) * sh.dim * elem / 1e9:.2f} GB)")
-        except GlinthawkAttnError as e:  # shapes the fused projection does not take
-            producer = {"unavailable": str(e)}
+        producer = guarded(region_producer)  # (an {"error": ...} entry for shapes the fused projection does not take)
 
     stats = stage.stats()
     if stats.device_error:
         raise SystemExit(f"device error flag {stats.device_error}")
+    stage.synchronize()
 
     # ---- CPU checker and CPU baseline on this workload's own inputs ----
     parity, cpu = None, None
@@ -861,9 +886,9 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
                 from tests import cases
                 checker, kind = cases.Oracle(), "port"
                 case = cases.make_case("cpu_sample", sh.name, DT_CODE["bf16"], case.pos, args.seed)
-            parity = parity_check(stage, wl, case, checker, kind, first_id=batch + n_pf + 1)
+            parity = guarded(lambda: parity_check(stage, wl, case, checker, kind, first_id=batch + n_pf + 1))
         if world == 1 and not args.no_cpu_baseline and plain:
-            cpu = time_cpu_sample(wl, case, batch, n_layers, reps=3)
+            cpu = guarded(lambda: time_cpu_sample(wl, case, batch, n_layers, reps=3))
 
     out = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
