@@ -441,8 +441,9 @@ def main():
                                         "pipeline_steps": False, "overlap_prefill": False})
         pf_wl = WORKLOADS["llama3_8b_mixed"]
         try:
-            pf = run_workload(pf_args, pf_wl, pf_wl.n_layers, pf_wl.batch, env, main_line=False, extras=False)
+            pf = run_workload(pf_args, pf_wl, pf_wl.n_layers, pf_wl.batch, env, main_line=False, extras=False, parity_too=True)
             out["prefill"] = {"workload": pf_wl.name, "ms_per_step": pf["ms_per_step"], "tokens_s": pf["value"],
+                              "decode_parity": pf["parity"],
                               "dtype": pf_wl.dtype + " (checked against the C restatement with bf16 storage: the "
                                                      "reference's amd64 backend has no bf16)", **pf["prefill"]}
         except Exception as e:  # noqa: BLE001  (an extra region must not take the main figures down with it)
@@ -468,7 +469,7 @@ def main():
         dist.destroy_process_group()
 
 
-def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: bool) -> dict:
+def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: bool, parity_too: bool = False) -> dict:
     import torch
     import torch.distributed as dist
 
@@ -487,7 +488,7 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
     do_via_ops = extras and plain
     do_strong = plain and (bool(args.strong_share) or (extras and world > 1))
     do_handoff = extras and plain and world > 1 and world % 2 == 0
-    do_parity = extras and plain and rank == 0
+    do_parity = ((extras and plain) or parity_too) and rank == 0
     do_producer_extra = extras and plain and world == 1 and wl.dtype != "f32"
     extra_steps = EXTRA_STEPS
     lens_global = wl.lengths(args.seed, headroom)[:batch]
@@ -495,7 +496,7 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
 
     # ---- set-up (untimed): slots, cached KV, inputs ----
     t_setup = time.perf_counter()
-    n_cpu = min(args.cpu_contexts or batch, batch) if world == 1 else min(48, batch)
+    n_cpu = min(args.cpu_contexts or batch, batch) if (world == 1 and main_line) else min(48, batch)
     stage = AttentionStage(sh, tdt, n_layers_hosted=n_layers, max_batch=max(batch, n_pf), device=local_rank,
                            max_contexts=batch + n_pf + (n_cpu if do_parity else 0), paged=not args.static,
                            decode_chunk=args.decode_chunk, pipeline_steps=args.pipeline_steps,
@@ -877,18 +878,23 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
 
     # ---- CPU checker and CPU baseline on this workload's own inputs ----
     parity, cpu = None, None
-    if (do_parity or (rank == 0 and world == 1 and not args.no_cpu_baseline and plain)) and main_line:
+    if do_parity or (rank == 0 and world == 1 and not args.no_cpu_baseline and plain and main_line):
         use_all_host_threads()
-        case, _ = cpu_sample_case(wl, lens_global, n_cpu, args.seed)
+        if wl.dtype == "bf16":  # the reference's amd64 backend has no bf16: the C restatement with bf16 storage checks
+            from tests import cases
+            sample = np.argsort(lens_global)[np.linspace(0, batch - 1, n_cpu).astype(int)]
+            case = cases.make_case("cpu_sample", sh.name, DT_CODE["bf16"], lens_global[sample].astype(np.uint32), args.seed)
+            checker, kind = cases.Oracle(), "port"
+        else:
+            case, _ = cpu_sample_case(wl, lens_global, n_cpu, args.seed)
+            if do_parity:
+                _, checker, kind, _, _ = cpu_runner(wl, case)
         if do_parity:
-            _, checker, kind, _, _ = cpu_runner(wl, case)
-            if wl.dtype == "bf16":
-                from tests import cases
-                checker, kind = cases.Oracle(), "port"
-                case = cases.make_case("cpu_sample", sh.name, DT_CODE["bf16"], case.pos, args.seed)
             parity = guarded(lambda: parity_check(stage, wl, case, checker, kind, first_id=batch + n_pf + 1))
-        if world == 1 and not args.no_cpu_baseline and plain:
-            cpu = guarded(lambda: time_cpu_sample(wl, case, batch, n_layers, reps=3))
+        if world == 1 and not args.no_cpu_baseline and plain and main_line:
+            # (for a bf16 workload the CPU arm times the reference's fp16 path: same bytes per element)
+            cpu_case = case if wl.dtype != "bf16" else cpu_sample_case(wl, lens_global, n_cpu, args.seed)[0]
+            cpu = guarded(lambda: time_cpu_sample(wl, cpu_case, batch, n_layers, reps=3))
 
     out = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
