@@ -477,8 +477,6 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
     from glinthawk_b200._lib import lib as ghlib
     from glinthawk_b200.rope import rope_tables
     from glinthawk_b200.stage import AttentionStage
-    from glinthawk_b200.workload import assign_contexts
-
     rank, world, local_rank, dev = env["rank"], env["world"], env["local_rank"], env["dev"]
     sh, elem = wl.shape, ELEM[wl.dtype]
     tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[wl.dtype]
@@ -814,12 +812,8 @@ def run_workload(args, wl, n_layers, batch, env, *, main_line: bool, extras: boo
         n_div, r_div = world, rank
         if args.strong_share:
             r_div, n_div = (int(v) for v in args.strong_share.split("/"))
-        mine = assign_contexts(lens_global, n_div)[r_div]
         # this rank holds the same multiset of lengths in its own order: the k-th shortest stands for the k-th shortest
-        order_global, order_local = np.argsort(lens_global, kind="stable"), np.argsort(lens0, kind="stable")
-        place = np.empty(batch, dtype=np.int64)
-        place[order_global] = np.arange(batch)
-        sel = np.sort(order_local[place[mine]])
+        sel = dist_util.strong_share_on_local_contexts(lens_global, lens0, r_div, n_div)
         strong_events = []
         device_step(sel=sel)
         tokens_mine = int((pos[sel].astype(np.int64) + 1).sum())

@@ -50,3 +50,17 @@ def strong_scaling_lengths(wl: Workload, seed: int, rank: int, world: int, headr
     lens = wl.lengths(seed, headroom)
     mine = assign_contexts(lens, world)[rank]
     return mine, lens[mine]
+
+
+def strong_share_on_local_contexts(lens_global, lens_local, share_of: int, n_shares: int) -> np.ndarray:
+    """A rank that already holds its own copy of the request set in another order (weak_scaling_lengths gives every
+    rank the same multiset of lengths, permuted) picks, among its local contexts, the ones that stand for share
+    `share_of` of the fixed request set divided `n_shares` ways: the k-th shortest local context stands for the k-th
+    shortest request.  Returns sorted local indices; their lengths are exactly the share's lengths."""
+    lens_global, lens_local = np.asarray(lens_global), np.asarray(lens_local)
+    mine = assign_contexts(lens_global, n_shares)[share_of]
+    order_global = np.argsort(lens_global, kind="stable")
+    order_local = np.argsort(lens_local, kind="stable")
+    place = np.empty(len(lens_global), dtype=np.int64)
+    place[order_global] = np.arange(len(lens_global))
+    return np.sort(order_local[place[mine]])

@@ -194,3 +194,19 @@ def test_reference_arm_under_torchrun_prints_one_line_from_rank_zero(tmp_path):
     assert out["impl"] == "reference" and out["n_gpus"] == 2 and out["value"] > 0
     assert out["cpu_baseline"]["kind"] in ("reference", "port") and out["e2e"]["h2d_bytes_per_step"] == 0
 
+
+
+def test_strong_share_is_found_among_a_rank_s_own_permuted_contexts():
+    wl = WORKLOADS["llama2_70b_gqa"]
+    lens = wl.lengths(20240, 40)
+    for world in (2, 4, 8):
+        covered = []
+        for rank in range(world):
+            local = dist_util.weak_scaling_lengths(wl, 20240, rank, 40)
+            sel = dist_util.strong_share_on_local_contexts(lens, local, rank, world)
+            want = np.sort(lens[assign_contexts(lens, world)[rank]])
+            assert np.array_equal(np.sort(local[sel]), want) and len(set(sel.tolist())) == len(sel)
+            covered.append(want)
+        assert np.array_equal(np.sort(np.concatenate(covered)), np.sort(lens)), "the shares make up the whole request set"
+        loads = [int((c + 1).sum()) for c in covered]
+        assert max(loads) - min(loads) <= lens.max() + 1
