@@ -56,12 +56,20 @@ __global__ void __launch_bounds__( 256 ) rmsnorm_kernel( T* __restrict__ out, co
 {
   constexpr int N = Vec16<T>::N;
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
-  // launched as a programmatic dependent of the kernel before it in the stream (its launch latency hides behind
-  // that kernel's tail); x and the scratch row may still be in use until that kernel has completed
-  asm volatile( "griddepcontrol.wait;" ::: "memory" );
   const T* X = x + (size_t)blockIdx.x * dim;
   T* O = out + (size_t)blockIdx.x * dim;
   const uint32_t pieces = dim / N; // dim is a multiple of 128
+  // the norm weights are model weights: nothing in the stream writes them, so they are fetched ahead of the wait
+  Vec16<T> wrow[kNormPieces];
+#pragma unroll
+  for ( int k = 0; k < kNormPieces; k++ ) {
+    const uint32_t p = threadIdx.x + k * 256;
+    if ( p < pieces )
+      wrow[k] = ld16( weight + (size_t)p * N );
+  }
+  // launched as a programmatic dependent of the kernel before it in the stream (its launch latency hides behind
+  // that kernel's tail); x and the scratch row may still be in use until that kernel has completed
+  asm volatile( "griddepcontrol.wait;" ::: "memory" );
   Vec16<T> row[kNormPieces];
   float ss = 0.f;
 #pragma unroll
@@ -93,11 +101,10 @@ __global__ void __launch_bounds__( 256 ) rmsnorm_kernel( T* __restrict__ out, co
   for ( int k = 0; k < kNormPieces; k++ ) {
     const uint32_t p = threadIdx.x + k * 256;
     if ( p < pieces ) {
-      const Vec16<T> w = ld16( weight + (size_t)p * N );
       Vec16<T> o;
 #pragma unroll
       for ( int e = 0; e < N; e++ )
-        o.v[e] = Conv<T>::from_f32( __fmul_rn( Conv<T>::to_f32( w.v[e] ), __fmul_rn( tot, Conv<T>::to_f32( row[k].v[e] ) ) ) );
+        o.v[e] = Conv<T>::from_f32( __fmul_rn( Conv<T>::to_f32( wrow[k].v[e] ), __fmul_rn( tot, Conv<T>::to_f32( row[k].v[e] ) ) ) );
       st16( O + (size_t)p * N, o );
     }
   }
@@ -306,13 +313,14 @@ __global__ void __launch_bounds__( kThreads, 1 )
 }
 
 constexpr int kFinishRows = 16; // batch rows per block of the finishing kernel
+constexpr int kFinishSegs = 3;  // pieces of a tile whose loads are in flight together
 
 // Second step of the projection: one block = (tile of 128 features, 16 batch rows); a thread owns one (even, odd)
 // feature pair and walks 4 of the rows.  It adds the tile's pieces in their fixed order (deterministic), rounds to the
 // storage type (the reference stores q and kv there), rotates q and K pairs by the row's position with separately
 // rounded products (src/arch/amd64/llama2/ops.hh:150-162) and writes q, or K/V straight into the slot row.
 template<typename T>
-__global__ void __launch_bounds__( 256, 4 ) project_finish_kernel( const ProjectArgs a )
+__global__ void __launch_bounds__( 256, 3 ) project_finish_kernel( const ProjectArgs a )
 {
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
   const int tile = blockIdx.x;
@@ -329,15 +337,15 @@ __global__ void __launch_bounds__( 256, 4 ) project_finish_kernel( const Project
   const float* tile_ws = a.ws + (size_t)tile * a.max_segs * slot_floats;
   const T* __restrict__ cos_t = static_cast<const T*>( a.rope_cos );
   const T* __restrict__ sin_t = static_cast<const T*>( a.rope_sin );
-  // the partial sums come from the projection kernel, the kernel before this one in the stream
-  asm volatile( "griddepcontrol.wait;" ::: "memory" );
-  // three rounds of independent loads (positions and row pointers, partial sums, table values), each with all of the
-  // thread's rows in flight
-  uint32_t pos[kFinishRows / 4];
-  T* row[kFinishRows / 4]; // the prompt's slot row at its position; nullptr = inactive prompt
-  float2 acc[kFinishRows / 4];
+  constexpr int R = kFinishRows / 4;
+  // First what the kernels before this one in the stream do not write (the batch description and the tables come
+  // from copies, which programmatic launches do not overtake): positions and row pointers, then the table values.
+  // Blocks that become resident while the projection still runs have these two rounds of loads behind them when it
+  // completes.
+  uint32_t pos[R];
+  T* row[R]; // the prompt's slot row at its position; nullptr = inactive prompt
 #pragma unroll
-  for ( int k = 0; k < kFinishRows / 4; k++ ) {
+  for ( int k = 0; k < R; k++ ) {
     const int i = blockIdx.y * kFinishRows + sub + 4 * k;
     pos[k] = 0;
     row[k] = nullptr;
@@ -352,23 +360,10 @@ __global__ void __launch_bounds__( 256, 4 ) project_finish_kernel( const Project
           row[k] = reinterpret_cast<T*>( a.arena + c.kv_off + a.layer_off ) + (size_t)c.pos * a.sh.row_elems;
       }
     }
-    acc[k] = make_float2( 0.f, 0.f );
   }
-  for ( int s = 0; s < nsegs; s++ ) { // fixed order: the same bits on every run
+  float cs[R], sn[R];
 #pragma unroll
-    for ( int k = 0; k < kFinishRows / 4; k++ ) {
-      const int i = blockIdx.y * kFinishRows + sub + 4 * k;
-      if ( i < batch ) {
-        const float2 part
-          = __ldcg( reinterpret_cast<const float2*>( tile_ws + (size_t)s * slot_floats + (size_t)i * kTileF + 2 * pair ) );
-        acc[k].x += part.x;
-        acc[k].y += part.y;
-      }
-    }
-  }
-  float cs[kFinishRows / 4], sn[kFinishRows / 4];
-#pragma unroll
-  for ( int k = 0; k < kFinishRows / 4; k++ ) {
+  for ( int k = 0; k < R; k++ ) {
     const int i = blockIdx.y * kFinishRows + sub + 4 * k;
     // An inactive prompt's position is not checked by the host (it may be any value): its q is don't-care and its
     // K goes nowhere, so nothing of the tables is read for it.
@@ -379,8 +374,36 @@ __global__ void __launch_bounds__( 256, 4 ) project_finish_kernel( const Project
       sn[k] = Conv<T>::to_f32( __ldg( sin_t + ti ) );
     }
   }
+  // the partial sums come from the projection kernel, the kernel before this one in the stream
+  asm volatile( "griddepcontrol.wait;" ::: "memory" );
+  // pieces three at a time, all of their rows' loads in flight, added in their fixed order (the same bits on every
+  // run; a missing piece adds +0, which changes no bit of a sum that started from +0)
+  float2 acc[R];
 #pragma unroll
-  for ( int k = 0; k < kFinishRows / 4; k++ ) {
+  for ( int k = 0; k < R; k++ )
+    acc[k] = make_float2( 0.f, 0.f );
+  for ( int s0 = 0; s0 < nsegs; s0 += kFinishSegs ) {
+    float2 part[kFinishSegs][R];
+#pragma unroll
+    for ( int ds = 0; ds < kFinishSegs; ds++ )
+#pragma unroll
+      for ( int k = 0; k < R; k++ ) {
+        const int i = blockIdx.y * kFinishRows + sub + 4 * k;
+        part[ds][k] = make_float2( 0.f, 0.f );
+        if ( s0 + ds < nsegs && i < batch )
+          part[ds][k] = __ldcg( reinterpret_cast<const float2*>( tile_ws + (size_t)( s0 + ds ) * slot_floats + (size_t)i * kTileF
+                                                                 + 2 * pair ) );
+      }
+#pragma unroll
+    for ( int ds = 0; ds < kFinishSegs; ds++ )
+#pragma unroll
+      for ( int k = 0; k < R; k++ ) {
+        acc[k].x += part[ds][k].x;
+        acc[k].y += part[ds][k].y;
+      }
+  }
+#pragma unroll
+  for ( int k = 0; k < R; k++ ) {
     const int i = blockIdx.y * kFinishRows + sub + 4 * k;
     if ( i >= batch )
       continue;
