@@ -19,6 +19,7 @@ GH_ERR_OOM, GH_ERR_UNSUPPORTED, GH_ERR_STATE, GH_ERR_NOT_FOUND = 5, 6, 7, 8
 GH_F16, GH_F32, GH_BF16 = 0, 1, 2
 GH_COPY_H2D, GH_COPY_D2H, GH_COPY_D2D, GH_COPY_H2H = 0, 1, 2, 3
 GH_BACKING_STATIC, GH_BACKING_PAGED = 0, 1
+GH_ROUTE_POSITION, GH_ROUTE_BALANCED = 0, 1
 
 
 class Config(C.Structure):
@@ -83,6 +84,15 @@ _PROTOS = {
     "gh_decode_noalloc": (C.c_int, [C.POINTER(NoallocShape), _U64, _P, _P, _P, _P, _P]),
     "gh_decode_noalloc_error": (C.c_char_p, []),
     "gh_plan_batch": (C.c_int, [_U32, _U32, _U32, _U32, _U32, _U64, _P, _P, C.POINTER(_U32), C.POINTER(_U32)]),
+    "gh_router_create": (C.c_int, [C.POINTER(_P), _U32, _U32, _U32, _U32]),
+    "gh_router_destroy": (None, [_P]),
+    "gh_router_is_context_available": (C.c_int, [_P]),
+    "gh_router_assign_ranks": (C.c_int, [_P, _U32, _P, _P, _P]),
+    "gh_router_lookup": (C.c_int, [_P, _U64, C.POINTER(_U32)]),
+    "gh_router_note_tokens": (C.c_int, [_P, _U32, _P, _P]),
+    "gh_router_release": (C.c_int, [_P, _U32, _P]),
+    "gh_router_loads": (C.c_int, [_P, _P, _P]),
+    "gh_router_cut": (C.c_int, [_U32, _U32, _P, _P, _P]),
 }
 
 

@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libglinthawk_attn.so"
 SOURCES = ["attn_api.cu", "kv_pool.cu", "gh_driver.cu", "append_kernel.cu", "decode_generic.cu", "decode_mma.cu", "prefill_umma.cu",
-           "qkv_umma.cu", "legacy_ops.cu", "decode_noalloc.cu"]
+           "qkv_umma.cu", "legacy_ops.cu", "decode_noalloc.cu", "router_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 

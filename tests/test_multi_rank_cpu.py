@@ -210,3 +210,47 @@ def test_strong_share_is_found_among_a_rank_s_own_permuted_contexts():
         assert np.array_equal(np.sort(np.concatenate(covered)), np.sort(lens)), "the shares make up the whole request set"
         loads = [int((c + 1).sum()) for c in covered]
         assert max(loads) - min(loads) <= lens.max() + 1
+
+
+def _router_worker(rank: int, world: int, port: int, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from glinthawk_b200.router import BALANCED, ContextRouter
+        wl = WORKLOADS["llama2_70b_gqa"]
+        lens = wl.lengths(20240, 16)
+        router = ContextRouter(world, wl.batch // world, wl.batch, BALANCED)  # every rank replays the same calls
+        ranks = router.assign_ranks(np.arange(wl.batch), lens)
+        mine = np.flatnonzero(ranks == rank)
+        # a second batch: a quarter of the prompts have finished, new ones take their place
+        gone = np.arange(0, wl.batch, 4)
+        router.release(gone)
+        ranks2 = router.assign_ranks(np.concatenate([np.setdiff1d(np.arange(wl.batch), gone), 1000 + gone]),
+                                     np.concatenate([np.delete(lens, gone), lens[gone]]))
+        tokens_mine = float(router.loads()[1][rank])
+        total = dist_util.sum_over_ranks(tokens_mine)
+        worst = dist_util.max_over_ranks(tokens_mine)
+        dist.barrier()
+        out.put((rank, mine.tolist(), ranks2.tolist(), total, worst))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_route_the_same_requests_without_talking():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_router_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(out.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    wl = WORKLOADS["llama2_70b_gqa"]
+    lens = wl.lengths(20240, 16)
+    (_, mine0, again0, total, worst), (_, mine1, again1, *_rest) = results
+    assert sorted(mine0 + mine1) == list(range(wl.batch)) and len(mine0) == len(mine1) == wl.batch // 2
+    assert again0 == again1, "both processes hold the same table after the same calls"
+    assert total == float(lens.sum()) and worst <= 1.02 * total / world
