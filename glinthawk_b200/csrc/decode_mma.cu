@@ -209,11 +209,11 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       asm volatile( "prefetch.tensormap [%0];" ::"l"( reinterpret_cast<uint64_t>( &kv_map ) ) : "memory" );
       // Launched as a programmatic dependent of the kernel before it in the stream (normally the append kernel):
       // everything above overlapped with that kernel; its writes are visible after this wait.
-      asm volatile( "griddepcontrol.wait;" ::: "memory" );
       const size_t row_bytes = (size_t)sh.row_elems * sizeof( T );
       const int row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / (long long)row_bytes ) + it.t_begin;
       const int xk = kvh * kHS;
       const int xv = (int)sh.kv_dim + kvh * kHS;
+      asm volatile( "griddepcontrol.wait;" ::: "memory" );
       for ( int t = 0; t < n_tiles; t++ ) {
         const int s = t % kStages;
         if ( t >= kStages && !mbar_wait( &bar_empty[s], ( ( t / kStages ) - 1 ) & 1 ) ) {
@@ -284,6 +284,9 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   const int v_tok = warp * 16 + ( lm & 1 ) * 8 + lr;  // V: matrices 0,2 -> tokens 0-7, 1,3 -> tokens 8-15
   const int v_chunk_sel = lm >> 1;                    //    matrices 0,1 -> dims +0..7, 2,3 -> dims +8..15
 
+  // Whether some block has already given up on a wait: read here, where the load's latency hides behind the first
+  // tile's, and used after the loop.
+  const uint32_t seen_error = threadIdx.x == 0 ? *reinterpret_cast<volatile uint32_t*>( a.dev_error ) : 0u;
   bool ok = true;
   for ( int t = 0; t < n_tiles; t++ ) {
     const int s = t % kStages;
@@ -389,10 +392,11 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
   }
 
   // ---- combine the warps' states through shared memory (the ring is free once every warp is here)
-  // The consumers meet at two more barriers below, so they must all stay or all leave: one thread reads the error
-  // word, and the barrier itself ORs every thread's verdict into one that is the same for the whole block.
+  // The consumers meet at two more barriers below, so they must all stay or all leave: the barrier itself ORs every
+  // thread's verdict (its own waits and, for one thread, the error word as it was when the block started) into one
+  // that is the same for the whole block.
   uint32_t bad = ok ? 0u : 1u;
-  if ( threadIdx.x == 0 && *reinterpret_cast<volatile uint32_t*>( a.dev_error ) != 0 )
+  if ( seen_error != 0 )
     bad = 1u;
   asm volatile( "{\n"
                 ".reg .pred p, q;\n"
@@ -460,7 +464,7 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       out[( (size_t)( r / group ) * sh.n_heads + ( r % group ) ) * kHS + d] = Conv<T>::from_f32( sm_o[e] / sm_l[r] );
     }
   } else {
-    store_item<T>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
+    store_item<T, kHS>( sh, c, it, kvh * group, group, sm_o, sm_m, sm_l, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
                    threadIdx.x, kConsumers );
 #ifndef GH_DECODE_MERGE_KERNEL // (defined only in comparison builds: the records then go to merge_partials_kernel)
     if ( c.nsplits > 1 ) {
@@ -480,7 +484,7 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
       if ( *sm_last != 0 ) {
         __threadfence();
         static_assert( 16 * ( 2 * kMaxSplits + 1 ) * 4 <= kStages * kStageBytes, "combine scratch must fit the ring" );
-        combine_records<T>( sh, c, it.ctx, kvh * group, group, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
+        combine_records<T, kHS>( sh, c, it.ctx, kvh * group, group, static_cast<T*>( a.xb ), a.part_o, a.part_ml,
                             reinterpret_cast<float*>( ring ), threadIdx.x, kConsumers );
       }
     }

@@ -20,7 +20,8 @@ constexpr int kMaxSplits = 64; // a context is never cut into more work items th
 //
 // `sm_o` [nrows][head_size], `sm_m` [nrows], `sm_l` [nrows] hold the calling block's result for query heads
 // head0 .. head0+nrows-1 in shared memory; threads tid, tid + nthreads, ... of the calling group take part.
-template<typename T>
+// HS: the head size when it is known at compile time (indices then need no division), 0 = take it from the shape.
+template<typename T, int HS = 0>
 __device__ __forceinline__ void store_item( const Shape& sh,
                                             const CtxMeta& c,
                                             const WorkItem& it,
@@ -35,7 +36,7 @@ __device__ __forceinline__ void store_item( const Shape& sh,
                                             const int tid,
                                             const int nthreads )
 {
-  const int hs = sh.head_size;
+  const int hs = HS != 0 ? HS : (int)sh.head_size;
   if ( c.nsplits == 1 ) {
     T* out = xb + (size_t)it.ctx * sh.n_heads * hs + (size_t)head0 * hs;
     for ( int e = tid; e < nrows * hs; e += nthreads )
@@ -54,7 +55,7 @@ __device__ __forceinline__ void store_item( const Shape& sh,
 // For the block of a cut context that arrived last (every record of the context is visible to it): combines the
 // records of query heads head0 .. head0+nrows-1 and writes xb.  `scratch` is shared memory for
 // nrows * (2 * nsplits + 1) floats; barrier `bar_id` is met by all `nthreads` calling threads.
-template<typename T>
+template<typename T, int HS = 0>
 __device__ __forceinline__ void combine_records( const Shape& sh,
                                                  const CtxMeta& c,
                                                  const int ctx_index,
@@ -67,10 +68,29 @@ __device__ __forceinline__ void combine_records( const Shape& sh,
                                                  const int tid,
                                                  const int nthreads )
 {
-  const int hs = sh.head_size, ns = c.nsplits;
+  const int hs = HS != 0 ? HS : (int)sh.head_size, ns = c.nsplits;
   float* sm_ml = scratch;                 // [nrows][ns][2], then the weights in place of m
   float* sm_L = scratch + nrows * ns * 2; // [nrows]
   const size_t rec0 = (size_t)c.partial_base * sh.n_heads + head0;
+  // The combining block sits at the tail of the launch, and its latency is what the launch pays: a thread finishes
+  // kU outputs at a time with the loads of kS records for all of them in flight together, and the first such round
+  // of loads is issued before the records' (m, l) are fetched and turned into weights, so that those two round trips
+  // to memory overlap.
+  constexpr int kU = 8, kS = 4;
+  T* out = xb + (size_t)ctx_index * sh.n_heads * hs + (size_t)head0 * hs;
+  const int n_out = nrows * hs;
+  const size_t rec_stride = (size_t)sh.n_heads * hs;
+  auto load_round = [&]( float ( &v )[kS][kU], const int e0, const int s0 ) {
+#pragma unroll
+    for ( int ds = 0; ds < kS; ds++ )
+#pragma unroll
+      for ( int u = 0; u < kU; u++ ) {
+        const int e = e0 + u * nthreads;
+        v[ds][u] = ( s0 + ds < ns && e < n_out ) ? __ldcg( part_o + rec0 * hs + (size_t)( s0 + ds ) * rec_stride + e ) : 0.f;
+      }
+  };
+  float v[kS][kU];
+  load_round( v, tid, 0 );
   for ( int i = tid; i < nrows * ns; i += nthreads ) {
     const int r = i / ns, sp = i - r * ns;
     const float2 ml = __ldcg( reinterpret_cast<const float2*>( part_ml + ( rec0 + (size_t)sp * sh.n_heads + r ) * 2 ) );
@@ -91,12 +111,6 @@ __device__ __forceinline__ void combine_records( const Shape& sh,
     sm_L[r] = L;
   }
   asm volatile( "bar.sync 1, %0;" ::"r"( nthreads ) : "memory" );
-  // Each thread finishes kU outputs at a time, so that kU loads per record are in flight together: the combining
-  // block sits at the tail of the launch, and its latency is what the launch pays.
-  constexpr int kU = 8;
-  T* out = xb + (size_t)ctx_index * sh.n_heads * hs + (size_t)head0 * hs;
-  const int n_out = nrows * hs;
-  const size_t rec_stride = (size_t)sh.n_heads * hs;
   for ( int e0 = tid; e0 < n_out; e0 += nthreads * kU ) {
     float O[kU];
     int row[kU];
@@ -105,17 +119,16 @@ __device__ __forceinline__ void combine_records( const Shape& sh,
       O[u] = 0.f;
       row[u] = min( e0 + u * nthreads, n_out - 1 ) / hs;
     }
-#pragma unroll 2
-    for ( int sp = 0; sp < ns; sp++ ) {
-      float v[kU];
+    for ( int s0 = 0; s0 < ns; s0 += kS ) {
+      if ( e0 != tid || s0 != 0 ) // (the first round is already here)
+        load_round( v, e0, s0 );
 #pragma unroll
-      for ( int u = 0; u < kU; u++ ) {
-        const int e = e0 + u * nthreads;
-        v[u] = e < n_out ? __ldcg( part_o + rec0 * hs + (size_t)sp * rec_stride + e ) : 0.f;
-      }
+      for ( int ds = 0; ds < kS; ds++ ) // records in their order: the same bits whichever block combines
+        if ( s0 + ds < ns ) {
 #pragma unroll
-      for ( int u = 0; u < kU; u++ )
-        O[u] += sm_ml[( row[u] * ns + sp ) * 2] * v[u];
+          for ( int u = 0; u < kU; u++ )
+            O[u] += sm_ml[( row[u] * ns + s0 + ds ) * 2] * v[ds][u];
+        }
     }
 #pragma unroll
     for ( int u = 0; u < kU; u++ ) {
