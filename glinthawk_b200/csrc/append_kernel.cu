@@ -110,9 +110,10 @@ __global__ void __launch_bounds__( 256, 6 ) append_ordered_kernel( const AppendA
   asm volatile( "griddepcontrol.launch_dependents;" ::: "memory" );
   // Launched as a programmatic dependent of the kernel before it in the stream (normally the previous layer-step's
   // decode kernel), so that this kernel's launch latency hides behind that kernel's tail.  Unless the caller declared
-  // consecutive calls independent, nothing is read or written before that kernel has completed.
-  if ( a.dependent_launch == 1 )
-    asm volatile( "griddepcontrol.wait;" ::: "memory" );
+  // consecutive calls independent, q and the new rows are not read, and nothing is written, before that kernel has
+  // completed (the waits below); the batch description and the rotation tables, which no kernel writes, are
+  // fetched ahead of the wait.
+  const bool wait_first = a.dependent_launch == 1;
   const CtxMeta c = a.ctx[i];
   if ( c.kv_off == kInactive )
     return;
@@ -133,6 +134,8 @@ __global__ void __launch_bounds__( 256, 6 ) append_ordered_kernel( const AppendA
 
   if ( u >= k_chunks + q_chunks ) { // V: plain copy
     const int e = sh.kv_dim + ( u - k_chunks - q_chunks ) * N;
+    if ( wait_first )
+      asm volatile( "griddepcontrol.wait;" ::: "memory" );
     Vec16<T> x[TB];
 #pragma unroll
     for ( int t = 0; t < TB; t++ )
@@ -166,10 +169,15 @@ __global__ void __launch_bounds__( 256, 6 ) append_ordered_kernel( const AppendA
 #pragma unroll
   for ( int t = 0; t < TB; t++ )
     if ( t < n_tok ) {
-      x[t] = ld16( from + (size_t)t * from_stride );
       cs[t] = *reinterpret_cast<const uint2*>( cs0 + (size_t)t * ( sh.head_size / 2 ) );
       sn[t] = *reinterpret_cast<const uint2*>( sn0 + (size_t)t * ( sh.head_size / 2 ) );
     }
+  if ( wait_first )
+    asm volatile( "griddepcontrol.wait;" ::: "memory" );
+#pragma unroll
+  for ( int t = 0; t < TB; t++ )
+    if ( t < n_tok )
+      x[t] = ld16( from + (size_t)t * from_stride );
 #pragma unroll
   for ( int t = 0; t < TB; t++ )
     if ( t < n_tok )
