@@ -953,7 +953,10 @@ int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* 
   if ( const int rc = prepare_layer( h, layer ); rc != GH_OK )
     return rc;
   const cudaStream_t st = static_cast<cudaStream_t>( stream );
-  const DecodeArgs a = decode_args( h, h->cur, h->cur_items, h->cur_split, h->pool.layer_offset( layer ), q, xb );
+  DecodeArgs a = decode_args( h, h->cur, h->cur_items, h->cur_split, h->pool.layer_offset( layer ), q, xb );
+  // Between gh_attn_batch_begin (whose upload orders everything before it) and this launch the library's kernels
+  // write row `pos` of the batch's contexts and nothing else of their K/V.
+  a.stream_old_rows_early = 1;
   if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
     return rc;
   return ring_touch( h, h->cur, st );
@@ -1637,7 +1640,8 @@ int gh_op_attention_fused( gh_attn_t h,
     // every layer of a step names the same slots and positions: one plan and one upload serve them all
     if ( const int rc = op_batch_entry( h, batch, st ); rc != GH_OK )
       return rc;
-    const DecodeArgs a = decode_args( h, h->op_entry, h->op_items, h->op_split, h->pool.layer_offset( own_layer ), query, xb );
+    DecodeArgs a = decode_args( h, h->op_entry, h->op_items, h->op_split, h->pool.layer_offset( own_layer ), query, xb );
+    a.stream_old_rows_early = 1; // (the shared description is only reused while the operations name the same rows)
     if ( const int rc = run_decode( h, a, true, st ); rc != GH_OK )
       return rc;
     return ring_touch( h, h->op_entry, st );

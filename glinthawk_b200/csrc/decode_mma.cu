@@ -207,18 +207,30 @@ __global__ void __launch_bounds__( G::kThreads, G::kMinBlocks )
     // ---------------- producer ----------------
     if ( lane == 0 ) {
       asm volatile( "prefetch.tensormap [%0];" ::"l"( reinterpret_cast<uint64_t>( &kv_map ) ) : "memory" );
-      // Launched as a programmatic dependent of the kernel before it in the stream (normally the append kernel):
-      // everything above overlapped with that kernel; its writes are visible after this wait.
+      // Launched as a programmatic dependent of the kernel before it in the stream (normally the append kernel), so
+      // this block may be running while that kernel still is.  In a decode step that kernel writes one row of the
+      // context, the one at the context's position; every row before it was written at least one step earlier.  The
+      // tiles that end before that row are therefore fetched without waiting for that kernel: the stream of old rows
+      // starts while the append (and the tail of the launch before it) still runs.  The wait comes before the first
+      // tile that reaches the new row, and before anything in chunk mode, where that kernel wrote the whole chunk.
       const size_t row_bytes = (size_t)sh.row_elems * sizeof( T );
       const int row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / (long long)row_bytes ) + it.t_begin;
       const int xk = kvh * kHS;
       const int xv = (int)sh.kv_dim + kvh * kHS;
-      asm volatile( "griddepcontrol.wait;" ::: "memory" );
+      bool waited = false;
+      if ( CHUNK || a.stream_old_rows_early == 0 ) {
+        asm volatile( "griddepcontrol.wait;" ::: "memory" );
+        waited = true;
+      }
       for ( int t = 0; t < n_tiles; t++ ) {
         const int s = t % kStages;
         if ( t >= kStages && !mbar_wait( &bar_empty[s], ( ( t / kStages ) - 1 ) & 1 ) ) {
           atomicOr( a.dev_error, 1u );
           break;
+        }
+        if ( !waited && it.t_begin + ( t + 1 ) * kTile > (int)c.pos ) {
+          asm volatile( "griddepcontrol.wait;" ::: "memory" );
+          waited = true;
         }
         uint8_t* st = ring + s * kStageBytes;
         mbar_expect_tx( &bar_full[s], kStageBytes );

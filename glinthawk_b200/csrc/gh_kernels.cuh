@@ -50,6 +50,9 @@ struct DecodeArgs
   uint32_t sm_count;
   uint32_t chunk_tokens; // 0 = decode step; T = prefill chunk of T tokens per context (tensor-core kernel only)
   uint32_t trigger_early; // 1 = release the next programmatic dependent launch as soon as every block has started
+  uint32_t stream_old_rows_early; // 1 = the kernels before this one in the stream write, of the contexts' K/V, only the
+                                  // row at each context's position (a decode step's append): the tensor-core kernel
+                                  // then fetches the rows before it without waiting for those kernels
 };
 
 struct ScoreArgs // the reference's three unfused operations

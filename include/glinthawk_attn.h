@@ -194,7 +194,12 @@ int gh_attn_append( gh_attn_t h, uint32_t layer, void* q_inout, const void* kv_n
 
 /* attention_0_gemm + attention_softmax + attention_2_gemm in one kernel (src/arch/amd64/llama2/ops.hh:
  * 170-223, 283-298, 225-281): xb[i][head] = softmax_t( q.K_t / sqrt(head_size) ) . V over t <= pos[i], fp32
- * accumulation, no score matrix in memory.  Rows of inactive prompts are left untouched. */
+ * accumulation, no score matrix in memory.  Rows of inactive prompts are left untouched.
+ * The kernel starts fetching the rows BEFORE each context's position while the library's kernels in front of it in
+ * the stream (the append of this step, the tail of the previous layer's launch) are still running; it waits for them
+ * before it touches the row at the position, q or xb.  So the cached rows before the position have to be in place
+ * when gh_attn_batch_begin is called for the batch, which is the case for rows written by earlier steps, by
+ * gh_attn_prefill_chunk calls issued before that gh_attn_batch_begin, by copies, or by kernels of the caller's. */
 int gh_attn_decode( gh_attn_t h, uint32_t layer, const void* q, void* xb, void* stream );
 
 /* gh_attn_append then gh_attn_decode: Llama2::attention_ops with the cache update of pre_attention_ops
