@@ -339,3 +339,62 @@ def test_copy_and_rope_in_one_call_on_foreign_rows(oracle):
         gpu_util.assert_rotation_close(got_rows[i][:kvd], want.rows[i][:kvd], case.kv_new[i][:kvd], case.dtype, f"K {i}")
         gpu_util.assert_rotation_close(got_q[i], want.q[i], case.q[i], case.dtype, f"q {i}")
     st.close()
+
+
+def test_the_appended_row_is_attended_although_old_rows_are_fetched_ahead_of_the_append(oracle):
+    """The decode kernel's producers start fetching a context's old rows while the append in front of the kernel has
+    not run yet (it waits for the previous layer's launch to complete); the tile that holds the new row must come
+    after it.  Three layers are issued back to back, without draining the device, on contexts whose positions sit
+    on and around the 32-token tile boundaries, next to long contexts that keep the previous layer's launch busy.
+    Every new K row is a multiple of its group's (identical) query heads, so nearly all of a head's weight lies on the
+    new row: an output computed from a tile that was fetched before the append wrote it would be nowhere near."""
+    wl = WORKLOADS["llama2_70b_gqa"]
+    sh = wl.shape
+    dtype, tdt = cases.F16, torch.float16
+    rng = np.random.default_rng(31)
+    pos = np.array([0, 1, 30, 31, 32, 33, 63, 64, 65, 95, 96, 127, 128, 129, 1023, 1024]
+                   + list(rng.integers(2500, 4090, size=12)), dtype=np.uint32)
+    B, L, row = len(pos), 3, 2 * sh.kv_dim
+    group, hs = sh.n_heads // sh.n_kv_heads, sh.head_size
+    st = AttentionStage(sh, tdt, n_layers_hosted=L, max_batch=B, max_contexts=B, paged=True)
+    cos, sin = rope_tables(sh.head_size, sh.seq_len, sh.rope_theta)
+    fcr, fci = cases.store(cos, dtype), cases.store(sin, dtype)
+    st.set_rope_tables(gpu_util.to_dev(fcr, dtype), gpu_util.to_dev(fci, dtype))
+    slots = st.get_contexts(np.arange(1, B + 1, dtype=np.uint32))
+    layer_cases, dev = [], []
+    for l in range(L):
+        cache = []
+        for i in range(B):
+            p = int(pos[i])
+            st.prepare(int(slots[i]), l, p)
+            if p > 0:
+                st.fill_normal(st.layer_ptr(int(slots[i]), l), p * row, tdt, 50 + l, offset=i * sh.seq_len * row)
+        torch.cuda.synchronize()
+        for i in range(B):
+            p = int(pos[i])
+            c = np.zeros((p + 1, row), dtype=cases.NP_DTYPE[dtype])
+            if p > 0:
+                c[:p] = gpu_util.to_host(st.layer_view(int(slots[i]), l, p), dtype)
+            cache.append(c)
+        u = rng.standard_normal((B, sh.n_kv_heads, 1, hs), dtype=np.float32)
+        q = cases.store(np.broadcast_to(u, (B, sh.n_kv_heads, group, hs)).reshape(B, sh.dim), dtype)
+        kv_new = np.concatenate([3.0 * u.reshape(B, sh.kv_dim), rng.standard_normal((B, sh.kv_dim), dtype=np.float32)], axis=1)
+        kv_new = cases.store(kv_new, dtype)
+        layer_cases.append(cases.Case(f"early{l}", sh, dtype, pos, np.ones(B, dtype=bool), cache, q, kv_new, fcr, fci, 31))
+        dev.append((gpu_util.to_dev(q, dtype), gpu_util.to_dev(kv_new, dtype), torch.zeros((B, sh.dim), dtype=tdt, device="cuda")))
+    torch.cuda.synchronize()
+    st.batch_begin(slots, pos)
+    for l in range(L):
+        st.step(l, *dev[l])
+    torch.cuda.synchronize()
+    assert st.stats().device_error == 0
+    for l in range(L):
+        want = oracle.layer_step(layer_cases[l])
+        rows = [gpu_util.to_host(st.layer_view(int(slots[i]), l, int(pos[i]) + 1)[int(pos[i])], dtype) for i in range(B)]
+        got = cases.StepResult(rows, gpu_util.to_host(dev[l][0], dtype), gpu_util.to_host(dev[l][2], dtype))
+        gpu_util.assert_step_close(got, want, layer_cases[l])
+        # the construction holds: every head's output is its group's new V row to within rounding
+        v_new = cases.as_f32(layer_cases[l].kv_new[:, sh.kv_dim:], dtype).reshape(B, sh.n_kv_heads, 1, hs)
+        xb = cases.as_f32(got.xb, dtype).reshape(B, sh.n_kv_heads, group, hs)
+        assert np.abs(xb - v_new).max() < 2e-2
+    st.close()
