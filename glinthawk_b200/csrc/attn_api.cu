@@ -1076,7 +1076,8 @@ int gh_attn_prefill_chunk( gh_attn_t h,
       for ( uint32_t g = 0; g * per_item < n_tokens; g++ ) {
         WorkItem w;
         w.ctx = static_cast<int32_t>( i );
-        w.t_begin = 0;
+        // (tcgen05 kernel: the arena row where the context's layer 0 starts; the chunk mode of the decode kernel: 0)
+        w.t_begin = umma ? static_cast<int32_t>( base[i].kv_off / static_cast<long long>( h->pool.geometry().row_bytes ) ) : 0;
         w.t_end = static_cast<int32_t>( pos0[i] + std::min( n_tokens, ( g + 1 ) * per_item ) ); // last token's prefix
         w.split = static_cast<int32_t>( g );
         items.push_back( w );
@@ -1104,6 +1105,7 @@ int gh_attn_prefill_chunk( gh_attn_t h,
       GH_CUDA( h, cudaMemcpyAsync( r.dev, r.host, h->off_items + n * sizeof( WorkItem ), cudaMemcpyHostToDevice, st ) );
       DecodeArgs a = decode_args( h, idx, static_cast<uint32_t>( n ), 0, h->pool.layer_offset( layer ), q_inout, xb );
       a.chunk_tokens = n_tokens;
+      a.layer_row = static_cast<int32_t>( h->pool.layer_offset( layer ) / static_cast<long long>( h->pool.geometry().row_bytes ) );
       if ( umma ) {
         if ( const cudaError_t e = launch_prefill_umma( a, &h->kv_map, &q_map, &xb_map, st, &h->stats.kernel_launches ); e != cudaSuccess )
           return cuda_fail( h, "prefill kernel launch", e );

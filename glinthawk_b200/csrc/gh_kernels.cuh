@@ -49,6 +49,8 @@ struct DecodeArgs
   uint32_t* dev_error;
   uint32_t sm_count;
   uint32_t chunk_tokens; // 0 = decode step; T = prefill chunk of T tokens per context (tensor-core kernel only)
+  int32_t layer_row;     // tcgen05 prompt-chunk kernel: layer_off in rows; its items carry the arena row of their
+                         // context's layer 0 in t_begin, so that a block needs no second look-up before its first copy
   uint32_t trigger_early; // 1 = release the next programmatic dependent launch as soon as every block has started
   uint32_t stream_old_rows_early; // 1 = the kernels before this one in the stream write, of the contexts' K/V, only the
                                   // row at each context's position (a decode step's append): the tensor-core kernel

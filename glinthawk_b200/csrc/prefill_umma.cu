@@ -140,9 +140,7 @@ __global__ void __launch_bounds__( kThreads, 2 )
 
   // The TMA lane sets the barriers up and has the Q block and the first tiles on their way before the rest of the
   // block has finished its own set-up; warp 5 gets the tensor memory.
-  const CtxMeta c = a.ctx[it.ctx];
-  const long long row_bytes = (long long)sh.row_elems * (long long)sizeof( T );
-  const int arena_row0 = static_cast<int>( ( c.kv_off + a.layer_off ) / row_bytes );
+  const int arena_row0 = it.t_begin + a.layer_row; // (the host put the context's first arena row into the item)
   const int xk = kvh * kHS, xv = (int)sh.kv_dim + kvh * kHS;
   // Only boxes holding at least one live key are fetched: rows beyond may lie in pages that are not mapped.
   auto load_tile = [&]( int t, uint8_t* dst, int x, uint64_t* bar ) {
